@@ -1,0 +1,219 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm (with and without the fused
+// residual sum), SwiGLU, and rotary position encoding fused with the paged key/value write.
+// All arithmetic is 32-bit; storage is float or bfloat16 (template parameter).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :].  An id outside [0, vocab) writes zeros and sets the error word.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             T* __restrict__ out, int hidden, int vocab, int* err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  T* dst = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, DSP_ERR_BAD_TOKEN);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  const int vec = 16 / sizeof(T);
+  if ((hidden % vec) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = threadIdx.x; i < hidden / vec; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+extern "C" int dsp_embed(const void* table, const int* ids, void* out, int T, int hidden,
+                         int vocab, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_embed: no device error word");
+  if (dtype == DSP_F32)
+    embed_kernel<float><<<T, 128, 0, stream>>>((const float*)table, ids, (float*)out, hidden, vocab, err);
+  else if (dtype == DSP_BF16)
+    embed_kernel<bf16><<<T, 128, 0, stream>>>((const bf16*)table, ids, (bf16*)out, hidden, vocab, err);
+  else
+    DSP_REQUIRE(false, "dsp_embed: unknown dtype %d", dtype);
+  DSP_CHECK_LAUNCH("dsp_embed");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------ RMSNorm
+// y = w * round_T( x * rsqrt(mean(x^2) + eps) ), x read as 32-bit, the product with w
+// rounded once more to T (for float both roundings are the identity).
+// With `delta`: s = x + delta in 32-bit, rounded to T; the norm is taken of the rounded sum
+// and, if `write_back`, the sum replaces x.  `rows` (optional) gathers input rows; output
+// row i is dense.
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                               const T* __restrict__ w, T* __restrict__ y,
+                               const int* __restrict__ rows, int hidden, float eps,
+                               int write_back) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const size_t in_row = rows ? (size_t)rows[r] : (size_t)r;
+  T* xr = x + in_row * hidden;
+  const T* dr = delta ? delta + in_row * hidden : nullptr;
+  T* yr = y + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_f32(xr[i]);
+    if (dr) {
+      v = to_f32(from_f32<T>(v + to_f32(dr[i])));
+      // stash the rounded sum in y so that the second pass need not redo the sum
+      yr[i] = from_f32<T>(v);
+      if (write_back) xr[i] = from_f32<T>(v);
+    }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = dr ? to_f32(yr[i]) : to_f32(xr[i]);
+    const T n = from_f32<T>(v * rstd);
+    yr[i] = from_f32<T>(to_f32(w[i]) * to_f32(n));
+  }
+}
+
+extern "C" int dsp_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows,
+                           int n_rows, int hidden, float eps, int write_back, int dtype,
+                           cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  DSP_REQUIRE(hidden > 0, "dsp_rmsnorm: hidden=%d", hidden);
+  DSP_REQUIRE(!(write_back && !delta), "dsp_rmsnorm: write_back without delta");
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == DSP_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)x, (const float*)delta,
+                                                          (const float*)w, (float*)y, rows, hidden,
+                                                          eps, write_back);
+  else if (dtype == DSP_BF16)
+    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>((bf16*)x, (const bf16*)delta,
+                                                         (const bf16*)w, (bf16*)y, rows, hidden, eps,
+                                                         write_back);
+  else
+    DSP_REQUIRE(false, "dsp_rmsnorm: unknown dtype %d", dtype);
+  DSP_CHECK_LAUNCH("dsp_rmsnorm");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------- SwiGLU
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g)), in 32-bit.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+  const size_t t = blockIdx.x;
+  const T* g = gu + t * 2 * (size_t)inter;
+  const T* u = g + inter;
+  T* o = out + t * (size_t)inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+    const float gv = to_f32(g[i]);
+    const float uv = to_f32(u[i]);
+    o[i] = from_f32<T>(gv / (1.f + expf(-gv)) * uv);
+  }
+}
+
+extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int dtype,
+                          cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int chunks = (inter + 255) / 256;
+  dim3 grid(T, chunks > 64 ? 64 : chunks);
+  if (dtype == DSP_F32)
+    swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+  else if (dtype == DSP_BF16)
+    swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+  else
+    DSP_REQUIRE(false, "dsp_swiglu: unknown dtype %d", dtype);
+  DSP_CHECK_LAUNCH("dsp_swiglu");
+  return 0;
+}
+
+// ------------------------------------------------- rotary encoding + paged key/value write
+// qkv: [T, (H + 2*KVH) * D], heads in the order q..., k..., v....  One block per (token, head).
+//  q head: rotated in place.
+//  k head: rotated and written to k_pool[page, kvh, offset, :]  (also rotated in place).
+//  v head: copied to v_pool[page, kvh, offset, :].
+// The rotation pairs element i with i + rotary_dim/2 (half-split), angle = pos * inv_freq[i]
+// in 32-bit: out[i] = x[i] cos - x[i+h] sin, out[i+h] = x[i+h] cos + x[i] sin.  Elements at
+// and beyond rotary_dim pass through.  rotary_dim == 0 means no rotation at all.
+// Pool layout: [num_pages, KVH, page_size, D].  page = page_table[seq, pos / page_size].
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ page_table, int pt_stride,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                     const float* __restrict__ inv_freq, int H, int KVH, int D,
+                                     int rotary_dim, int page_size, int num_pages, int write_kv,
+                                     int* err) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;
+  const int pos = positions[t];
+  if (pos < 0) return;  // padding row of a fixed-shape batch
+  T* x = qkv + ((size_t)t * (H + 2 * KVH) + head) * D;
+  const bool is_q = head < H;
+  const bool is_k = !is_q && head < H + KVH;
+  T* dst = nullptr;
+  if (!is_q) {
+    if (!write_kv) return;
+    const int seq = seq_of_token[t];
+    const int page = page_table[(size_t)seq * pt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, DSP_ERR_BAD_PAGE);
+      return;
+    }
+    const int kvh = is_k ? head - H : head - H - KVH;
+    T* pool = is_k ? k_pool : v_pool;
+    dst = pool + (((size_t)page * KVH + kvh) * page_size + (pos % page_size)) * D;
+  }
+  if (is_q || is_k) {
+    const int half = rotary_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float ang = (float)pos * inv_freq[i];
+      float s, c;
+      sincosf(ang, &s, &c);
+      const float a = to_f32(x[i]), b = to_f32(x[i + half]);
+      const T ra = from_f32<T>(a * c - b * s);
+      const T rb = from_f32<T>(b * c + a * s);
+      x[i] = ra;
+      x[i + half] = rb;
+      if (dst) {
+        dst[i] = ra;
+        dst[i + half] = rb;
+      }
+    }
+    if (dst)
+      for (int i = rotary_dim + threadIdx.x; i < D; i += blockDim.x) dst[i] = x[i];
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = x[i];
+  }
+}
+
+extern "C" int dsp_rope_kv_store(void* qkv, const int* positions, const int* seq_of_token,
+                                 const int* page_table, int pt_stride, void* k_pool, void* v_pool,
+                                 const float* inv_freq, int T, int H, int KVH, int D,
+                                 int rotary_dim, int page_size, int num_pages, int write_kv,
+                                 int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  DSP_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
+              "dsp_rope_kv_store: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, D);
+  DSP_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "dsp_rope_kv_store: no inv_freq table");
+  DSP_REQUIRE(H + 2 * KVH <= 65535, "dsp_rope_kv_store: too many heads");
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_rope_kv_store: no device error word");
+  dim3 grid(T, H + 2 * KVH);
+  const int threads = D / 2 >= 64 ? 64 : 32;
+  if (dtype == DSP_F32)
+    rope_kv_store_kernel<float><<<grid, threads, 0, stream>>>(
+        (float*)qkv, positions, seq_of_token, page_table, pt_stride, (float*)k_pool, (float*)v_pool,
+        inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+  else if (dtype == DSP_BF16)
+    rope_kv_store_kernel<bf16><<<grid, threads, 0, stream>>>(
+        (bf16*)qkv, positions, seq_of_token, page_table, pt_stride, (bf16*)k_pool, (bf16*)v_pool,
+        inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+  else
+    DSP_REQUIRE(false, "dsp_rope_kv_store: unknown dtype %d", dtype);
+  DSP_CHECK_LAUNCH("dsp_rope_kv_store");
+  return 0;
+}

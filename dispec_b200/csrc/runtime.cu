@@ -1,0 +1,37 @@
+// Error reporting and the device error word.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[1024] = "";
+
+void dsp_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* dsp_last_error() { return g_error; }
+
+__device__ int g_dsp_device_error = 0;
+
+int* dsp_device_error_ptr() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_dsp_device_error) != cudaSuccess) return nullptr;
+  return p;
+}
+
+// Reads and clears the device error word (synchronises the device).
+extern "C" int dsp_device_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dsp_device_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_dsp_device_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
+extern "C" int dsp_abi_version() { return 1; }

@@ -1,0 +1,93 @@
+"""The step function: runs a batch of (request, its next tokens) from the cache and returns
+the logits at the wanted places.
+
+``ModelRunner`` owns the cache manager, the device pools and the state buffers of one model.
+``step(entries)`` runs only the tokens it is given, as one flat batch (portions of prompts
+beside single decoded tokens), and leaves their keys and values in the pages.  It plays the
+role of ``ModelRunner.forward`` + ``ModelRunner.logits`` of the reference (puneethgv/DiSpec
+dispec/engine/model_runner.py:188-231) with the bookkeeping its callers do by hand
+(dispec/sched/scheduler.py:132-197) moved behind one call.
+"""
+from __future__ import annotations
+
+import torch
+
+from dispec_b200 import ops
+from dispec_b200.cache.manager import CacheManager
+from dispec_b200.cache.storage import CacheStorage, StateStorage
+from dispec_b200.engine.batch import HostStaging, SeqEntry, build_context
+from dispec_b200.models.model import DecoderModel
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, page_size: int = 16, num_pages=4096,
+                 max_num_seqs: int = 256, poison: bool = False):
+        if model.device is None:
+            raise ValueError("the model has no weights yet (load it first)")
+        self.model = model
+        self.dtype = model.dtype
+        self.device = model.device
+        self.page_size = page_size
+        groups = model.cache_groups
+        counts = [num_pages] * len(groups) if isinstance(num_pages, int) else list(num_pages)
+        self.cache = CacheManager(groups, page_size, counts, max_num_seqs)
+        self.storage = CacheStorage(groups, page_size, counts, self.dtype, self.device, poison=poison)
+        self.states = StateStorage(model.state_needs, max_num_seqs, self.device)
+        self.staging = HostStaging(self.device)
+        self.poison = poison  # tests: pages given back are filled with NaN
+        self.vocab_size = model.spec.vocab_size
+        self.num_steps = 0
+
+    # ---------------------------------------------------------------- request lifecycle
+    def admit(self, req_id, prompt_len: int = 0, max_total_len: int = 0, max_chunk: int = 1) -> None:
+        slot = self.cache.admit(req_id, prompt_len, max_total_len, max_chunk)
+        if self.states.buffers:
+            self.states.reset_slot(slot)
+
+    def release(self, req_id) -> None:
+        self._poison(self.cache.free(req_id))
+
+    def _poison(self, released) -> None:
+        if self.poison and released:
+            for g in range(len(self.cache.groups)):
+                self.storage.poison_pages(g, [p for gg, p in released if gg == g])
+
+    # ----------------------------------------------------------------------- the step
+    @torch.inference_mode()
+    def step(self, entries: list[SeqEntry]) -> torch.Tensor:
+        """Logits [number of wanted places, vocab] in float32, in the order of ``entries`` and
+        of each entry's ``want``."""
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.req_id in seen:
+                raise ValueError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if not self.cache.has(e.req_id):
+                raise KeyError(f"request {e.req_id!r} was not admitted")
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.req_id!r} brings no tokens")
+            stored = self.cache.num_tokens(e.req_id)
+            if e.start != stored:
+                raise ValueError(f"request {e.req_id!r}: tokens start at position {e.start} but "
+                                 f"{stored} tokens are stored")
+        for e in entries:  # may raise OutOfPagesError before anything ran
+            self.cache.extend(e.req_id, e.start + len(e.tokens))
+        ctx, _ = build_context(entries, self.cache, self.storage, self.states, self.staging,
+                               self.dtype, self.device, self.model.attention_tile_tokens,
+                               self.vocab_size)
+        x, pending = self.model.forward(ctx)
+        n_rows = ctx.logit_rows.shape[0]
+        if n_rows:
+            logits = self.model.logits(ctx, x, pending, ctx.logit_rows)
+        else:
+            logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        for e in entries:
+            self._poison(self.cache.commit(e.req_id, e.start + len(e.tokens)))
+        self.num_steps += 1
+        return logits
+
+    def check_device(self, where: str = "step") -> None:
+        """Raises if a kernel recorded a bad page or token id (synchronises)."""
+        ops.raise_on_device_error(where)

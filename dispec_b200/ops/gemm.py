@@ -1,0 +1,94 @@
+"""y = x W^T (+ bias) (+ residual): the one matrix product the model uses.
+
+float32: the FMA kernel (``dsp_gemm_simt``), always; no tensor cores, no reduced-precision
+mode, one FMA chain per output so that a row does not depend on its batch.
+bfloat16: the weight-streaming tensor-core kernel for up to 64 rows (decoding and the
+rows whose logits are wanted); above that, ``LARGE_BACKEND`` picks the tensor-core kernel
+of this package or the library matrix product (cuBLAS through torch.matmul), which is where
+the reference engine itself calls a library (puneethgv/DiSpec
+dispec/engine/model_runner.py:132,158,225-226,231).
+"""
+from __future__ import annotations
+
+import torch
+
+from dispec_b200.ops import library as L
+
+SKINNY_MAX_ROWS = 0  # rows the weight-streaming kernel takes (0: kernel not built in)
+LARGE_BACKEND = "library"  # "library" | "simt"
+
+
+def _simt(x, w, bias, residual, out):
+    M, K = x.shape
+    N = w.shape[0]
+    L.check(L.core().dsp_gemm_simt(
+        L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
+        L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
+        M, N, K, L.dtype_code(x.dtype), L.dtype_code(out.dtype), L.stream_handle()))
+    return out
+
+
+def _skinny(x, w, bias, residual, out):
+    M, K = x.shape
+    N = w.shape[0]
+    L.check(L.core().dsp_gemm_skinny(
+        L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
+        L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
+        M, N, K, L.dtype_code(out.dtype), L.stream_handle()))
+    return out
+
+
+def skinny_supported(M: int, N: int, K: int, x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+           out: torch.Tensor | None = None, backend: str | None = None) -> torch.Tensor:
+    """x [M, K] (row stride free, unit column stride), w [N, K] contiguous, bias [N],
+    residual [M, N] of the output type.  Output type: ``out_dtype`` (default: x's);
+    bfloat16 inputs may produce float32 (logits)."""
+    if not (x.is_cuda and w.is_cuda):
+        raise L.KernelError("linear: CUDA tensors only (there is no CPU path)")
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
+    assert x.stride(1) == 1 and w.is_contiguous() and x.dtype == w.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or (out.dtype if out is not None else x.dtype)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype == out_dtype
+    if bias is not None:
+        assert bias.shape == (N,) and bias.dtype == x.dtype and bias.is_contiguous()
+    if residual is not None:
+        assert residual.shape == (M, N) and residual.dtype == out_dtype and residual.stride(1) == 1
+    if M == 0:
+        return out
+    if x.dtype == torch.float32:
+        assert out_dtype == torch.float32
+        return _simt(x, w, bias, residual, out)
+    if backend is None:
+        if skinny_supported(M, N, K, x, w):
+            backend = "skinny"
+        elif out_dtype == torch.bfloat16 and M > SKINNY_MAX_ROWS:
+            backend = LARGE_BACKEND
+        else:
+            backend = "simt"
+    if backend == "skinny":
+        return _skinny(x, w, bias, residual, out)
+    if backend == "library":
+        # the library matrix product; bias and residual are folded in by the library as well
+        assert out_dtype == torch.bfloat16
+        if residual is not None:
+            if out.data_ptr() != residual.data_ptr():
+                out.copy_(residual)
+            out.addmm_(x, w.t())
+            if bias is not None:
+                out.add_(bias)
+        elif bias is not None:
+            torch.addmm(bias, x, w.t(), out=out)
+        else:
+            torch.mm(x, w.t(), out=out)
+        return out
+    return _simt(x, w, bias, residual, out)

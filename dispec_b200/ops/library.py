@@ -1,0 +1,91 @@
+"""Loads the compiled kernel libraries (ctypes, C ABI over raw device pointers).
+
+There is no fallback: if the library cannot be built or loaded, importing an op raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from dispec_b200.csrc import build
+
+F32, BF16 = 0, 1
+
+_core = None
+_special: dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def core() -> ctypes.CDLL:
+    global _core
+    if _core is None:
+        with _lock:
+            if _core is None:
+                path = build.core_library()
+                lib = ctypes.CDLL(path)
+                lib.dsp_last_error.restype = ctypes.c_char_p
+                _core = lib
+    return _core
+
+
+def attention_library(head_dim: int) -> ctypes.CDLL:
+    key = f"attn_mma_d{head_dim}"
+    if key not in _special:
+        with _lock:
+            if key not in _special:
+                _special[key] = ctypes.CDLL(build.attention_library(head_dim))
+    return _special[key]
+
+
+def loaded_libraries() -> list[str]:
+    out = [] if _core is None else [_core._name]
+    return out + [lib._name for lib in _special.values()]
+
+
+def check(rc: int, lib: ctypes.CDLL | None = None) -> None:
+    if rc != 0:
+        msg = core().dsp_last_error()
+        raise KernelError(msg.decode() if msg else f"kernel library returned {rc}")
+
+
+def device_error() -> int:
+    """Reads and clears the device error word (synchronises)."""
+    return int(core().dsp_device_error())
+
+
+def raise_on_device_error(where: str) -> None:
+    v = device_error()
+    if v:
+        names = [n for bit, n in ((1, "page id outside the pool"), (2, "token id outside the vocabulary"),
+                                  (4, "a bounded wait ran out")) if v & bit]
+        raise KernelError(f"{where}: device reported: {', '.join(names) or v}")
+
+
+def ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream_handle() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def i64(v: int) -> ctypes.c_long:
+    return ctypes.c_long(int(v))
+
+
+def f32(v: float) -> ctypes.c_float:
+    return ctypes.c_float(float(v))

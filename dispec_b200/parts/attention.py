@@ -1,0 +1,80 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v = h W^T + b (one fused product, rows ordered q, k, v: puneethgv/DiSpec
+dispec/engine/model_runner.py:104-118,131-136); rotation of q and k and the write of k, v
+into the pages (:145-148); scores scaled by ``scale`` (default head_dim**-0.5, :72), key b
+visible to the query at position p iff b <= p (and b > p - window for a window layer), softmax
+and weighted sum in 32-bit (:160-183 and dispec/engine/triton_attn.py:59-95); output
+projection without bias (:158,185).
+"""
+from __future__ import annotations
+
+import torch
+
+from dispec_b200 import ops
+from dispec_b200.ops import attention as attn_ops
+from dispec_b200.parts.base import KVNeed, Mixer, TensorSpec
+from dispec_b200.registry import register_part
+
+
+@register_part("mixer", "gqa_attention")
+class GQAAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, position_encoding, window: int = 0, scale: float | None = None,
+                 out_bias: bool = False):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.qkv_bias = qkv_bias
+        self.out_bias = out_bias
+        self.window = window
+        self.scale = head_dim ** -0.5 if scale is None else scale
+        self.position_encoding = position_encoding
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    def tensor_specs(self):
+        h, d = self.hidden_size, self.head_dim
+        specs = {
+            "q_proj.weight": TensorSpec((self.num_heads * d, h)),
+            "k_proj.weight": TensorSpec((self.num_kv_heads * d, h)),
+            "v_proj.weight": TensorSpec((self.num_kv_heads * d, h)),
+            "o_proj.weight": TensorSpec((h, self.num_heads * d)),
+        }
+        if self.qkv_bias:
+            specs["q_proj.bias"] = TensorSpec((self.num_heads * d,))
+            specs["k_proj.bias"] = TensorSpec((self.num_kv_heads * d,))
+            specs["v_proj.bias"] = TensorSpec((self.num_kv_heads * d,))
+        if self.out_bias:
+            specs["o_proj.bias"] = TensorSpec((h,))
+        return specs
+
+    def load(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                tensors["v_proj.weight"]], dim=0).contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+                                    tensors["v_proj.bias"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"]
+        self.b_o = tensors.get("o_proj.bias")
+
+    def cache_need(self):
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def tokens_per_attention_tile(self):
+        return attn_ops.tokens_per_tile(self.num_heads // self.num_kv_heads)
+
+    def forward(self, ctx, x, cache, state):
+        H, KVH, D = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        pe = self.position_encoding
+        ops.rope_kv_store(qkv, ctx.positions, ctx.seq_of_token, cache.page_table,
+                          cache.key_pool if cache.write else None,
+                          cache.value_pool if cache.write else None,
+                          pe.inv_freq, H, KVH, D, pe.rotary_dim, write_kv=cache.write)
+        out = torch.empty((x.shape[0], H * D), dtype=x.dtype, device=x.device)
+        attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
+                                 self.scale)
+        return ops.linear(out, self.w_o, self.b_o)

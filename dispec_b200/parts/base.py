@@ -1,0 +1,118 @@
+"""Interfaces of the parts a decoder is assembled from.
+
+A part owns its sizes and constants (constructor arguments), declares the tensors it
+needs (``tensor_specs``), receives them once (``load``) and runs on a flat batch of
+tokens described by a ``StepContext``.  No part knows which model it is in: what it
+needs from outside arrives as an argument (another part object, a cache view, a state
+view).
+
+Roles and their required methods:
+
+* ``Norm.forward(ctx, x, rows=None) -> y`` and
+  ``Norm.forward_add(ctx, residual, delta) -> y`` (adds ``delta`` into ``residual`` in
+  place in 32-bit, then normalises the sum).
+* ``PositionEncoding``: whatever its mixers consume; the rotary one exposes
+  ``inv_freq`` and ``rotary_dim`` for the q/k rotation kernel.
+* ``Mixer.forward(ctx, x, cache, state) -> y``; ``cache_need()`` says what kind of
+  key/value cache a call of this mixer needs (or None), ``state_need()`` what
+  fixed-size per-request state (or None).
+* ``FeedForward.forward(ctx, x) -> y``.
+* ``Block.forward(ctx, x, cache, state) -> x``: the arrangement of two norms, a mixer
+  and a feed-forward with their residual sums.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """Shape and storage class of one tensor a part needs.
+
+    ``dtype``: "model" follows the engine (bfloat16, or float32 on the 32-bit path);
+    "float32" stays 32-bit in every mode; "int32" is an integer table.
+    ``init`` tells the random-weights mode how to draw it: "normal" is N(0, std),
+    "one_plus_normal" is 1 + N(0, std) (gains), "zeros" is 0.
+    """
+    shape: tuple[int, ...]
+    dtype: str = "model"
+    init: str = "normal"
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """Declarative description of one part: registered kind, constructor parameters,
+    and the checkpoint tensor name behind each of the part's local tensor names."""
+    role: str
+    kind: str
+    params: dict[str, Any] = field(default_factory=dict)
+    tensors: dict[str, str] = field(default_factory=dict)  # local name -> checkpoint name
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Key/value cache one mixer call needs. ``window`` 0: all keys stay; W > 0: only
+    the last W positions are ever read, older pages can be given back."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Fixed-size per-request state of one mixer call: a tensor of ``shape`` per live
+    request, zeroed when a request is admitted."""
+    shape: tuple[int, ...]
+    dtype: str = "float32"
+
+
+class Part:
+    role = ""
+    kind = ""
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no tensors")
+
+
+class Norm(Part):
+    def forward(self, ctx, x, rows=None):
+        raise NotImplementedError
+
+    def forward_add(self, ctx, residual, delta):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def tokens_per_attention_tile(self) -> int | None:
+        """Query tokens per attention tile this mixer wants listed in the batch (or None)."""
+        return None
+
+    def forward(self, ctx, x, cache, state):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, ctx, x, pending, cache, state):
+        raise NotImplementedError
