@@ -1,0 +1,305 @@
+"""Each CUDA kernel alone against a plain float32 torch restatement of the same operation,
+at sizes that differ from the engine's test configurations (widths and vocabularies that are
+no power of two, odd head counts, page sizes 8/16/32)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    from dispec_b200 import ops
+    table = rnd((301, 88), dtype, 1)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=dev())
+    out = ops.embed(table, ids)
+    assert torch.equal(out, table[ids.long()])
+    table2 = rnd((50, 33), dtype, 2)  # row bytes not a multiple of 16
+    out2 = ops.embed(table2, ids[:1] * 0 + 49)
+    assert torch.equal(out2, table2[49:50])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [96, 1536, 200])
+def test_rms_norm(dtype, hidden):
+    from dispec_b200 import ops
+    x = rnd((7, hidden), dtype, 3, 2.0)
+    w = (1 + rnd((hidden,), torch.float32, 4, 0.1)).to(dtype)
+    eps = 1e-5
+    y = ops.rms_norm(x, w, eps)
+    xf = x.float()
+    n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype).float()
+    ref = (w.float() * n).to(dtype)
+    torch.testing.assert_close(y.float(), ref.float(), **tol(dtype))
+    # fused residual sum, written back
+    d = rnd((7, hidden), dtype, 5)
+    x2 = x.clone()
+    y2 = ops.rms_norm(x2, w, eps, delta=d, write_back=True)
+    s = (x.float() + d.float()).to(dtype)
+    assert torch.equal(x2, s)
+    sf = s.float()
+    n2 = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype).float()
+    torch.testing.assert_close(y2.float(), (w.float() * n2).to(dtype).float(), **tol(dtype))
+    # gathered rows, nothing written back
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=dev())
+    x3 = x.clone()
+    y3 = ops.rms_norm(x3, w, eps, delta=d, rows=rows)
+    assert torch.equal(x3, x)
+    torch.testing.assert_close(y3.float(), y2[rows.long()].float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from dispec_b200 import ops
+    gu = rnd((5, 2 * 224), dtype, 6, 3.0)
+    out = ops.swiglu(gu)
+    g, u = gu[:, :224].float(), gu[:, 224:].float()
+    ref = (g * torch.sigmoid(g) * u).to(dtype)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 100, 96), (5, 130, 224), (70, 257, 40), (33, 64, 1536)])
+def test_gemm_fma(dtype, M, N, K):
+    from dispec_b200.ops import gemm
+    x = rnd((M, K), dtype, 7)
+    w = rnd((N, K), dtype, 8, 0.1)
+    b = rnd((N,), dtype, 9)
+    r = rnd((M, N), dtype, 10)
+    out = gemm.linear(x, w, b, r, backend="simt")
+    ref = (x.double() @ w.double().T + b.double() + r.double())
+    torch.testing.assert_close(out.double(), ref, **tol(dtype))
+    out32 = gemm.linear(x, w, out_dtype=torch.float32, backend="simt")
+    torch.testing.assert_close(out32.double(), x.double() @ w.double().T, atol=1e-4, rtol=1e-4)
+
+
+def test_gemm_fma_rows_do_not_depend_on_batch():
+    from dispec_b200.ops import gemm
+    x = rnd((37, 200), torch.float32, 11)
+    w = rnd((77, 200), torch.float32, 12)
+    full = gemm.linear(x, w)
+    one = gemm.linear(x[20:21].contiguous(), w)
+    assert torch.equal(full[20:21], one)
+
+
+def _rope_reference(x, pos, theta, rotary_dim):
+    half = rotary_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+    ang = pos.float()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    a, b = x[..., :half], x[..., half:rotary_dim]
+    out[..., :half] = a * c - b * s
+    out[..., half:rotary_dim] = b * c + a * s
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,D,rot,page", [(3, 1, 32, 32, 8), (6, 2, 48, 48, 16), (4, 4, 16, 8, 32)])
+def test_rope_kv_store(dtype, H, KVH, D, rot, page):
+    from dispec_b200 import ops
+    T, num_pages = 9, 7
+    theta = 50000.0
+    qkv = rnd((T, (H + 2 * KVH) * D), dtype, 13)
+    # two sequences: seq 0 holds positions 14..18 (crosses a page edge), seq 1 positions 0..3
+    pos = torch.tensor([14, 15, 16, 17, 18, 0, 1, 2, 3], dtype=torch.int32)
+    seq = torch.tensor([0] * 5 + [1] * 4, dtype=torch.int32)
+    table = torch.tensor([[5, 2, 6, 0], [3, -1, -1, -1]], dtype=torch.int32)
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=dtype, device=dev())
+    vp = kp.clone()
+    inv = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev())
+    q0 = qkv.clone()
+    ops.rope_kv_store(qkv, pos.to(dev()), seq.to(dev()), table.to(dev()), kp, vp, inv, H, KVH, D, rot)
+    x = q0.float().cpu().view(T, H + 2 * KVH, D)
+    ref_qk = _rope_reference(x[:, :H + KVH], pos, theta, rot)
+    got = qkv.float().cpu().view(T, H + 2 * KVH, D)
+    torch.testing.assert_close(got[:, :H + KVH], ref_qk.to(dtype).float(), **tol(dtype))
+    assert torch.equal(got[:, H + KVH:], x[:, H + KVH:])
+    for t in range(T):
+        p, s = int(pos[t]), int(seq[t])
+        pg = int(table[s, p // page])
+        torch.testing.assert_close(kp[pg, :, p % page].float().cpu(), got[t, H:H + KVH], atol=0, rtol=0)
+        torch.testing.assert_close(vp[pg, :, p % page].float().cpu(), got[t, H + KVH:], atol=0, rtol=0)
+    # nothing else was touched
+    written = torch.zeros((num_pages, page), dtype=torch.bool)
+    for t in range(T):
+        written[int(table[int(seq[t]), int(pos[t]) // page]), int(pos[t]) % page] = True
+    assert torch.isnan(kp.float().cpu().permute(0, 2, 1, 3)[~written]).all()
+
+
+def _attention_reference(q, k, v, positions, window, scale):
+    """q [T,H,D] (T tokens of one sequence at ``positions``), k/v [ctx,KVH,D] in float64."""
+    T, H, D = q.shape
+    G = H // k.shape[1]
+    out = torch.zeros(T, H, D, dtype=torch.float64)
+    for t in range(T):
+        p = int(positions[t])
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(H):
+            s = (k[lo:p + 1, h // G] @ q[t, h]) * scale
+            out[t, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // G]
+    return out
+
+
+def _paged(k, v, page, num_pages, dtype, seed):
+    """Scatter contiguous k/v [ctx,KVH,D] into pools through a shuffled page table."""
+    ctx, KVH, D = k.shape
+    n = (ctx + page - 1) // page
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g)[:n]
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=dtype)
+    vp = kp.clone()
+    for b in range(ctx):
+        kp[perm[b // page], :, b % page] = k[b].to(dtype)
+        vp[perm[b // page], :, b % page] = v[b].to(dtype)
+    return kp.to(dev()), vp.to(dev()), perm.to(torch.int32)
+
+
+ATTN_CASES = [
+    # H, KVH, D, page, ctx, q_len, window
+    (4, 2, 16, 16, 33, 33, 0),
+    (3, 1, 32, 8, 70, 5, 0),
+    (6, 2, 48, 16, 300, 1, 0),
+    (12, 2, 128, 16, 257, 17, 0),
+    (4, 2, 16, 8, 90, 90, 12),
+    (6, 2, 32, 16, 200, 3, 40),
+    (9, 1, 64, 32, 140, 1, 64),
+]
+
+
+def run_attention(kind, dtype, H, KVH, D, page, ctx, q_len, window, plant=None, seed=0):
+    """One sequence, its last q_len positions as queries.  ``plant``: key index whose score is
+    made to stand out for every query that can see it."""
+    from dispec_b200.ops import attention as A
+    g = torch.Generator().manual_seed(100 + seed)
+    q = torch.randn(q_len, H, D, generator=g)
+    k = torch.randn(ctx, KVH, D, generator=g)
+    v = torch.randn(ctx, KVH, D, generator=g)
+    if plant is not None:
+        G = H // KVH
+        for kvh in range(KVH):
+            direction = q[:, kvh * G:(kvh + 1) * G].mean(dim=(0, 1))
+            q[:, kvh * G:(kvh + 1) * G] += 3.0 * direction / direction.norm()
+            k[plant, kvh] = 12.0 * direction / direction.norm()
+    q, k, v = q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float()
+    positions = torch.arange(ctx - q_len, ctx, dtype=torch.int32)
+    scale = D ** -0.5
+    ref = _attention_reference(q.double(), k.double(), v.double(), positions, window, scale)
+    num_pages = (ctx + page - 1) // page + 3
+    kp, vp, perm = _paged(k, v, page, num_pages, dtype, seed)
+    table = perm.view(1, -1).to(dev())
+    qd = q.to(dtype).reshape(q_len, H * D).to(dev())
+    out = torch.empty((q_len, H * D), dtype=dtype, device=dev())
+    seq = torch.zeros(q_len, dtype=torch.int32, device=dev())
+    if kind == "generic":
+        A.paged_attention_generic(qd, H * D, kp, vp, table, positions.to(dev()), seq, out, H, KVH, D,
+                                  window, scale)
+    else:
+        A.paged_attention_tensor_core(qd, H * D, kp, vp, table, positions.to(dev()), seq, out, H, KVH,
+                                      D, window, scale, q_lens=[q_len], ctx_lens=[ctx])
+    return out.float().cpu().view(q_len, H, D).double(), ref
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_generic(dtype, case):
+    out, ref = run_attention("generic", dtype, *case)
+    torch.testing.assert_close(out, ref, **(dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32
+                                           else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("plant", [0, 7, 8, 15, 16, 17, 127, 128, 255, 256])
+def test_attention_generic_far_key_stands_out(plant):
+    # one key among hundreds carries the result: a skipped or misplaced key (page edge, tile edge)
+    # changes the output completely
+    out, ref = run_attention("generic", torch.float32, 4, 2, 32, 16, 300, 2, 0, plant=plant, seed=plant)
+    torch.testing.assert_close(out, ref, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("offset", [-1, 0, 1])
+def test_attention_generic_window_edge(offset):
+    # the planted key sits just outside (offset -1), on (0) and just inside (+1) the window's far
+    # edge of the last query
+    ctx, window = 150, 40
+    plant = ctx - 1 - window + 1 + offset
+    out, ref = run_attention("generic", torch.float32, 4, 2, 32, 16, ctx, 1, window, plant=plant, seed=5)
+    torch.testing.assert_close(out, ref, atol=1e-5, rtol=1e-5)
+
+
+def test_argmax_ties_go_to_the_lowest_index():
+    from dispec_b200 import ops
+    x = torch.randn(5, 1000, generator=torch.Generator().manual_seed(1))
+    x[0, 700] = x[0, 20] = 9.0
+    x[1, 999] = 10.0
+    x[2, 0] = 10.0
+    got = ops.argmax(x.to(dev())).cpu()
+    assert got.tolist() == [20, 999, 0, int(x[3].argmax()), int(x[4].argmax())]
+    # a large vocabulary that is no power of two
+    y = torch.randn(3, 151937, generator=torch.Generator().manual_seed(2))
+    assert ops.argmax(y.to(dev())).cpu().tolist() == y.argmax(-1).tolist()
+
+
+def test_sampling_matches_plain_inverse_cdf():
+    import plain_qwen2 as plain
+    from dispec_b200 import ops
+    V = 1003
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(8, V, generator=g) * 3
+    cases = [(0.8, 0, 1.0), (1.3, 10, 1.0), (0.7, 0, 0.9), (1.0, 50, 0.5), (0.0, 0, 1.0),
+             (2.0, 1, 1.0), (0.5, 0, 0.01), (1.0, 2000, 0.999)]
+    us = [0.03, 0.5, 0.77, 0.999, 0.4, 0.6, 0.9, 0.25]
+    t = torch.tensor([c[0] for c in cases], dtype=torch.float32, device=dev())
+    k = torch.tensor([c[1] for c in cases], dtype=torch.int32, device=dev())
+    p = torch.tensor([c[2] for c in cases], dtype=torch.float32, device=dev())
+    u = torch.tensor(us, dtype=torch.float32, device=dev())
+    got = ops.sample(logits.to(dev()), t, k, p, u).cpu().tolist()
+    for r, (temp, tk, tp) in enumerate(cases):
+        probs = plain.sampling_distribution(logits[r], temp, tk, tp)
+        want = plain.draw_inverse_cdf(probs, us[r]) if temp > 0 else int(logits[r].argmax())
+        assert probs[got[r]] > 0, (r, got[r])
+        assert got[r] == want, (r, got[r], want)
+
+
+def test_sampling_distribution_is_the_masked_softmax():
+    import plain_qwen2 as plain
+    from dispec_b200 import ops
+    V, n = 50, 4000
+    logits = (torch.randn(V, generator=torch.Generator().manual_seed(4)) * 2)
+    probs = plain.sampling_distribution(logits, 0.9, 12, 0.8)
+    u = torch.rand(n, generator=torch.Generator().manual_seed(5))
+    rows = logits[None].expand(n, V).contiguous().to(dev())
+    got = ops.sample(rows, torch.full((n,), 0.9, device=dev()), torch.full((n,), 12, dtype=torch.int32, device=dev()),
+                     torch.full((n,), 0.8, device=dev()), u.to(dev())).cpu()
+    freq = torch.bincount(got.long(), minlength=V).double() / n
+    assert (freq[probs == 0] == 0).all()
+    assert (freq - probs).abs().max().item() < 4 * math.sqrt(0.25 / n)
+
+
+def test_sampling_keeps_ties_at_the_kth_value():
+    from dispec_b200 import ops
+    logits = torch.full((1, 64), -5.0)
+    logits[0, [3, 9, 40]] = 2.0  # three tokens tie for the top; top_k = 2 keeps all three
+    seen = set()
+    for u in [0.01, 0.34, 0.5, 0.67, 0.99]:
+        got = ops.sample(logits.to(dev()), torch.tensor([1.0], device=dev()),
+                         torch.tensor([2], dtype=torch.int32, device=dev()),
+                         torch.tensor([1.0], device=dev()), torch.tensor([u], device=dev()))
+        seen.add(int(got[0]))
+    assert seen == {3, 9, 40}
