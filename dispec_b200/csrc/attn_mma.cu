@@ -1,0 +1,328 @@
+// Causal grouped-query attention over the paged cache on the tensor cores, bfloat16 in, 32-bit
+// softmax and accumulation.  Compiled once per head size (-DDSP_HEAD_DIM=...).
+//
+// A tile is 64 query rows of one KV head of one sequence; a row is a (token, head-in-group)
+// pair, so the G query heads that share a KV head share every key/value load, and a single
+// decoded token fills G rows.  Keys are walked in tiles of 64 through the page table
+// (cp.async, two stages).  S = Q K^T and O += P V are mma.m16n8k16; the softmax is the online
+// form (running max and sum per row, base 2).  The query at position p sees keys b with
+// max(0, p - window + 1) <= b <= p.  With num_splits > 1 the key tiles of a query tile are
+// divided among grid.z CTAs, each writing an unnormalised partial (o, m, l) per row; a second
+// kernel (dsp_attn_combine) merges them.
+//
+// Shared memory rows are 16-byte pieces XOR-swizzled by the row index, so ldmatrix reads are
+// conflict-free for head sizes of 64 and above.  Keys at or beyond the sequence length, and keys
+// on pages that were given back, are zero-filled, never read.
+#include "common.cuh"
+
+#ifndef DSP_HEAD_DIM
+#error "compile with -DDSP_HEAD_DIM=<head size>"
+#endif
+
+#define DSP_CAT2(a, b) a##b
+#define DSP_CAT(a, b) DSP_CAT2(a, b)
+
+namespace {
+constexpr int D = DSP_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int BM = 64, BN = 64, THREADS = 128;
+constexpr int CHUNKS = D / 8;  // 16-byte pieces per row
+constexpr int ROW_CHUNKS = CHUNKS <= 2 ? 2 : CHUNKS <= 4 ? 4 : ((CHUNKS + 7) / 8) * 8;
+constexpr int SW_MASK = (ROW_CHUNKS < 8 ? ROW_CHUNKS : 8) - 1;
+constexpr int ROW_BYTES = ROW_CHUNKS * 16;
+constexpr int TILE_BYTES = 64 * ROW_BYTES;
+
+struct Params {
+  const bf16* q;
+  long q_stride;
+  const bf16* k_pool;
+  const bf16* v_pool;
+  const int* page_table;
+  int pt_stride;
+  const int* q_start;
+  const int* ctx_len;
+  const int* tile_seq;
+  const int* tile_tok0;
+  bf16* out;
+  long out_stride;
+  float* part_o;   // [(t * H + h) * splits + split][D]
+  float* part_ml;  // [(t * H + h) * splits + split][2]
+  int H, KVH, G, tokens_per_tile, page_size, num_pages, window, num_splits;
+  float scale_log2;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t sw(int row, int chunk) {
+  return (uint32_t)(row * ROW_BYTES + ((chunk ^ (row & SW_MASK)) << 4));
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int tile_offset) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t q_s = s_base;
+  const uint32_t k_s[2] = {s_base + TILE_BYTES, s_base + 2 * TILE_BYTES};
+  const uint32_t v_s[2] = {s_base + 3 * TILE_BYTES, s_base + 4 * TILE_BYTES};
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g4 = lane >> 2, c4 = lane & 3;
+  const int tile = blockIdx.x + tile_offset, kvh = blockIdx.y, split = blockIdx.z;
+  const int seq = p.tile_seq[tile], tok0 = p.tile_tok0[tile];
+  const int qs = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - qs;
+  const int ctx = p.ctx_len[seq];
+  if (ctx <= 0 || q_len <= 0 || tok0 >= q_len) return;
+  const int G = p.G;
+  const int ntok = min(p.tokens_per_tile, q_len - tok0);
+  const int nrows = ntok * G;
+  const int pos0 = ctx - q_len + tok0;
+  const int pos_last = pos0 + ntok - 1;
+  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int kt_begin = lo / BN, kt_end = pos_last / BN + 1;
+  const int per = (kt_end - kt_begin + p.num_splits - 1) / p.num_splits;
+  const int my_begin = kt_begin + split * per;
+  const int my_end = min(kt_end, my_begin + per);
+  const int* table = p.page_table + (size_t)seq * p.pt_stride;
+
+  // ---- Q tile
+  for (int i = tid; i < BM * CHUNKS; i += THREADS) {
+    const int row = i / CHUNKS, chunk = i % CHUNKS;
+    const bool valid = row < nrows;
+    const bf16* src = p.q;
+    if (valid)
+      src = p.q + (size_t)(qs + tok0 + row / G) * p.q_stride + (size_t)(kvh * G + row % G) * D + chunk * 8;
+    cp_async16(q_s + sw(row, chunk), src, valid);
+  }
+  cp_async_commit();
+
+  auto load_kv = [&](int kt, int buf) {
+    for (int i = tid; i < BN * CHUNKS; i += THREADS) {
+      const int r = i / CHUNKS, chunk = i % CHUNKS;
+      const int b = kt * BN + r;
+      bool valid = b < ctx && b <= pos_last;
+      size_t off = 0;
+      if (valid) {
+        const int page = table[b / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+          if (b >= lo && chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          valid = false;
+        } else {
+          off = (((size_t)page * p.KVH + kvh) * p.page_size + (b % p.page_size)) * D + chunk * 8;
+        }
+      }
+      cp_async16(k_s[buf] + sw(r, chunk), p.k_pool + off, valid);
+      cp_async16(v_s[buf] + sw(r, chunk), p.v_pool + off, valid);
+    }
+    cp_async_commit();
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  const int row0 = warp * 16 + g4, row1 = row0 + 8;
+  const bool warp_active = warp * 16 < nrows;
+  const int pos_r[2] = {pos0 + row0 / G, pos0 + row1 / G};
+  const bool row_ok[2] = {row0 < nrows, row1 < nrows};
+
+  if (my_begin < my_end) load_kv(my_begin, 0);
+  for (int kt = my_begin; kt < my_end; ++kt) {
+    const int buf = (kt - my_begin) & 1;
+    if (kt + 1 < my_end) {
+      load_kv(kt + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (warp_active) {
+      float s[BN / 8][4];
+#pragma unroll
+      for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+      const int m8 = lane >> 3, l8 = lane & 7;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_s + sw(warp * 16 + (m8 & 1) * 8 + l8, kk * 2 + (m8 >> 1)));
+#pragma unroll
+        for (int nn = 0; nn < BN / 16; ++nn) {
+          uint32_t b[4];
+          ldmatrix_x4(b, k_s[buf] + sw(nn * 16 + (m8 >> 1) * 8 + l8, kk * 2 + (m8 & 1)));
+          mma_bf16(s[2 * nn], a, b[0], b[1]);
+          mma_bf16(s[2 * nn + 1], a, b[2], b[3]);
+        }
+      }
+      // mask, scale, online softmax
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int key = kt * BN + nt * 8 + 2 * c4 + (e & 1);
+          const bool vis = row_ok[r] && key <= pos_r[r] && (p.window == 0 || key > pos_r[r] - p.window);
+          const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+          s[nt][e] = v;
+          tmax[r] = fmaxf(tmax[r], v);
+        }
+      float alpha[2], m_safe[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+        const float m_new = fmaxf(m_run[r], tmax[r]);
+        m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(m_run[r] - m_safe[r]);
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(s[nt][e] - m_safe[e >> 1]);
+          s[nt][e] = pv;
+          l_run[e >> 1] += pv;
+        }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= alpha[0];
+        o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1];
+        o[i][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int j = 0; j < BN / 16; ++j) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+        a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+        a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+        a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+        for (int dd = 0; dd < D / 16; ++dd) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, v_s[buf] + sw(j * 16 + (m8 & 1) * 8 + l8, dd * 2 + (m8 >> 1)));
+          mma_bf16(o[2 * dd], a, b[0], b[1]);
+          mma_bf16(o[2 * dd + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (my_begin >= my_end) cp_async_wait<0>();
+
+  // ---- epilogue
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r == 0 ? row0 : row1;
+    if (row >= nrows) continue;
+    const size_t t = (size_t)qs + tok0 + row / G;
+    const int h = kvh * G + row % G;
+    if (p.num_splits == 1) {
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      bf16* dst = p.out + t * p.out_stride + (size_t)h * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * c4) = v;
+      }
+    } else {
+      const size_t idx = (t * p.H + h) * p.num_splits + split;
+      float* dst = p.part_o + idx * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+      if (c4 == 0) {
+        p.part_ml[idx * 2] = m_run[r];
+        p.part_ml[idx * 2 + 1] = l_run[r];
+      }
+    }
+  }
+}
+}  // namespace
+
+// Runs tiles [tile_offset, tile_offset + num_tiles) of the tile list.  With num_splits > 1 the
+// partials go to part_o / part_ml and dsp_attn_combine must follow.
+extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
+    const void* q, long q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int pt_stride, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0,
+    int tile_offset, int num_tiles, void* out, long out_stride, float* part_o, float* part_ml, int H,
+    int KVH, int tokens_per_tile, int page_size, int num_pages, int window, int num_splits,
+    float scale, int* err, cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (KVH <= 0 || H % KVH != 0 || (H / KVH) * tokens_per_tile > BM || tokens_per_tile < 1) return 2;
+  if (num_splits < 1 || num_splits > 65535 || KVH > 65535) return 2;
+  if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return 2;
+  if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) ||
+      ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4))
+    return 3;
+  Params p;
+  p.q = (const bf16*)q;
+  p.q_stride = q_stride;
+  p.k_pool = (const bf16*)k_pool;
+  p.v_pool = (const bf16*)v_pool;
+  p.page_table = page_table;
+  p.pt_stride = pt_stride;
+  p.q_start = q_start;
+  p.ctx_len = ctx_len;
+  p.tile_seq = tile_seq;
+  p.tile_tok0 = tile_tok0;
+  p.out = (bf16*)out;
+  p.out_stride = out_stride;
+  p.part_o = part_o;
+  p.part_ml = part_ml;
+  p.H = H;
+  p.KVH = KVH;
+  p.G = H / KVH;
+  p.tokens_per_tile = tokens_per_tile;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.window = window;
+  p.num_splits = num_splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = err;
+  const int smem = 5 * TILE_BYTES;
+  if (cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return 4;
+  dim3 grid(num_tiles, KVH, num_splits);
+  attn_mma_kernel<<<grid, THREADS, smem, stream>>>(p, tile_offset);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}

@@ -27,7 +27,9 @@ CORE_SOURCES = [
     "runtime.cu",
     "elementwise.cu",
     "gemm_simt.cu",
+    "gemm_skinny.cu",
     "attn_generic.cu",
+    "attn_combine.cu",
     "sampling.cu",
 ]
 

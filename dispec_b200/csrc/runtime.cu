@@ -35,3 +35,8 @@ extern "C" int dsp_device_error() {
 }
 
 extern "C" int dsp_abi_version() { return 1; }
+
+// Device address of the error word, for kernels that live in other libraries.
+extern "C" unsigned long long dsp_device_error_address() {
+  return (unsigned long long)(uintptr_t)dsp_device_error_ptr();
+}

@@ -71,6 +71,7 @@ class StepContext:
         self.states = None
         self.cache_groups = None
         self.page_size = 0
+        self.decode_splits = 0  # fixed number of key splits for single-token rows (0: chosen per step)
         self.graph_capture = False  # host-side choices must not depend on the step's values
         self.scratch: dict = {}
 

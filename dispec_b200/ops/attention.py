@@ -1,6 +1,8 @@
 """Causal grouped-query attention over the paged key/value cache."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from dispec_b200.ops import library as L
@@ -41,9 +43,137 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
     return out
 
 
+_MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
+               3: "operands must be 16-byte aligned with strides in whole 16-byte pieces",
+               4: "shared memory opt-in failed"}
+MAX_SPLITS = 32
+TARGET_CTAS = 148 * 2
+_partials: dict = {}
+_err_addr: dict = {}
+
+
+def tensor_core_supported(head_dim: int, group_size: int, dtype: torch.dtype) -> bool:
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and group_size <= ROWS_PER_TILE)
+
+
+def _partial_buffers(device, rows: int, splits: int, head_dim: int):
+    """Scratch for split attention: unnormalised outputs and (max, sum) per row and split."""
+    key = torch.device(device).index or 0
+    need = rows * splits * (head_dim + 2)
+    buf = _partials.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device)
+        _partials[key] = buf
+    n_o = rows * splits * head_dim
+    return buf[:n_o], buf[n_o:n_o + rows * splits * 2]
+
+
+def reserve_partials(device, rows: int, splits: int, head_dim: int) -> None:
+    """Sizes the scratch ahead of time (before a CUDA graph is captured)."""
+    _partial_buffers(device, rows, splits, head_dim)
+
+
+def _device_error_address(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _err_addr:
+        fn = L.core().dsp_device_error_address
+        fn.restype = ctypes.c_ulonglong
+        _err_addr[key] = int(fn())
+    return _err_addr[key]
+
+
+def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int) -> int:
+    """Key splits for single-token rows, so that the launch covers the SMs about twice."""
+    if num_decode_tiles <= 0:
+        return 1
+    want = -(-TARGET_CTAS // (num_decode_tiles * num_kv_heads))
+    return max(1, min(want, MAX_SPLITS, -(-max_ctx // 256)))
+
+
+def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
+                tile_offset, num_tiles, out, part_o, part_ml, H, KVH, D, tpt, window, splits, scale):
+    num_pages, _, page_size, _ = k_pool.shape
+    lib = L.attention_library(D)
+    fn = getattr(lib, f"dsp_attn_mma_d{D}")
+    rc = fn(L.ptr(q), L.i64(q_stride), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table),
+            page_table.stride(0), L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0),
+            tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml),
+            H, KVH, tpt, page_size, num_pages, window, splits, L.f32(scale),
+            ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
+    if rc != 0:
+        raise L.KernelError(f"dsp_attn_mma_d{D}: {_MMA_ERRORS.get(rc, rc)}")
+
+
+def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
+                          tile_tok0, num_tiles, num_decode_tiles, out, H, KVH, D, window, scale,
+                          splits: int) -> torch.Tensor:
+    """Tensor-core attention over a tile list whose first ``num_decode_tiles`` tiles are single
+    tokens (run with ``splits`` key splits and merged), the rest portions of prompts."""
+    assert q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
+    tpt = tokens_per_tile(H // KVH)
+    if num_decode_tiles > 0:
+        if splits > 1:
+            rows = num_decode_tiles * H  # decode tokens are the first rows of the flat batch
+            part_o, part_ml = _partial_buffers(q.device, rows, splits, D)
+            _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
+                        tile_tok0, 0, num_decode_tiles, out, part_o, part_ml, H, KVH, D, tpt, window,
+                        splits, scale)
+            L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out),
+                                              L.i64(out.stride(0)), num_decode_tiles, H, D, splits,
+                                              L.dtype_code(out.dtype), L.stream_handle()))
+        else:
+            _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
+                        tile_tok0, 0, num_decode_tiles, out, None, None, H, KVH, D, tpt, window, 1, scale)
+    if num_tiles > num_decode_tiles:
+        _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
+                    num_decode_tiles, num_tiles - num_decode_tiles, out, None, None, H, KVH, D, tpt,
+                    window, 1, scale)
+    return out
+
+
+def paged_attention_tensor_core(q, q_stride, k_pool, v_pool, page_table, positions, seq_of_token, out,
+                                num_heads, num_kv_heads, head_dim, window, scale, q_lens, ctx_lens,
+                                splits=None) -> torch.Tensor:
+    """Stand-alone form (tests, tools): builds the tile list for sequences given by their
+    ``q_lens`` and ``ctx_lens`` (single-token sequences must come first)."""
+    dev_ = q.device
+    tpt = tokens_per_tile(num_heads // num_kv_heads)
+    ts, t0 = [], []
+    n_dec = 0
+    for s, n in enumerate(q_lens):
+        if n == 1 and n_dec == s:
+            n_dec += 1
+        for a in range(0, n, tpt):
+            ts.append(s)
+            t0.append(a)
+    starts = [0]
+    for n in q_lens:
+        starts.append(starts[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev_)
+    if splits is None:
+        splits = choose_splits(n_dec, num_kv_heads, max(ctx_lens))
+    return paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, i32(starts), i32(ctx_lens),
+                                 i32(ts), i32(t0), len(ts), n_dec, out, num_heads, num_kv_heads,
+                                 head_dim, window, scale, splits)
+
+
 def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tensor, num_heads: int,
                     num_kv_heads: int, head_dim: int, window: int, scale: float) -> torch.Tensor:
-    """Attention of the step described by ``ctx`` over the layer cache ``cache``."""
+    """Attention of the step described by ``ctx`` over the layer cache ``cache``: the
+    tensor-core kernel for bfloat16 where it is built for the sizes, the 32-bit kernel
+    otherwise (and always on the float32 path)."""
+    group = num_heads // num_kv_heads
+    tpt = tokens_per_tile(group)
+    if tensor_core_supported(head_dim, group, q.dtype) and tpt in ctx.attention_tiles:
+        tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
+        splits = ctx.decode_splits if ctx.decode_splits else choose_splits(
+            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len)
+        return paged_attention_tiles(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
+                                     ctx.q_start, ctx.ctx_len, tile_seq, tile_tok0, num_tiles,
+                                     ctx.num_decode_seqs, out, num_heads, num_kv_heads, head_dim,
+                                     window, scale, splits)
     return paged_attention_generic(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads,
                                    head_dim, window, scale)

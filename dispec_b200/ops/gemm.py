@@ -14,7 +14,11 @@ import torch
 
 from dispec_b200.ops import library as L
 
-SKINNY_MAX_ROWS = 0  # rows the weight-streaming kernel takes (0: kernel not built in)
+SKINNY_MAX_ROWS = 64  # rows the weight-streaming kernel takes
+SKINNY_TARGET_CTAS = 148 * 4  # CTAs a weight-streaming launch aims for (split-K fills the SMs)
+_WORKSPACE_FLOATS = 8 << 20  # 32 MB of split-K partials
+_NUM_COUNTERS = 4096
+_workspaces: dict = {}
 LARGE_BACKEND = "library"  # "library" | "simt"
 
 
@@ -28,13 +32,26 @@ def _simt(x, w, bias, residual, out):
     return out
 
 
-def _skinny(x, w, bias, residual, out):
+def workspace(device):
+    """Scratch for split-K partials and the per-block arrival counters (zero between calls),
+    one pair per device.  Launches that overlap on the device must not share it; the engine
+    runs on one stream."""
+    key = torch.device(device).index or 0
+    if key not in _workspaces:
+        _workspaces[key] = (torch.empty(_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+                            torch.zeros(_NUM_COUNTERS, dtype=torch.int32, device=device))
+    return _workspaces[key]
+
+
+def _skinny(x, w, bias, residual, out, target_ctas=None):
     M, K = x.shape
     N = w.shape[0]
+    scratch, counters = workspace(x.device)
     L.check(L.core().dsp_gemm_skinny(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
-        M, N, K, L.dtype_code(out.dtype), L.stream_handle()))
+        M, N, K, L.dtype_code(out.dtype), SKINNY_TARGET_CTAS if target_ctas is None else target_ctas,
+        L.ptr(scratch), L.i64(scratch.numel()), L.ptr(counters), counters.numel(), L.stream_handle()))
     return out
 
 

@@ -303,3 +303,94 @@ def test_sampling_keeps_ties_at_the_kth_value():
                          torch.tensor([1.0], device=dev()), torch.tensor([u], device=dev()))
         seen.add(int(got[0]))
     assert seen == {3, 9, 40}
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 100, 96), (3, 130, 224), (8, 2048, 1536), (9, 1536, 8960),
+                                   (16, 257, 40), (31, 384, 96), (64, 1000, 776), (1, 5000, 1536)])
+def test_gemm_weight_streaming(out_dtype, M, N, K):
+    from dispec_b200.ops import gemm
+    x = rnd((M, K), torch.bfloat16, 21)
+    w = rnd((N, K), torch.bfloat16, 22, 0.1)
+    b = rnd((N,), torch.bfloat16, 23)
+    r = rnd((M, N), out_dtype, 24)
+    ref = x.double() @ w.double().T + b.double() + r.double()
+    for target in (1, 148 * 4):  # without and with split-K
+        out = gemm._skinny(x, w, b, r, torch.empty((M, N), dtype=out_dtype, device=dev()), target)
+        torch.testing.assert_close(out.double(), ref, **tol(out_dtype if out_dtype == torch.bfloat16 else torch.bfloat16))
+    plain_out = gemm._skinny(x, w, None, None, torch.empty((M, N), dtype=torch.float32, device=dev()))
+    torch.testing.assert_close(plain_out.double(), x.double() @ w.double().T, atol=2e-3, rtol=2e-3)
+
+
+def test_gemm_weight_streaming_is_deterministic_and_strided():
+    from dispec_b200.ops import gemm
+    big = rnd((8, 3 * 1536), torch.bfloat16, 25)
+    x = big[:, 1536:2 * 1536]  # a strided view
+    w = rnd((1536, 1536), torch.bfloat16, 26, 0.05)
+    a = gemm.linear(x, w)
+    for _ in range(3):
+        assert torch.equal(a, gemm.linear(x, w))
+    torch.testing.assert_close(a.double(), x.double() @ w.double().T, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("case", ATTN_CASES + [(28, 4, 128, 16, 1200, 1, 0), (5, 5, 80, 16, 130, 64, 0),
+                                               (8, 1, 256, 16, 100, 9, 0), (12, 2, 128, 16, 700, 300, 0)])
+def test_attention_tensor_core(case):
+    out, ref = run_attention("tensor_core", torch.bfloat16, *case)
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("plant", [0, 15, 16, 63, 64, 65, 255, 256, 511, 600])
+@pytest.mark.parametrize("q_len", [1, 37])
+def test_attention_tensor_core_far_key_stands_out(plant, q_len):
+    out, ref = run_attention("tensor_core", torch.bfloat16, 12, 2, 64, 16, 700, q_len, 0, plant=plant,
+                             seed=plant)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("offset", [-1, 0, 1])
+@pytest.mark.parametrize("q_len", [1, 20])
+def test_attention_tensor_core_window_edge(offset, q_len):
+    ctx, window = 333, 100
+    plant = ctx - 1 - window + 1 + offset
+    out, ref = run_attention("tensor_core", torch.bfloat16, 6, 2, 32, 8, ctx, q_len, window, plant=plant,
+                             seed=9)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+def test_attention_tensor_core_mixed_batch_matches_alone():
+    """Single tokens (with key splits) beside a portion of a prompt, ragged lengths."""
+    from dispec_b200.ops import attention as A
+    H, KVH, D, page = 6, 2, 64, 16
+    q_lens = [1, 1, 1, 23, 70]
+    ctx_lens = [17, 300, 64, 23, 200]
+    g = torch.Generator().manual_seed(11)
+    num_pages = sum((c + page - 1) // page for c in ctx_lens) + 2
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=torch.bfloat16)
+    vp = kp.clone()
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    maxp = max((c + page - 1) // page for c in ctx_lens)
+    table = torch.full((len(q_lens), maxp), -1, dtype=torch.int32)
+    qs, refs, positions, seqs = [], [], [], []
+    for s, (ql, cl) in enumerate(zip(q_lens, ctx_lens)):
+        k = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
+        v = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
+        q = torch.randn(ql, H, D, generator=g).bfloat16().float()
+        for j in range((cl + page - 1) // page):
+            table[s, j] = perm.pop()
+        for b in range(cl):
+            kp[table[s, b // page], :, b % page] = k[b].bfloat16()
+            vp[table[s, b // page], :, b % page] = v[b].bfloat16()
+        pos = torch.arange(cl - ql, cl, dtype=torch.int32)
+        refs.append(_attention_reference(q.double(), k.double(), v.double(), pos, 0, D ** -0.5))
+        qs.append(q)
+        positions.append(pos)
+        seqs += [s] * ql
+    qd = torch.cat(qs).bfloat16().reshape(-1, H * D).to(dev())
+    out = torch.empty_like(qd)
+    A.paged_attention_tensor_core(qd, H * D, kp.to(dev()), vp.to(dev()), table.to(dev()),
+                                  torch.cat(positions).to(dev()),
+                                  torch.tensor(seqs, dtype=torch.int32, device=dev()), out, H, KVH, D, 0,
+                                  D ** -0.5, q_lens=q_lens, ctx_lens=ctx_lens, splits=4)
+    got = out.float().cpu().view(-1, H, D).double()
+    torch.testing.assert_close(got, torch.cat(refs), atol=2e-2, rtol=2e-2)
