@@ -21,7 +21,7 @@ from dispec_b200.models.model import DecoderModel
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages=4096,
-                 max_num_seqs: int = 256, poison: bool = False):
+                 max_num_seqs: int = 256, poison: bool = False, cuda_graph: bool = False):
         if model.device is None:
             raise ValueError("the model has no weights yet (load it first)")
         self.model = model
@@ -37,6 +37,7 @@ class ModelRunner:
         self.poison = poison  # tests: pages given back are filled with NaN
         self.vocab_size = model.spec.vocab_size
         self.num_steps = 0
+        self.cuda_graph = bool(cuda_graph) and self.dtype == torch.bfloat16
 
     # ---------------------------------------------------------------- request lifecycle
     def admit(self, req_id, prompt_len: int = 0, max_total_len: int = 0, max_chunk: int = 1) -> None:

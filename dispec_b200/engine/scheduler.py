@@ -1,0 +1,298 @@
+"""Continuous batching: admits requests, cuts prompts into portions under a token budget,
+decodes, finishes and frees.
+
+Structure, names and defaults follow puneethgv/DiSpec dispec/sched/scheduler.py: states
+(:28-32), ``Request`` (:35-57), per step first one token for every running request, then
+prompts in progress, then waiting requests by (-priority, id) (:132-197), admission that
+stops at the first request that does not fit (:159-164), a portion that does not finish the
+prompt yields no token (:189-197), the end-of-sequence token is kept in the output (:222-232).
+
+Decided here, where the reference raises out of ``step()`` (its ``append_token`` at :137
+lets OutOfBlocksError through): when a running request cannot get a page, the newest live
+request is preempted by recomputation: its pages are given back, it returns to the head of the
+waiting queue with prompt + emitted tokens as its new prompt, and it keeps what it emitted.
+A request that could never fit the pool alone is refused in ``add_request``.  Sampling uses
+each request's own parameters and generator.
+
+``Scheduler`` is pure bookkeeping over a ``CacheManager`` (testable without a GPU);
+``ContinuousBatchingEngine`` joins it with the step function and the sampler.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from enum import Enum, auto
+
+from dispec_b200.cache.manager import CacheManager
+from dispec_b200.cache.pages import OutOfPagesError
+from dispec_b200.config.engine_config import KVConfig
+from dispec_b200.engine.batch import SeqEntry
+from dispec_b200.sampling.sampler import SamplingParams, make_rng
+
+
+class State(Enum):
+    WAITING = auto()
+    PREFILLING = auto()
+    RUNNING = auto()
+    FINISHED = auto()
+
+
+@dataclass
+class Request:
+    id: int
+    prompt_ids: list
+    params: SamplingParams
+    max_new_tokens: int
+    eos_id: int | None = None
+    output_ids: list = field(default_factory=list)
+    state: State = State.WAITING
+    priority: int = 0  # higher is admitted sooner
+    prefill_pos: int = 0  # tokens of the current prompt already stored
+    prefilled: bool = False
+    num_preemptions: int = 0
+    finish_reason: str | None = None
+    rng: object = None
+    _recompute: list | None = None  # prompt + emitted tokens after a preemption
+
+    @property
+    def feed(self) -> list:
+        """Tokens that must be stored before the next token can be sampled."""
+        return self._recompute if self._recompute is not None else self.prompt_ids
+
+    @property
+    def done(self) -> bool:
+        if len(self.output_ids) >= self.max_new_tokens:
+            return True
+        return bool(self.output_ids) and self.eos_id is not None and self.output_ids[-1] == self.eos_id
+
+
+@dataclass
+class StepPlan:
+    entries: list  # SeqEntry, single-token entries first
+    sampled: list  # requests that get a token this step, in the order of the logits rows
+    num_decode_tokens: int = 0
+    num_prefill_tokens: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_batch_tokens: int = 2048, chunk_size: int | None = None,
+                 max_model_len: int | None = None, on_admit=None, on_free=None):
+        self.cache = cache
+        self.max_batch_tokens = max_batch_tokens
+        self.chunk_size = chunk_size or max_batch_tokens
+        self.max_model_len = max_model_len
+        self.waiting: list[Request] = []
+        self.prefilling: list[Request] = []
+        self.running: list[Request] = []
+        self.finished: list[Request] = []
+        self._ids = itertools.count()
+        self._on_admit = on_admit or (lambda req_id, *a: cache.admit(req_id, *a))
+        self._on_free = on_free or cache.free
+        self.num_steps = 0
+        self.num_prefill_tokens = 0
+        self.num_decode_tokens = 0
+        self.num_preemptions = 0
+
+    # -------------------------------------------------------------------------- requests
+    def add_request(self, prompt_ids, max_new_tokens: int, params: SamplingParams | None = None,
+                    eos_id: int | None = None, priority: int = 0) -> int:
+        prompt = list(prompt_ids)
+        if not prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be at least 1")
+        total = len(prompt) + max_new_tokens
+        # the last emitted token is never stored, hence total - 1 positions
+        if total - 1 > self.cache.capacity_tokens():
+            raise ValueError(f"request of {len(prompt)} + {max_new_tokens} tokens can never fit the "
+                             f"cache pool of {self.cache.capacity_tokens()} tokens")
+        if self.max_model_len is not None and total - 1 > self.max_model_len:
+            raise ValueError(f"request of {len(prompt)} + {max_new_tokens} tokens exceeds the longest "
+                             f"sequence the engine serves ({self.max_model_len})")
+        params = params or SamplingParams()
+        req = Request(next(self._ids), prompt, params, max_new_tokens, eos_id, priority=priority,
+                      rng=make_rng(params))
+        self.waiting.append(req)
+        return req.id
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.prefilling or self.running)
+
+    def collect_outputs(self) -> dict:
+        return {r.id: r.output_ids for r in self.finished + self.running}
+
+    # ------------------------------------------------------------------------ preemption
+    def _preempt(self, req: Request) -> None:
+        self._on_free(req.id)
+        if req in self.running:
+            self.running.remove(req)
+        if req in self.prefilling:
+            self.prefilling.remove(req)
+        req.state = State.WAITING
+        req.prefill_pos = 0
+        req.prefilled = False
+        req._recompute = list(req.prompt_ids) + list(req.output_ids)
+        req.num_preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.append(req)
+
+    def _newest_live(self) -> Request | None:
+        live = self.running + self.prefilling
+        if not live:
+            return None
+        return max(live, key=lambda r: (-r.priority, r.id))
+
+    # ------------------------------------------------------------------------- one step
+    def schedule(self) -> StepPlan:
+        budget = self.max_batch_tokens
+        entries: dict[int, SeqEntry] = {}
+        sampled: list[Request] = []
+        n_dec = n_pre = 0
+
+        # 1) one token for every running request, oldest first
+        for req in sorted(self.running, key=lambda r: r.id):
+            if budget < 1:
+                break
+            if req.state != State.RUNNING:
+                continue  # preempted a moment ago
+            stored = self.cache.num_tokens(req.id)
+            placed = True
+            while not self.cache.can_extend(req.id, stored + 1):
+                victim = self._newest_live()
+                if victim is None or victim is req:
+                    # the request itself is the newest: it waits, the older ones go on
+                    if victim is req:
+                        self._preempt(req)
+                    placed = False
+                    break
+                if victim.id in entries:
+                    gone = entries.pop(victim.id)
+                    budget += len(gone.tokens)
+                    n_dec -= 1
+                    sampled.remove(victim)
+                self._preempt(victim)
+            if not placed:
+                continue
+            self.cache.extend(req.id, stored + 1)
+            entries[req.id] = SeqEntry(req.id, [req.output_ids[-1]], stored, [0])
+            sampled.append(req)
+            budget -= 1
+            n_dec += 1
+
+        # 2) prompts in progress, then waiting requests by priority and age
+        self.waiting.sort(key=lambda r: (-r.priority, r.id))
+        for req in self.prefilling + self.waiting:
+            if budget < 1:
+                break
+            feed = req.feed
+            if req.state == State.WAITING:
+                remaining_new = req.max_new_tokens - len(req.output_ids)
+                args = (len(feed), len(feed) + remaining_new, min(self.chunk_size, self.max_batch_tokens))
+                if not self.cache.can_admit(*args):
+                    break
+                self._on_admit(req.id, *args)
+                req.state = State.PREFILLING
+                self.waiting.remove(req)
+                self.prefilling.append(req)
+            chunk = min(len(feed) - req.prefill_pos, self.chunk_size, budget)
+            try:
+                self.cache.extend(req.id, req.prefill_pos + chunk)
+            except OutOfPagesError:
+                break
+            finishes = req.prefill_pos + chunk >= len(feed)
+            entries[req.id] = SeqEntry(req.id, feed[req.prefill_pos:req.prefill_pos + chunk],
+                                       req.prefill_pos, [chunk - 1] if finishes else [])
+            req.prefill_pos += chunk
+            budget -= chunk
+            n_pre += chunk
+            if finishes:
+                sampled.append(req)
+                req.prefilled = True
+                req.state = State.RUNNING
+                self.prefilling.remove(req)
+                self.running.append(req)
+
+        ordered = [e for e in entries.values() if len(e.tokens) == 1] + \
+                  [e for e in entries.values() if len(e.tokens) != 1]
+        order = {e.req_id: i for i, e in enumerate(ordered)}
+        want_rows = [r for r in sampled]
+        # logits rows follow the order of the entries
+        want_rows.sort(key=lambda r: order[r.id])
+        self.num_decode_tokens += n_dec
+        self.num_prefill_tokens += n_pre
+        return StepPlan(ordered, want_rows, n_dec, n_pre)
+
+    def process(self, plan: StepPlan, token_ids: list) -> list[Request]:
+        """Appends the sampled tokens, retires finished requests; returns those retired."""
+        self.num_steps += 1
+        done = []
+        for req, tid in zip(plan.sampled, token_ids):
+            req.output_ids.append(int(tid))
+            if req.done:
+                req.finish_reason = ("stop" if req.eos_id is not None and req.output_ids[-1] == req.eos_id
+                                     else "length")
+                req.state = State.FINISHED
+                done.append(req)
+        for req in done:
+            self.running.remove(req)
+            self.finished.append(req)
+            self._on_free(req.id)
+        return done
+
+
+class ContinuousBatchingEngine:
+    """``ContinuousBatchingEngine(model, kv, num_blocks, max_batch_tokens, chunk_size)`` with
+    ``add_request / step / has_work / run_until_done / collect_outputs`` as in the reference
+    (dispec/sched/scheduler.py:60-63,85-101,234-244).  ``model`` is a model loaded by
+    ``dispec_b200.load_model``; the reference's ``attn_backend`` and ``fuse`` switches have no
+    counterpart (there is one attention path, projections are always fused)."""
+
+    def __init__(self, model, kv: KVConfig | None = None, num_blocks: int = 2048,
+                 max_batch_tokens: int = 2048, chunk_size: int | None = None, max_num_seqs: int = 256,
+                 cuda_graph: bool = True, poison: bool = False):
+        from dispec_b200.engine.runner import ModelRunner
+        from dispec_b200.sampling.sampler import Sampler
+
+        kv = kv or KVConfig()
+        self.block_size = kv.block_size
+        self.runner = ModelRunner(model, page_size=kv.block_size, num_pages=num_blocks,
+                                  max_num_seqs=max_num_seqs, poison=poison, cuda_graph=cuda_graph)
+        self.sampler = Sampler(model.device)
+        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens, chunk_size,
+                                   max_model_len=model.spec.max_position or None,
+                                   on_admit=self.runner.admit, on_free=self.runner.release)
+
+    # queues and counters under the reference's names
+    waiting = property(lambda self: self.scheduler.waiting)
+    prefilling = property(lambda self: self.scheduler.prefilling)
+    running = property(lambda self: self.scheduler.running)
+    finished = property(lambda self: self.scheduler.finished)
+    num_steps = property(lambda self: self.scheduler.num_steps)
+    num_prefill_tokens = property(lambda self: self.scheduler.num_prefill_tokens)
+    num_decode_tokens = property(lambda self: self.scheduler.num_decode_tokens)
+    num_preemptions = property(lambda self: self.scheduler.num_preemptions)
+
+    def add_request(self, prompt_ids, max_new_tokens: int, params: SamplingParams | None = None,
+                    eos_id: int | None = None, priority: int = 0) -> int:
+        return self.scheduler.add_request(prompt_ids, max_new_tokens, params, eos_id, priority)
+
+    def step(self) -> None:
+        plan = self.scheduler.schedule()
+        if not plan.entries:
+            return
+        logits = self.runner.step(plan.entries)
+        tokens = self.sampler.sample(logits, [r.params for r in plan.sampled],
+                                     [r.rng for r in plan.sampled])
+        self.scheduler.process(plan, tokens)
+
+    def collect_outputs(self) -> dict:
+        return self.scheduler.collect_outputs()
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def run_until_done(self, max_steps: int = 100_000) -> None:
+        steps = 0
+        while self.has_work() and steps < max_steps:
+            self.step()
+            steps += 1

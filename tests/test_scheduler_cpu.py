@@ -1,0 +1,205 @@
+"""The scheduler's decisions, driven by a fake step function on the CPU: order within a step,
+token budget, portions, admission, priority, finishing, and what happens when pages run out
+(preemption by recomputation)."""
+import pytest
+
+from dispec_b200.cache import CacheGroupSpec, CacheManager
+from dispec_b200.engine.scheduler import Scheduler, State
+from dispec_b200.sampling import SamplingParams
+
+VOCAB = 97
+
+
+def make(pages=64, page_size=4, budget=2048, chunk=None, slots=16, groups=None):
+    cache = CacheManager(groups or [CacheGroupSpec(1, 8)], page_size, pages, slots)
+    return Scheduler(cache, max_batch_tokens=budget, chunk_size=chunk), cache
+
+
+class FakeModel:
+    """Next token = a hash of everything the request has stored so far: any token lost,
+    repeated or fed at the wrong place changes the output."""
+
+    def __init__(self):
+        self.stored = {}
+
+    def step(self, plan, cache):
+        out = {}
+        for e in plan.entries:
+            seq = self.stored.setdefault(e.req_id, [])
+            assert e.start == len(seq), "tokens fed at the wrong position"
+            seq.extend(e.tokens)
+            cache.commit(e.req_id, len(seq))
+            if e.want:
+                h = 7
+                for i, t in enumerate(seq):
+                    h = (h * 31 + t * (i + 1)) % 1000003
+                out[e.req_id] = h % VOCAB
+        return [out[r.id] for r in plan.sampled]
+
+    def forget(self, req_id):
+        self.stored.pop(req_id, None)
+
+
+def run(sched, cache, model, max_steps=10000):
+    steps = 0
+    while sched.has_work() and steps < max_steps:
+        plan = sched.schedule()
+        cache.check()
+        assert plan.entries, "a step with work scheduled nothing"
+        tokens = model.step(plan, cache)
+        for r in sched.process(plan, tokens):
+            model.forget(r.id)
+        steps += 1
+    assert not sched.has_work()
+    return steps
+
+
+def wire(sched, cache, model):
+    """Route frees through the fake model so that a preempted request starts over."""
+    def on_free(rid):
+        model.forget(rid)
+        return cache.free(rid)
+    sched._on_free = on_free
+
+
+def expected(prompt, n, eos=None):
+    m = FakeModel()
+    seq = list(prompt)
+    out = []
+    while len(out) < n:
+        h = 7
+        for i, t in enumerate(seq):
+            h = (h * 31 + t * (i + 1)) % 1000003
+        out.append(h % VOCAB)
+        seq.append(out[-1])
+        if eos is not None and out[-1] == eos:
+            break
+    return out
+
+
+def test_decodes_first_then_prompts_and_only_a_finished_prompt_yields_a_token():
+    sched, cache = make(chunk=8)
+    model = FakeModel()
+    a = sched.add_request(list(range(5)), 4)
+    plan = sched.schedule()
+    assert [(e.req_id, len(e.tokens), e.want) for e in plan.entries] == [(a, 5, [4])]
+    sched.process(plan, model.step(plan, cache))
+    b = sched.add_request(list(range(20)), 3)
+    plan = sched.schedule()  # a decodes, b's first portion of 8 yields nothing
+    assert [(e.req_id, len(e.tokens), e.want) for e in plan.entries] == [(a, 1, [0]), (b, 8, [])]
+    assert [r.id for r in plan.sampled] == [a]
+    assert sched.prefilling[0].id == b and sched.prefilling[0].state == State.PREFILLING
+    sched.process(plan, model.step(plan, cache))
+    plan = sched.schedule()
+    assert [(e.req_id, e.start, len(e.tokens)) for e in plan.entries] == [(a, 6, 1), (b, 8, 8)]
+    sched.process(plan, model.step(plan, cache))
+    plan = sched.schedule()  # last portion of b: 4 tokens, now it samples
+    assert [(e.req_id, e.start, len(e.tokens), e.want) for e in plan.entries] == [(a, 7, 1, [0]), (b, 16, 4, [3])]
+    assert [r.id for r in plan.sampled] == [a, b]
+    sched.process(plan, model.step(plan, cache))
+    assert sched.finished[0].id == a and sched.finished[0].output_ids == expected(range(5), 4)
+    run(sched, cache, model)
+    assert sched.collect_outputs()[b] == expected(range(20), 3)
+    assert sched.num_prefill_tokens == 25 and sched.num_decode_tokens == 3 + 2
+    assert cache.num_free_pages() == 64
+
+
+def test_token_budget_bounds_a_step_and_skipped_decodes_catch_up():
+    sched, cache = make(budget=2)
+    model = FakeModel()
+    wire(sched, cache, model)
+    ids = [sched.add_request([i, i + 1], 5) for i in range(3)]
+    seen = []
+    while sched.has_work():
+        plan = sched.schedule()
+        seen.append(sum(len(e.tokens) for e in plan.entries))
+        sched.process(plan, model.step(plan, cache))
+    assert max(seen) <= 2
+    for i, rid in enumerate(ids):
+        assert sched.collect_outputs()[rid] == expected([i, i + 1], 5)
+
+
+def test_priority_then_age_and_head_of_line_admission():
+    sched, cache = make(pages=6, page_size=4, slots=8)  # 24 tokens of cache
+    model = FakeModel()
+    wire(sched, cache, model)
+    low = sched.add_request(list(range(14)), 2, priority=0)  # 4 pages, room for its 2 tokens
+    high = sched.add_request(list(range(6)), 2, priority=5)  # 2 pages, room for its 2 tokens
+    tail = sched.add_request([1], 2, priority=0)  # would fit, but waits behind `low`
+    plan = sched.schedule()
+    assert [e.req_id for e in plan.entries] == [high, low]
+    sched.process(plan, model.step(plan, cache))
+    late = sched.add_request(list(range(12)), 2, priority=9)  # 3 pages: does not fit yet
+    plan = sched.schedule()
+    assert sorted(e.req_id for e in plan.entries) == [low, high]  # `late` blocks `tail` too
+    assert [r.id for r in sched.waiting] == [late, tail]
+    sched.process(plan, model.step(plan, cache))
+    run(sched, cache, model)
+    assert sched.collect_outputs()[tail] == expected([1], 2)
+    assert sched.collect_outputs()[late] == expected(range(12), 2)
+
+
+def test_end_of_sequence_token_is_kept_and_stops_the_request():
+    sched, cache = make()
+    model = FakeModel()
+    want = expected([3, 4, 5], 50)
+    eos = want[6]
+    first = want.index(eos)
+    rid = sched.add_request([3, 4, 5], 50, eos_id=eos)
+    run(sched, cache, model)
+    out = sched.collect_outputs()[rid]
+    assert out == want[:first + 1] and sched.finished[0].finish_reason == "stop"
+
+
+def test_running_out_of_pages_preempts_the_newest_and_recomputes():
+    # 3 pages of 16 tokens, two 16-token prompts, 24 new tokens each: the reference raises out
+    # of step() here (dispec/sched/scheduler.py:137 lets OutOfBlocksError through)
+    sched, cache = make(pages=3, page_size=16)
+    model = FakeModel()
+    wire(sched, cache, model)
+    a = sched.add_request(list(range(16)), 24)
+    b = sched.add_request(list(range(100, 116)), 24)
+    steps = run(sched, cache, model)
+    out = sched.collect_outputs()
+    assert out[a] == expected(range(16), 24)
+    assert out[b] == expected(range(100, 116), 24)
+    assert sched.num_preemptions >= 1 and steps < 200
+    by_id = {r.id: r for r in sched.finished}
+    assert by_id[b].num_preemptions >= 1 and by_id[a].num_preemptions == 0  # the older one goes on
+    cache.check()
+    assert cache.num_free_pages() == 3 and cache.free_slots() == 16
+
+
+def test_many_requests_through_a_small_pool_all_finish_with_the_right_tokens():
+    sched, cache = make(pages=10, page_size=4, budget=24, chunk=8, slots=6)
+    model = FakeModel()
+    wire(sched, cache, model)
+    specs = [([i * 3 + j for j in range(1 + (i * 7) % 19)], 3 + (i * 5) % 11) for i in range(14)]
+    ids = [sched.add_request(p, n, SamplingParams()) for p, n in specs]
+    run(sched, cache, model)
+    out = sched.collect_outputs()
+    for rid, (p, n) in zip(ids, specs):
+        assert out[rid] == expected(p, n), rid
+    cache.check()
+    assert cache.num_free_pages() == 10
+
+
+def test_window_group_requests_finish_under_their_promise():
+    groups = [CacheGroupSpec(1, 8), CacheGroupSpec(1, 8, window=6)]
+    sched, cache = make(pages=[40, 8], page_size=4, budget=16, chunk=8, slots=4, groups=groups)
+    model = FakeModel()
+    wire(sched, cache, model)
+    ids = [sched.add_request(list(range(i, i + 30)), 20) for i in range(3)]
+    run(sched, cache, model)
+    for i, rid in enumerate(ids):
+        assert sched.collect_outputs()[rid] == expected(range(i, i + 30), 20)
+    assert cache.num_free_pages(1) == 8 and cache.pools[1].reserved == 0
+
+
+def test_a_request_that_can_never_fit_is_refused():
+    sched, _ = make(pages=2, page_size=4)
+    with pytest.raises(ValueError, match="never fit"):
+        sched.add_request(list(range(8)), 2)
+    sched.add_request(list(range(8)), 1)  # 8 stored positions fit exactly
+    with pytest.raises(ValueError):
+        sched.add_request([], 2)
