@@ -64,6 +64,8 @@ class StepContext:
         self.logit_rows = None  # [n] int32
         self.page_tables: list = []  # per cache group [S, max_pages] int32
         self.host_q_len: list = []
+        self.host_q_start: list = []
+        self.host_state_slot: list = []
         self.host_ctx_len: list = []
         self.max_ctx_len = 0
         self.attention_tiles: dict = {}  # tokens per tile -> (tile_seq, tile_tok0, n_tiles) device int32
@@ -243,6 +245,8 @@ def build_context(entries: list, cache, storage, states, staging: HostStaging, d
     ctx.logit_rows = dview("logit_rows")
     ctx.page_tables = [dview(f"page_table{g}").view(S, pages_per_group[g]) for g in range(ng)]
     ctx.host_q_len, ctx.host_ctx_len = q_lens, ctx_lens
+    ctx.host_q_start = [int(v) for v in q_start]
+    ctx.host_state_slot = [cache.state_slot(e.req_id) for e in sorted_entries]
     ctx.max_ctx_len = max(ctx_lens) if ctx_lens else 0
     for tpt in tile_tokens:
         ctx.attention_tiles[tpt] = (dview(f"tile_seq{tpt}"), dview(f"tile_tok0{tpt}"), tiles[tpt])

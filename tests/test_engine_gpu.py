@@ -1,0 +1,176 @@
+"""Generation through the Python entry points against the plain implementation: greedy and
+temperature sampling, chunked prompts mixed with decoding, long decoding, the first tokens of
+a sequence, and a pool so small that requests are preempted and recomputed."""
+import random
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name in ("a", "b", "c"):
+        d = str(tmp_path_factory.mktemp(f"model_{name}"))
+        out[name] = (d,) + ru.make_model_folder(d, name, dtype="bfloat16")
+    return out
+
+
+def load(folder, dtype):
+    from dispec_b200 import load_model
+    return load_model(folder, dtype, "cuda:0")
+
+
+def replay_sampling(weights, config, prompt, tokens, params):
+    """What the plain implementation would have drawn, teacher-forced with the engine's own
+    tokens, from the same stream of uniform numbers.  Returns (tokens, smallest margin)."""
+    rng = random.Random(params.seed)
+    out, margin = [], 1.0
+    ids = list(prompt)
+    for tok in tokens:
+        logits = plain.forward_logits(weights, config, ids)[-1]
+        if params.temperature <= 0:
+            top2 = torch.topk(logits, 2).values
+            margin = min(margin, float(top2[0] - top2[1]))
+            out.append(int(logits.argmax()))
+        else:
+            u = min(rng.random(), 1.0 - 2.0 ** -24)
+            probs = plain.sampling_distribution(logits, params.temperature, params.top_k, params.top_p)
+            cdf = probs.cumsum(-1)
+            want = plain.draw_inverse_cdf(probs, u)
+            margin = min(margin, float((cdf - u * cdf[-1]).abs().min()))
+            out.append(want)
+        ids.append(tok)
+    return out, margin
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_greedy_generation_through_llm_engine(folders, name, dtype):
+    from dispec_b200 import LLMEngine, SamplingParams
+    folder, config, weights = folders[name]
+    engine = LLMEngine(load(folder, dtype), num_blocks=64)
+    for n in ([5, 17, 33] if name == "a" else [1, 9, 40]):
+        prompt = ru.random_ids(n, config["vocab_size"], 300 + n)
+        got = engine.generate(prompt, 8, SamplingParams(temperature=0.0))
+        want, margin = replay_sampling(weights, config, prompt, got, SamplingParams())
+        if dtype == "float32":
+            assert margin > 1e-4 and got == want
+        else:
+            scale = 0.03 * plain.forward_logits(weights, config, prompt).abs().max().item() + 0.02
+            assert got == want or margin < 2 * scale
+    assert engine.runner.cache.num_free_pages() == 64
+
+
+def test_long_decoding_float32(folders):
+    from dispec_b200 import LLMEngine, SamplingParams
+    folder, config, weights = folders["a"]
+    engine = LLMEngine(load(folder, "float32"), num_blocks=64)
+    prompt = ru.random_ids(3, config["vocab_size"], 1)
+    got = engine.generate(prompt, 260, SamplingParams())
+    assert len(got) == 260
+    # logits of the whole generated sequence, computed once by the plain implementation
+    logits = plain.forward_logits(weights, config, prompt + got)
+    for i, tok in enumerate(got):
+        row = logits[len(prompt) - 1 + i]
+        top2 = torch.topk(row, 2)
+        if float(top2.values[0] - top2.values[1]) > 1e-4:
+            assert int(top2.indices[0]) == tok, i
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_continuous_batching_chunked_mixed_greedy_and_temperature(folders, dtype):
+    """Config B's workload: prompts of 1, 9, 40, 64 tokens, portions of 16 mixed with decoding,
+    12 new tokens each, greedy and temperature 0.8 side by side."""
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    folder, config, weights = folders["b"]
+    engine = ContinuousBatchingEngine(load(folder, dtype), KVConfig(block_size=8), num_blocks=48,
+                                      max_batch_tokens=32, chunk_size=16)
+    reqs = []
+    for i, n in enumerate([1, 9, 40, 64, 9, 40]):
+        prompt = ru.random_ids(n, config["vocab_size"], 400 + i)
+        params = SamplingParams(temperature=0.8 if i % 2 else 0.0, top_k=40 if i == 3 else 0,
+                                top_p=0.9 if i == 5 else 1.0, seed=50 + i)
+        reqs.append((engine.add_request(prompt, 12, params), prompt, params))
+    engine.run_until_done()
+    out = engine.collect_outputs()
+    assert engine.num_prefill_tokens == 1 + 9 + 40 + 64 + 9 + 40
+    for rid, prompt, params in reqs:
+        got = out[rid]
+        assert len(got) == 12
+        want, margin = replay_sampling(weights, config, prompt, got, params)
+        if dtype == "float32":
+            assert got == want or margin < 1e-5, (rid, got, want, margin)
+        else:
+            agree = sum(g == w for g, w in zip(got, want))
+            assert agree >= 10, (rid, got, want)
+    assert engine.runner.cache.num_free_pages() == 48
+
+
+def test_no_leak_between_identical_requests(folders):
+    from dispec_b200 import ContinuousBatchingEngine, SamplingParams
+    folder, config, _ = folders["a"]
+    engine = ContinuousBatchingEngine(load(folder, "bfloat16"), num_blocks=64, max_batch_tokens=64,
+                                      chunk_size=16)
+    prompt = ru.random_ids(21, config["vocab_size"], 7)
+    ids = [engine.add_request(prompt, 48, SamplingParams()) for _ in range(3)]
+    engine.run_until_done()
+    out = engine.collect_outputs()
+    assert out[ids[0]] == out[ids[1]] == out[ids[2]] and len(out[ids[0]]) == 48
+
+
+def test_small_pool_preempts_and_recomputes_with_the_same_tokens(folders):
+    from dispec_b200 import ContinuousBatchingEngine, SamplingParams
+    folder, config, weights = folders["a"]
+    model = load(folder, "float32")
+    prompts = [ru.random_ids(n, config["vocab_size"], 500 + n) for n in (16, 16, 30)]
+    outs = []
+    for blocks in (64, 5):  # 5 pages of 16: the three requests cannot all stay
+        engine = ContinuousBatchingEngine(model, num_blocks=blocks, max_batch_tokens=64, poison=True)
+        ids = [engine.add_request(p, 24, SamplingParams(temperature=0.7, seed=i)) for i, p in enumerate(prompts)]
+        engine.run_until_done()
+        outs.append([engine.collect_outputs()[i] for i in ids])
+        if blocks == 5:
+            assert engine.num_preemptions >= 1
+        assert engine.runner.cache.num_free_pages() == blocks
+        engine.runner.check_device()
+    for roomy, tight, p in zip(outs[0], outs[1], prompts):
+        if roomy != tight:  # only a draw on a knife's edge may differ
+            want, margin = replay_sampling(weights, config, p, tight, SamplingParams(temperature=0.7))
+            assert margin < 1e-5
+
+
+def test_first_tokens_of_a_sequence(folders):
+    """Positions 0, 1, 2: one token at a time from an empty cache."""
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    folder, config, weights = folders["b"]
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 0.05)):
+        runner = ModelRunner(load(folder, dtype), page_size=8, num_pages=4, max_num_seqs=2)
+        ids = ru.random_ids(3, config["vocab_size"], 9)
+        ref = plain.forward_logits(weights, config, ids)
+        runner.admit("s")
+        for i, t in enumerate(ids):
+            row = runner.step([SeqEntry("s", [t], i, [0])])[0].cpu()
+            assert (row - ref[i]).abs().max().item() < tol * max(1.0, ref[i].abs().max().item())
+
+
+def test_step_refuses_bad_input(folders):
+    from dispec_b200.cache import OutOfPagesError
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    folder, config, _ = folders["a"]
+    runner = ModelRunner(load(folder, "float32"), page_size=16, num_pages=2, max_num_seqs=2)
+    runner.admit("s")
+    with pytest.raises(ValueError, match="start at position"):
+        runner.step([SeqEntry("s", [1, 2], 5, [])])
+    with pytest.raises(ValueError, match="token id"):
+        runner.step([SeqEntry("s", [1, 9999], 0, [])])
+    with pytest.raises(KeyError):
+        runner.step([SeqEntry("nobody", [1], 0, [])])
+    with pytest.raises(OutOfPagesError):
+        runner.step([SeqEntry("s", list(range(40)), 0, [])])
+    assert runner.step([SeqEntry("s", [1, 2, 3], 0, [])]).shape == (0, config["vocab_size"])

@@ -1,0 +1,361 @@
+"""Each part alone against its plain function, and the generality of the assembly: a toy
+mixer with state of its own and a toy architecture whose schedule runs a layer twice and lets
+a layer read another layer's cache, all defined here and registered through the public
+calls, without touching the package."""
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_ctx(entries, groups, page_size, num_pages, dtype, tile_tokens=(), state_needs=(), harness=None):
+    from dispec_b200.cache import CacheManager
+    from dispec_b200.cache.storage import CacheStorage, StateStorage
+    from dispec_b200.engine.batch import HostStaging, build_context
+    if harness is None:
+        cache = CacheManager(groups, page_size, num_pages, 8)
+        harness = dict(cache=cache, storage=CacheStorage(groups, page_size, [num_pages] * len(groups), dtype, DEV, poison=True),
+                       states=StateStorage(list(state_needs), 8, DEV), staging=HostStaging(DEV))
+    cache = harness["cache"]
+    for e in entries:
+        if not cache.has(e.req_id):
+            cache.admit(e.req_id)
+        cache.extend(e.req_id, e.start + len(e.tokens))
+    ctx, _ = build_context(entries, cache, harness["storage"], harness["states"], harness["staging"], dtype,
+                           torch.device(DEV), list(tile_tokens), 1 << 30)
+    return ctx, harness
+
+
+def commit(harness, entries):
+    for e in entries:
+        harness["cache"].commit(e.req_id, e.start + len(e.tokens))
+
+
+def rnd(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_part(dtype):
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.parts.norms import RMSNorm
+    norm = RMSNorm(hidden_size=72, eps=1e-5)
+    assert norm.tensor_specs()["weight"].shape == (72,)
+    w = (1 + rnd((72,), 1, 0.1)).to(dtype)
+    norm.load({"weight": w.to(DEV)})
+    x, d = rnd((6, 72), 2).to(dtype), rnd((6, 72), 3).to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    y = norm.forward(None, x.to(DEV))
+    torch.testing.assert_close(y.float().cpu(), plain.rms_norm(x.float(), w.float(), 1e-5), atol=tol, rtol=tol)
+    resid = x.to(DEV).clone()
+    y2 = norm.forward_add(None, resid, d.to(DEV))
+    s = (x.float() + d.float()).to(dtype)
+    assert torch.equal(resid.cpu(), s)
+    torch.testing.assert_close(y2.float().cpu(), plain.rms_norm(s.float(), w.float(), 1e-5), atol=tol, rtol=tol)
+
+
+def test_rotary_part_matches_the_plain_tables():
+    from dispec_b200.parts.rotary import RotaryEncoding
+    pe = RotaryEncoding(head_dim=48, theta=50000.0)
+    pe.prepare(DEV)
+    pos = torch.tensor([0, 1, 77, 4000])
+    cos, sin = plain.rope_tables(pos, 48, 50000.0)
+    ang = pos.float()[:, None] * pe.inv_freq.cpu()[None]
+    assert torch.equal(torch.cat([ang, ang], -1).cos(), cos) and pe.rotary_dim == 48
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from dispec_b200.parts.swiglu import SwiGLUFeedForward
+    ff = SwiGLUFeedForward(hidden_size=72, intermediate_size=200)
+    wg, wu, wd = rnd((200, 72), 4, 0.2).to(dtype), rnd((200, 72), 5, 0.2).to(dtype), rnd((72, 200), 6, 0.2).to(dtype)
+    ff.load({"gate_proj.weight": wg.to(DEV), "up_proj.weight": wu.to(DEV), "down_proj.weight": wd.to(DEV)})
+    x = rnd((5, 72), 7).to(dtype)
+    y = ff.forward(None, x.to(DEV)).float().cpu()
+    ref = plain.swiglu_mlp(x.float(), wg.float(), wu.float(), wd.float())
+    tol = 2e-5 if dtype == torch.float32 else 5e-2
+    torch.testing.assert_close(y, ref, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.parts.embedding import LinearHead, TokenEmbedding
+    emb, head = TokenEmbedding(101, 40), LinearHead(101, 40)
+    table = rnd((101, 40), 8).to(dtype).to(DEV)
+    emb.load({"weight": table})
+    head.load({"weight": table})
+    ctx, _ = make_ctx([SeqEntry("s", [100, 0, 7], 0, [])], [], 4, 4, dtype)
+    x = emb.forward(ctx)
+    assert torch.equal(x, table[[100, 0, 7]])
+    logits = head.forward(ctx, x)
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits.cpu(), x.float().cpu() @ table.float().cpu().T,
+                               atol=1e-4 if dtype == torch.float32 else 2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 9])
+def test_attention_part_in_two_portions(dtype, window):
+    from dispec_b200.cache import CacheGroupSpec
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.parts.attention import GQAAttention
+    from dispec_b200.parts.rotary import RotaryEncoding
+    H, KVH, D, hidden = 6, 2, 32, 72
+    pe = RotaryEncoding(D, 20000.0)
+    pe.prepare(DEV)
+    mixer = GQAAttention(hidden, H, KVH, D, qkv_bias=True, position_encoding=pe, window=window)
+    specs = mixer.tensor_specs()
+    cpu = {n: rnd(s.shape, 10 + i, 0.15).to(dtype) for i, (n, s) in enumerate(specs.items())}
+    mixer.load({n: t.to(DEV) for n, t in cpu.items()})
+    assert mixer.cache_need().window == window
+    T = 29
+    x = rnd((T, hidden), 40).to(dtype)
+    groups = [CacheGroupSpec(KVH, D, window, 1)]
+    tiles = [mixer.tokens_per_attention_tile()]
+    from dispec_b200.models.model import CachePlacement
+    out, harness, pos = [], None, 0
+    for n in (18, 11):
+        e = [SeqEntry("s", list(range(n)), pos, [])]
+        ctx, harness = make_ctx(e, groups, 8, 6, dtype, tiles, harness=harness)
+        out.append(mixer.forward(ctx, x[pos:pos + n].to(DEV), ctx.cache_view(CachePlacement(0, 0), True), None))
+        commit(harness, e)
+        pos += n
+    got = torch.cat(out).float().cpu()
+    f = {n: t.float() for n, t in cpu.items()}
+    q, k, v = plain.qkv_projection(x.float(), f["q_proj.weight"], f["q_proj.bias"], f["k_proj.weight"],
+                                   f["k_proj.bias"], f["v_proj.weight"], f["v_proj.bias"], H, KVH, D)
+    cos, sin = plain.rope_tables(torch.arange(T), D, 20000.0)
+    o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, window)
+    ref = o.reshape(T, -1) @ f["o_proj.weight"].T
+    tol = 2e-5 if dtype == torch.float32 else 5e-2
+    torch.testing.assert_close(got, ref, atol=tol, rtol=tol)
+
+
+# ------------------------------------------------------------------- toy parts and models
+
+def register_toys():
+    """A mixer with fixed-size state of its own (a per-channel decaying sum), and two toy
+    architectures.  Registered once per process through the public calls."""
+    from dispec_b200 import register_architecture, register_part
+    from dispec_b200.config.model_config import ModelConfig
+    from dispec_b200.models.spec import LayerCall, ModelSpec
+    from dispec_b200.parts.base import Mixer, PartSpec, StateNeed, TensorSpec
+    from dispec_b200.registry import architectures
+
+    if "ToyStateForCausalLM" in architectures():
+        return
+
+    @register_part("mixer", "toy_decay")
+    class DecayMixer(Mixer):
+        """s_t = sigmoid(a) * s_{t-1} + x_t W_in^T ;  y_t = s_t W_out^T.  The state s lives in
+        the request's state slot and is carried across portions and steps."""
+
+        def __init__(self, hidden_size, state_size):
+            self.hidden_size, self.state_size = hidden_size, state_size
+
+        def tensor_specs(self):
+            return {"in.weight": TensorSpec((self.state_size, self.hidden_size)),
+                    "out.weight": TensorSpec((self.hidden_size, self.state_size)),
+                    "decay": TensorSpec((self.state_size,), dtype="float32")}
+
+        def load(self, tensors):
+            self.w_in, self.w_out, self.decay = tensors["in.weight"], tensors["out.weight"], tensors["decay"]
+            assert self.decay.dtype == torch.float32  # stays 32-bit in every mode
+
+        def state_need(self):
+            return StateNeed((self.state_size,), "float32")
+
+        def forward(self, ctx, x, cache, state):
+            assert cache is None
+            u = x.float() @ self.w_in.float().T
+            y = torch.empty_like(u)
+            a = torch.sigmoid(self.decay)
+            for s in range(ctx.num_seqs):
+                slot = ctx.host_state_slot[s]
+                st = state.buffer[slot]
+                for t in range(ctx.host_q_start[s], ctx.host_q_start[s + 1]):
+                    st = a * st + u[t]
+                    y[t] = st
+                state.buffer[slot] = st
+            return (y @ self.w_out.float().T).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyStateForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+        state_size: int = 0
+        intermediate_size: int = 0
+        num_layers: int = 0
+        eps: float = 0.0
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "state_size",
+                                            "intermediate_size", "num_layers", "eps")})
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in (
+                "vocab_size", "hidden_size", "state_size", "intermediate_size", "num_layers", "eps")})
+
+    def build_toy(cfg):
+        h = cfg.hidden_size
+        layers = []
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            norm = lambda n: PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": p + n})
+            mixer = PartSpec("mixer", "toy_decay", {"hidden_size": h, "state_size": cfg.state_size},
+                             {"in.weight": p + "mix.in", "out.weight": p + "mix.out", "decay": p + "mix.decay"})
+            ffn = PartSpec("feed_forward", "swiglu", {"hidden_size": h, "intermediate_size": cfg.intermediate_size},
+                           {f"{n}_proj.weight": p + "ffn." + n for n in ("gate", "up", "down")})
+            layers.append(PartSpec("block", "pre_norm", {"mixer_norm": norm("n1"), "mixer": mixer,
+                                                         "ffn_norm": norm("n2"), "feed_forward": ffn}))
+        return ModelSpec("ToyStateForCausalLM",
+                         PartSpec("embedding", "token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                         layers,
+                         PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": "final"}),
+                         PartSpec("head", "linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                         vocab_size=cfg.vocab_size, max_position=4096)
+
+    register_architecture("ToyStateForCausalLM", ToyConfig, build_toy)
+
+    # a Qwen2-shaped toy whose schedule runs layer 0 twice and lets the last call of layer 1
+    # read the cache its first call wrote
+    from dispec_b200.config import Qwen2Config
+    from dispec_b200.models.qwen2 import build_qwen2
+
+    @dataclass(frozen=True)
+    class LoopConfig(Qwen2Config):
+        architecture: ClassVar[str] = "ToyLoopForCausalLM"
+
+    def build_loop(cfg):
+        spec = build_qwen2(cfg)
+        spec.architecture = "ToyLoopForCausalLM"
+        spec.schedule = [LayerCall(0, 0, True), LayerCall(1, 1, True), LayerCall(0, 2, True),
+                         LayerCall(1, 1, False)]
+        return spec
+
+    register_architecture("ToyLoopForCausalLM", LoopConfig, build_loop)
+
+
+def plain_toy_state(weights, cfg, ids):
+    x = weights["emb"][torch.as_tensor(ids)]
+    for i in range(cfg["num_layers"]):
+        p = f"layers.{i}."
+        h = plain.rms_norm(x, weights[p + "n1"], cfg["eps"])
+        u = h @ weights[p + "mix.in"].T
+        a = torch.sigmoid(weights[p + "mix.decay"])
+        st = torch.zeros(cfg["state_size"])
+        ys = []
+        for t in range(len(ids)):
+            st = a * st + u[t]
+            ys.append(st)
+        x = x + torch.stack(ys) @ weights[p + "mix.out"].T
+        h = plain.rms_norm(x, weights[p + "n2"], cfg["eps"])
+        x = x + plain.swiglu_mlp(h, weights[p + "ffn.gate"], weights[p + "ffn.up"], weights[p + "ffn.down"])
+    return plain.rms_norm(x, weights["final"], cfg["eps"]) @ weights["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    from safetensors.torch import load_file
+    from dispec_b200 import load_model, load_model_config, write_random_model
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    register_toys()
+    cfg_dict = dict(architectures=["ToyStateForCausalLM"], vocab_size=90, hidden_size=48, state_size=40,
+                    intermediate_size=64, num_layers=2, eps=1e-5)
+    cfg = load_model_config(cfg_dict)
+    write_random_model(cfg, str(tmp_path), seed=3, std=0.2, dtype="bfloat16")
+    weights = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+    model = load_model(str(tmp_path), dtype, DEV)
+    assert model.cache_groups == [] and len(model.state_needs) == 2
+    assert model.layers[0].mixer.decay.dtype == torch.float32
+    runner = ModelRunner(model, page_size=16, num_pages=4, max_num_seqs=3)
+    a, b = ru.random_ids(23, 90, 1), ru.random_ids(11, 90, 2)
+    ref_a, ref_b = plain_toy_state(weights, cfg_dict, a), plain_toy_state(weights, cfg_dict, b)
+    runner.admit("a")
+    runner.admit("b")
+    got_a, got_b = [], []
+    # a in portions and single tokens, b beside it, cut anywhere
+    got_a.append(runner.step([SeqEntry("a", a[:9], 0, list(range(9)))]))
+    l = runner.step([SeqEntry("a", a[9:10], 9, [0]), SeqEntry("b", b[:6], 0, list(range(6)))])
+    got_a.append(l[:1]); got_b.append(l[1:])
+    l = runner.step([SeqEntry("b", b[6:7], 6, [0]), SeqEntry("a", a[10:23], 10, list(range(13)))])
+    got_b.append(l[:1]); got_a.append(l[1:])
+    got_b.append(runner.step([SeqEntry("b", b[7:], 7, list(range(4)))]))
+    tol = 1e-4 if dtype == "float32" else 0.05
+    scale = max(1.0, ref_a.abs().max().item())
+    assert (torch.cat(got_a).cpu() - ref_a).abs().max().item() < tol * scale
+    assert (torch.cat(got_b).cpu() - ref_b).abs().max().item() < tol * scale
+    # a state slot is zeroed when it is handed to the next request
+    runner.release("a")
+    runner.admit("c")
+    again = runner.step([SeqEntry("c", a, 0, list(range(len(a))))])
+    assert (again.cpu() - ref_a).abs().max().item() < tol * scale
+
+
+def plain_loop(weights, config, ids):
+    c = plain.read_config(config)
+    w = weights
+    T = len(ids)
+    cos, sin = plain.rope_tables(torch.arange(T), c["head_dim"], c["theta"])
+    x = plain.embed(w["model.embed_tokens.weight"], torch.as_tensor(ids))
+    x = plain.decoder_layer(x, w, "model.layers.0.", c, cos, sin, 0)
+    # layer 1, first call: remember its rotated keys and its values
+    p = "model.layers.1."
+    a = p + "self_attn."
+    kept = {}
+
+    def layer1(x, reuse):
+        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+        q, k, v = plain.qkv_projection(h, w[a + "q_proj.weight"], w[a + "q_proj.bias"], w[a + "k_proj.weight"],
+                                       w[a + "k_proj.bias"], w[a + "v_proj.weight"], w[a + "v_proj.bias"],
+                                       c["heads"], c["kv_heads"], c["head_dim"])
+        q, k = plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin)
+        if reuse:
+            k, v = kept["k"], kept["v"]
+        else:
+            kept["k"], kept["v"] = k, v
+        o = plain.causal_attention(q, k, v)
+        x = x + o.reshape(T, -1) @ w[a + "o_proj.weight"].T
+        h = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+        return x + plain.swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                    w[p + "mlp.down_proj.weight"])
+
+    x = layer1(x, False)
+    x = plain.decoder_layer(x, w, "model.layers.0.", c, cos, sin, 0)
+    x = layer1(x, True)
+    x = plain.rms_norm(x, w["model.norm.weight"], c["eps"])
+    return x @ w["lm_head.weight"].T
+
+
+def test_schedule_runs_a_layer_twice_and_shares_a_cache(tmp_path):
+    import json
+    from safetensors.torch import load_file
+    from dispec_b200 import load_model, load_model_config, write_random_model
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    register_toys()
+    d = dict(ru.CONFIG_B, architectures=["ToyLoopForCausalLM"], num_hidden_layers=2)
+    cfg = load_model_config(d)
+    write_random_model(cfg, str(tmp_path), seed=4, std=0.08, dtype="bfloat16")
+    cfg_json = json.load(open(tmp_path / "config.json"))
+    weights = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+    model = load_model(str(tmp_path), "float32", DEV)
+    assert len(model.schedule) == 4 and model.cache_groups[0].num_slots == 3
+    runner = ModelRunner(model, page_size=8, num_pages=8, max_num_seqs=2, poison=True)
+    ids = ru.random_ids(37, d["vocab_size"], 5)
+    ref = plain_loop(weights, cfg_json, ids)
+    runner.admit("s")
+    out, pos = [], 0
+    for n in (14, 2, 1, 1, 19):
+        out.append(runner.step([SeqEntry("s", ids[pos:pos + n], pos, list(range(n)))]))
+        pos += n
+    assert (torch.cat(out).cpu() - ref).abs().max().item() < 1e-4
