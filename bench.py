@@ -1,0 +1,380 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine: decoded tokens a second on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests (Qwen2.5-1.5B layer sizes, random weights
+N(0, 0.02) from seed 2, 1024-token random prompts, page size 16, context limit 4096).  W warm-up
+steps, then exactly K steps between two device synchronisations, timed with CUDA events; each
+step feeds back the tokens the previous step chose (argmax), read on the host.  One JSON line
+goes to standard output:
+
+  value      decoded tokens a second, step function + argmax driven directly
+  e2e        the same through ContinuousBatchingEngine (scheduler, sampler, pinned staging):
+             host token ids in, host token ids out, wall clock
+  prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
+  roofline   bytes a decode step must read (every weight once + the live requests' cache)
+             divided by its time, against the measured copy bandwidth
+  points     decode at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when present ("of measured"), else the
+fallback 6.65 TB/s and 1.59 PFLOP/s ("of fallback").  ``--impl reference`` runs the unmodified
+reference (installed under baseline/_ref) through its own ContinuousBatchingEngine on the same
+shapes.  With --gpus above 1 it prints one line saying so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen2.5-1.5B layer sizes (the benchmark's configuration, not the package's)
+BENCH_CONFIG = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28, hidden_size=1536,
+    num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960,
+    vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, hidden_act="silu",
+    tie_word_embeddings=True, max_position_embeddings=4096, use_sliding_window=False)
+SEED, STD = 2, 0.02
+BATCH, PROMPT_LEN, NEW_TOKENS, CONTEXT_LEN, PAGE_SIZE = 8, 1024, 256, 4096, 16
+PREFILL_TOKENS = 2048
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip().splitlines()
+                if out:
+                    self.samples.append([x.strip() for x in out[0].split(",")])
+            except Exception:  # noqa: BLE001 - sampling must never break the run
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:]) if v.lower().startswith("active")})
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(mhz)}
+
+
+def random_prompts(n, length, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def model_bytes_and_flops(cfg: dict, layers: int):
+    h, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, KVH, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (H + 2 * KVH) * D * h + (H + 2 * KVH) * D + H * D * h + 3 * I * h + 2 * h
+    weight_bytes = 2 * (layers * per_layer + V * h + h)  # lm_head (tied or not) read once
+    kv_bytes_per_token = 2 * layers * KVH * D * 2
+    matmul_params = layers * ((H + 2 * KVH) * D * h + H * D * h + 3 * I * h)
+
+    def prefill_flops(T):
+        return 2 * T * matmul_params + layers * 2 * H * D * T * T + 2 * V * h
+
+    return weight_bytes, kv_bytes_per_token, prefill_flops
+
+
+# ------------------------------------------------------------------------------ our arm
+
+def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
+    """Step function + argmax, no scheduler: returns (ms per step, launches in the timed region,
+    mean context length over the timed steps)."""
+    import torch
+    from dispec_b200 import ops
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.ops.library import LaunchCounter
+    ids = [f"r{i}" for i in range(len(prompts))]
+    for rid in ids:
+        runner.admit(rid)
+    last = {}
+    pending = list(zip(ids, prompts))
+    while pending:  # prefill, untimed
+        batch, used = [], 0
+        while pending and used + len(pending[0][1]) <= max_batch_tokens:
+            rid, p = pending.pop(0)
+            batch.append(SeqEntry(rid, p, 0, [len(p) - 1]))
+            used += len(p)
+        toks = ops.argmax(runner.step(batch)).tolist()
+        for e, t in zip(batch, toks):
+            last[e.req_id] = t
+    pos = {rid: len(p) for rid, p in zip(ids, prompts)}
+
+    def one_step():
+        entries = [SeqEntry(rid, [last[rid]], pos[rid], [0]) for rid in ids]
+        toks = ops.argmax(runner.step(entries)).tolist()  # device -> host read of the result
+        for rid, t in zip(ids, toks):
+            last[rid] = t
+            pos[rid] += 1
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    ctx0 = statistics.mean(pos.values())
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = LaunchCounter.n
+    start.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = LaunchCounter.n - n0
+    mean_ctx = (ctx0 + statistics.mean(pos.values())) / 2
+    for rid in ids:
+        runner.release(rid)
+    return ms, launches, mean_ctx
+
+
+def decode_e2e(model, prompts, steps, warmup, num_blocks):
+    """Through the public entry point: host token ids in, host token ids out."""
+    import torch
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    engine = ContinuousBatchingEngine(model, KVConfig(block_size=PAGE_SIZE), num_blocks=num_blocks,
+                                      max_batch_tokens=8192, max_num_seqs=max(len(prompts), 8))
+    for p in prompts:
+        engine.add_request(p, warmup + steps + 8, SamplingParams(0.0))
+    while engine.waiting or engine.prefilling:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert len(engine.running) == len(prompts)
+    h2d = engine.runner.staging.last_bytes
+    return len(prompts) * steps / dt, dt / steps * 1000, h2d, 4 * len(prompts)
+
+
+def prefill_time(runner, prompt, repeats=5):
+    import torch
+    from dispec_b200.engine import SeqEntry
+    ts = []
+    for _ in range(repeats + 2):
+        runner.admit("p")
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        runner.step([SeqEntry("p", prompt, 0, [len(prompt) - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+        runner.release("p")
+    return statistics.median(ts[2:])
+
+
+def run_ours(args) -> dict:
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+
+    cfg_dict = dict(BENCH_CONFIG)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    layers = cfg_dict["num_hidden_layers"]
+    cfg = load_model_config(cfg_dict)
+    t0 = time.time()
+    model = load_random_model(cfg, SEED, STD, "bfloat16", "cuda:0")
+    print(f"bench: model ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+    pk = peaks()
+    weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg_dict, layers)
+    pages_per_req = (PROMPT_LEN + NEW_TOKENS + args.steps + args.warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    vocab = cfg_dict["vocab_size"]
+
+    def runner_for(batch):
+        return ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(batch * pages_per_req, 160),
+                           max_num_seqs=max(batch, 8), cuda_graph=True)
+
+    if args.only == "decode":
+        r = runner_for(args.batch)
+        ms, launches, ctx = decode_direct(r, random_prompts(args.batch, PROMPT_LEN, vocab, 11), args.steps, args.warmup)
+        return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+                "tok_s": round(args.batch * 1000.0 / ms, 1), "gpu_launches": launches, "mean_ctx": ctx}
+    if args.only == "prefill":
+        r = runner_for(1)
+        pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=max(1, args.steps))
+        return {"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                "frac": round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    # headline: batch 8
+    runner = runner_for(BATCH)
+    prompts = random_prompts(BATCH, PROMPT_LEN, vocab, 11)
+    with ClockSampler() as clocks:
+        ms, launches, mean_ctx = decode_direct(runner, prompts, args.steps, args.warmup)
+    value = BATCH * 1000.0 / ms
+    step_bytes = weight_bytes + BATCH * mean_ctx * kv_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    # prefill of 2,048 tokens
+    pms = prefill_time(runner, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0])
+    pflops = prefill_flops(PREFILL_TOKENS)
+    del runner
+    torch.cuda.empty_cache()
+    e2e_value, e2e_ms, h2d, d2h = decode_e2e(model, prompts, args.steps, args.warmup, BATCH * pages_per_req + 64)
+    points = {}
+    for b in (1, 64):
+        r = runner_for(b)
+        steps = max(20, min(args.steps, 100))
+        bms, _, _ = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, max(3, args.warmup // 2))
+        points[f"decode_b{b}"] = round(b * 1000.0 / bms, 1)
+        del r
+        torch.cuda.empty_cache()
+    from dispec_b200.ops import library
+    return {
+        "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": full_layers,
+            "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
+            "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
+            "intermediate": cfg_dict["intermediate_size"], "vocab": vocab, "tied": True,
+            "global_batch": BATCH, "seq_len": PROMPT_LEN, "context_len": CONTEXT_LEN,
+            "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+            "weights": f"random N(0,{STD}) seed {SEED}",
+            "l2": "no flush: each step reads %.2f GB of weights, above the 126 MB L2" % (weight_bytes / 1e9),
+            "peaks": "of " + pk["source"],
+        },
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / pms * 1000.0, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pms, 3), "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "kernel_libraries": [os.path.basename(p) for p in library.loaded_libraries()],
+    }
+
+
+# ------------------------------------------------------------------------- reference arm
+
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "dispec")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is absent (the reference was not installed)"}
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from transformers import Qwen2Config, Qwen2ForCausalLM
+        from dispec.sampling import SamplingParams
+        from dispec.sched.scheduler import ContinuousBatchingEngine
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:200]}
+    cfg = {k: v for k, v in BENCH_CONFIG.items() if k not in ("architectures", "model_type")}
+    torch.manual_seed(SEED)
+    with torch.device("cuda"):
+        model = Qwen2ForCausalLM(Qwen2Config(**cfg)).to(torch.bfloat16)
+    model.eval()
+    model.requires_grad_(False)
+    pages = BATCH * ((PROMPT_LEN + NEW_TOKENS + args.steps + args.warmup) // PAGE_SIZE + 2) + 64
+    eng = ContinuousBatchingEngine(model, num_blocks=pages, max_batch_tokens=8192,
+                                   attn_backend="triton", fuse=True)
+    for p in random_prompts(BATCH, PROMPT_LEN, cfg["vocab_size"], 11):
+        eng.add_request(p, args.warmup + args.steps + 8, SamplingParams(0.0))
+    while eng.waiting or eng.prefilling:
+        eng.step()
+    with ClockSampler() as clocks:
+        for _ in range(args.warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        s.record()
+        for _ in range(args.steps):
+            eng.step()
+        e.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    ms = s.elapsed_time(e) / args.steps
+    return {
+        "metric": "decode_tokens_per_s", "value": round(BATCH * 1000.0 / ms, 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "reference",
+        "config": {"model": "Qwen2.5-1.5B shape", "layers": cfg["num_hidden_layers"], "global_batch": BATCH,
+                   "seq_len": PROMPT_LEN, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+                   "path": "dispec ContinuousBatchingEngine(attn_backend=triton, fuse=True)"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(BATCH * args.steps / wall, 1), "unit": "tok/s"},
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="profiling aid: run one phase only and print a short line")
+    ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    try:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    except Exception as e:  # noqa: BLE001
+        if args.impl == "reference":
+            line = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
+        else:
+            raise
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -13,7 +13,7 @@ from dispec_b200.registry import (architectures, register_architecture,  # noqa:
 def __getattr__(name):
     # heavier pieces load on first use, so that configuration and cache bookkeeping import
     # without touching CUDA
-    if name in ("load_model", "build_model", "write_random_model"):
+    if name in ("load_model", "build_model", "write_random_model", "load_random_model"):
         import dispec_b200.weights as w
         return getattr(w, name)
     if name in ("LLMEngine", "ContinuousBatchingEngine", "ModelRunner", "SeqEntry", "Scheduler"):

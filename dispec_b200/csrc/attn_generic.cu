@@ -172,15 +172,23 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
   const size_t smem = (size_t)(GCHUNK * D + GCHUNK * THREADS) * sizeof(float) + THREADS * sizeof(long);
   dim3 grid(T, KVH);
   if (dtype == DSP_F32) {
-    DSP_CUDA(cudaFuncSetAttribute(attn_generic_kernel<float>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t configured = 0;
+    if (smem > configured) {
+      DSP_CUDA(cudaFuncSetAttribute(attn_generic_kernel<float>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = smem;
+    }
     attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
         (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, page_table, pt_stride,
         positions, seq_of_token, (float*)out, out_stride, H, KVH, D, page_size, num_pages, window,
         scale, err);
   } else if (dtype == DSP_BF16) {
-    DSP_CUDA(cudaFuncSetAttribute(attn_generic_kernel<bf16>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t configured = 0;
+    if (smem > configured) {
+      DSP_CUDA(cudaFuncSetAttribute(attn_generic_kernel<bf16>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = smem;
+    }
     attn_generic_kernel<bf16><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride,
         positions, seq_of_token, (bf16*)out, out_stride, H, KVH, D, page_size, num_pages, window,

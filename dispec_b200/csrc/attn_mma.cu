@@ -320,8 +320,12 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = err;
   const int smem = 5 * TILE_BYTES;
-  if (cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return 4;
+  static bool configured = false;  // once; not repeated under graph capture
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return 4;
+    configured = true;
+  }
   dim3 grid(num_tiles, KVH, num_splits);
   attn_mma_kernel<<<grid, THREADS, smem, stream>>>(p, tile_offset);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;

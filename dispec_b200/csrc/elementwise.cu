@@ -79,23 +79,117 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
   }
 }
 
+// Fast form of the same computation for rows whose bytes are a multiple of 16 and that fit in
+// registers (hidden <= 256 threads * 4 vectors): one read of x (and delta), one write of y.
+template <typename T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ w,
+                   T* __restrict__ y, const int* __restrict__ rows, int hidden, float eps,
+                   int write_back) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const size_t in_row = rows ? (size_t)rows[r] : (size_t)r;
+  const int nvec = hidden / N;
+  uint4* xr = reinterpret_cast<uint4*>(x + in_row * hidden);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + in_row * hidden) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)r * hidden);
+  float vals[VPT][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nvec) {
+      uint4 raw = xr[i];
+      const T* e = reinterpret_cast<const T*>(&raw);
+      if (dr) {
+        uint4 draw = dr[i];
+        const T* d = reinterpret_cast<const T*>(&draw);
+        uint4 sum_raw;
+        T* sp = reinterpret_cast<T*>(&sum_raw);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          sp[k] = from_f32<T>(to_f32(e[k]) + to_f32(d[k]));
+          vals[j][k] = to_f32(sp[k]);
+        }
+        if (write_back) xr[i] = sum_raw;
+      } else {
+#pragma unroll
+        for (int k = 0; k < N; ++k) vals[j][k] = to_f32(e[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) ss += vals[j][k] * vals[j][k];
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nvec) {
+      uint4 wraw = wr[i];
+      const T* wv = reinterpret_cast<const T*>(&wraw);
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const T n = from_f32<T>(vals[j][k] * rstd);
+        o[k] = from_f32<T>(to_f32(wv[k]) * to_f32(n));
+      }
+      yr[i] = out;
+    }
+  }
+}
+
+template <typename T>
+static bool launch_rmsnorm_vec(void* x, const void* delta, const void* w, void* y, const int* rows,
+                               int n_rows, int hidden, float eps, int write_back,
+                               cudaStream_t stream) {
+  constexpr int N = Vec16<T>::N;
+  if (hidden % N != 0) return false;
+  const uintptr_t bits = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)y;
+  if (bits % 16 != 0) return false;
+  const int nvec = hidden / N;
+  if (nvec <= 256)
+    rmsnorm_vec_kernel<T, 1><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+  else if (nvec <= 512)
+    rmsnorm_vec_kernel<T, 2><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+  else if (nvec <= 1024)
+    rmsnorm_vec_kernel<T, 4><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+  else
+    return false;
+  return true;
+}
+
 extern "C" int dsp_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows,
                            int n_rows, int hidden, float eps, int write_back, int dtype,
                            cudaStream_t stream) {
   if (n_rows == 0) return 0;
   DSP_REQUIRE(hidden > 0, "dsp_rmsnorm: hidden=%d", hidden);
   DSP_REQUIRE(!(write_back && !delta), "dsp_rmsnorm: write_back without delta");
+  DSP_REQUIRE(dtype == DSP_F32 || dtype == DSP_BF16, "dsp_rmsnorm: unknown dtype %d", dtype);
+  const bool fast = dtype == DSP_F32
+      ? launch_rmsnorm_vec<float>(x, delta, w, y, rows, n_rows, hidden, eps, write_back, stream)
+      : launch_rmsnorm_vec<bf16>(x, delta, w, y, rows, n_rows, hidden, eps, write_back, stream);
+  if (fast) {
+    DSP_CHECK_LAUNCH("dsp_rmsnorm");
+    return 0;
+  }
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == DSP_F32)
     rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)x, (const float*)delta,
                                                           (const float*)w, (float*)y, rows, hidden,
                                                           eps, write_back);
-  else if (dtype == DSP_BF16)
+  else
     rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>((bf16*)x, (const bf16*)delta,
                                                          (const bf16*)w, (bf16*)y, rows, hidden, eps,
                                                          write_back);
-  else
-    DSP_REQUIRE(false, "dsp_rmsnorm: unknown dtype %d", dtype);
   DSP_CHECK_LAUNCH("dsp_rmsnorm");
   return 0;
 }
@@ -115,17 +209,51 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs) {
+  constexpr int N = Vec16<T>::N;
+  const int vec_per_row = inter / N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / vec_per_row;
+    const int c = (int)(i % vec_per_row);
+    const uint4 graw = reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter)[c];
+    const uint4 uraw = reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + inter)[c];
+    const T* g = reinterpret_cast<const T*>(&graw);
+    const T* u = reinterpret_cast<const T*>(&uraw);
+    uint4 oraw;
+    T* o = reinterpret_cast<T*>(&oraw);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const float gv = to_f32(g[k]);
+      o[k] = from_f32<T>(gv / (1.f + expf(-gv)) * to_f32(u[k]));
+    }
+    reinterpret_cast<uint4*>(out + t * (size_t)inter)[c] = oraw;
+  }
+}
+
 extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int dtype,
                           cudaStream_t stream) {
   if (T == 0) return 0;
+  DSP_REQUIRE(dtype == DSP_F32 || dtype == DSP_BF16, "dsp_swiglu: unknown dtype %d", dtype);
+  const int N = dtype == DSP_F32 ? 4 : 8;
+  if (inter % N == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const size_t total = (size_t)T * (inter / N);
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (dtype == DSP_F32)
+      swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else
+      swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+    DSP_CHECK_LAUNCH("dsp_swiglu");
+    return 0;
+  }
   const int chunks = (inter + 255) / 256;
   dim3 grid(T, chunks > 64 ? 64 : chunks);
   if (dtype == DSP_F32)
     swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter);
-  else if (dtype == DSP_BF16)
-    swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
   else
-    DSP_REQUIRE(false, "dsp_swiglu: unknown dtype %d", dtype);
+    swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
   DSP_CHECK_LAUNCH("dsp_swiglu");
   return 0;
 }
@@ -190,6 +318,81 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// One block per token for head sizes in whole 16-byte pieces: cos and sin of the token's angles
+// are computed once into shared memory and every head reuses them; data moves in 16-byte pieces.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_store_token_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                           const int* __restrict__ seq_of_token,
+                           const int* __restrict__ page_table, int pt_stride,
+                           T* __restrict__ k_pool, T* __restrict__ v_pool,
+                           const float* __restrict__ inv_freq, int H, int KVH, int D,
+                           int rotary_dim, int page_size, int num_pages, int write_kv, int* err) {
+  constexpr int N = Vec16<T>::N;
+  extern __shared__ float cs[];  // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int half = rotary_dim / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    cs[i] = c;
+    cs[half + i] = s;
+  }
+  long kv_base = -1;  // element offset of this token's row of kv head 0 in the pools
+  if (write_kv) {
+    const int seq = seq_of_token[t];
+    const int page = page_table[(size_t)seq * pt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, DSP_ERR_BAD_PAGE);
+    } else {
+      kv_base = ((long)page * KVH * page_size + (pos % page_size)) * D;
+    }
+  }
+  __syncthreads();
+  T* row = qkv + (size_t)t * (H + 2 * KVH) * D;
+  const int hv = half / N;        // 16-byte pieces in the rotated half
+  const int dv = D / N;           // pieces per head
+  // rotated heads (q and k): one work item rotates piece j of the low half with piece j of the high half
+  const int rot_items = (H + KVH) * hv;
+  for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+    const int head = it / hv, j = it % hv;
+    uint4* lo_p = reinterpret_cast<uint4*>(row + (size_t)head * D) + j;
+    uint4* hi_p = reinterpret_cast<uint4*>(row + (size_t)head * D + half) + j;
+    uint4 lo = *lo_p, hi = *hi_p;
+    T* a = reinterpret_cast<T*>(&lo);
+    T* b = reinterpret_cast<T*>(&hi);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const float c = cs[j * N + k], sn = cs[half + j * N + k];
+      const float av = to_f32(a[k]), bv = to_f32(b[k]);
+      a[k] = from_f32<T>(av * c - bv * sn);
+      b[k] = from_f32<T>(bv * c + av * sn);
+    }
+    *lo_p = lo;
+    *hi_p = hi;
+    if (head >= H && kv_base >= 0) {
+      T* dst = k_pool + kv_base + (long)(head - H) * page_size * D;
+      reinterpret_cast<uint4*>(dst)[j] = lo;
+      reinterpret_cast<uint4*>(dst + half)[j] = hi;
+    }
+  }
+  if (kv_base < 0) return;
+  // unrotated tail of k heads, and v heads
+  const int tail_v = (D - rotary_dim) / N;
+  for (int it = threadIdx.x; it < KVH * tail_v; it += blockDim.x) {
+    const int kvh = it / tail_v, j = it % tail_v;
+    const uint4 v = reinterpret_cast<const uint4*>(row + (size_t)(H + kvh) * D + rotary_dim)[j];
+    reinterpret_cast<uint4*>(k_pool + kv_base + (long)kvh * page_size * D + rotary_dim)[j] = v;
+  }
+  for (int it = threadIdx.x; it < KVH * dv; it += blockDim.x) {
+    const int kvh = it / dv, j = it % dv;
+    const uint4 v = reinterpret_cast<const uint4*>(row + (size_t)(H + KVH + kvh) * D)[j];
+    reinterpret_cast<uint4*>(v_pool + kv_base + (long)kvh * page_size * D)[j] = v;
+  }
+}
+
 extern "C" int dsp_rope_kv_store(void* qkv, const int* positions, const int* seq_of_token,
                                  const int* page_table, int pt_stride, void* k_pool, void* v_pool,
                                  const float* inv_freq, int T, int H, int KVH, int D,
@@ -200,20 +403,35 @@ extern "C" int dsp_rope_kv_store(void* qkv, const int* positions, const int* seq
               "dsp_rope_kv_store: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, D);
   DSP_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "dsp_rope_kv_store: no inv_freq table");
   DSP_REQUIRE(H + 2 * KVH <= 65535, "dsp_rope_kv_store: too many heads");
+  DSP_REQUIRE(dtype == DSP_F32 || dtype == DSP_BF16, "dsp_rope_kv_store: unknown dtype %d", dtype);
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_rope_kv_store: no device error word");
+  const int N = dtype == DSP_F32 ? 4 : 8;
+  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool;
+  if (rotary_dim > 0 && (rotary_dim / 2) % N == 0 && D % N == 0 && bits % 16 == 0 && rotary_dim <= 4096) {
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
+    const int threads = (H + KVH) * (rotary_dim / 2 / N) >= 256 ? 256 : 128;
+    if (dtype == DSP_F32)
+      rope_kv_store_token_kernel<float><<<T, threads, smem, stream>>>(
+          (float*)qkv, positions, seq_of_token, page_table, pt_stride, (float*)k_pool, (float*)v_pool,
+          inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+    else
+      rope_kv_store_token_kernel<bf16><<<T, threads, smem, stream>>>(
+          (bf16*)qkv, positions, seq_of_token, page_table, pt_stride, (bf16*)k_pool, (bf16*)v_pool,
+          inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+    DSP_CHECK_LAUNCH("dsp_rope_kv_store");
+    return 0;
+  }
   dim3 grid(T, H + 2 * KVH);
   const int threads = D / 2 >= 64 ? 64 : 32;
   if (dtype == DSP_F32)
     rope_kv_store_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)qkv, positions, seq_of_token, page_table, pt_stride, (float*)k_pool, (float*)v_pool,
         inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
-  else if (dtype == DSP_BF16)
+  else
     rope_kv_store_kernel<bf16><<<grid, threads, 0, stream>>>(
         (bf16*)qkv, positions, seq_of_token, page_table, pt_stride, (bf16*)k_pool, (bf16*)v_pool,
         inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
-  else
-    DSP_REQUIRE(false, "dsp_rope_kv_store: unknown dtype %d", dtype);
   DSP_CHECK_LAUNCH("dsp_rope_kv_store");
   return 0;
 }

@@ -1,27 +1,36 @@
-// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for M <= 64 rows, bfloat16 in, 32-bit
+// C[M,N] = op(A)[M,K] * W[N,K]^T (+ bias) (+ residual) for M <= 64 rows, bfloat16 in, 32-bit
 // accumulation: the matrix product of decoding, bound by streaming W once from HBM.
 //
 // Roles are swapped for the tensor cores: W is the 16-row operand of mma.m16n8k16, the few rows
 // of A are its 8-column operand.  Each warp streams 32 rows of W straight from global memory
-// into registers (16-byte loads, eight 32-wide k blocks in flight) and takes A from shared
-// memory, where the CTA stages it in 256-wide k chunks (cp.async, two stages).  The k index
-// inside a 32-wide block is permuted identically for both operands so that every thread's
+// into registers in groups of four 32-wide k blocks (16 loads of 16 bytes per lane), two groups
+// in flight (register double buffer), so that a warp always has 16 KB of W on its way.  The k
+// index inside a 32-wide block is permuted identically for both operands so that every lane's
 // 16-byte load lands in its own fragments without a shuffle.
 //
-// Split-K: grid.y CTAs share the K range of one 128-row block of W; each writes its partial
-// tile to scratch memory, and the last one to arrive (a counter per block) adds the partials in
-// split order, so the result is deterministic, then applies bias and residual and resets the
-// counter.  Calls that overlap in time on the device must not share scratch and counters.
+// A comes from global memory directly for up to 16 rows (it stays in L1/L2), optionally
+// transformed on the way in:
+//   prologue 1: RMSNorm, a = round(gain[k] * round(x * rsqrt(mean(x^2) + eps))), the row
+//               statistics recomputed by every CTA (a few KB of reads);
+//   prologue 2: SwiGLU, a = silu(x[m, k]) * x[m, K + k] with x of row length 2K.
+// For 17..64 rows A is staged through shared memory in 256-wide k chunks (cp.async, two stages).
+//
+// Split-K: the CTAs that share one block of W rows form a thread-block cluster (up to 8); each
+// leaves its partial tile in its own shared memory, and after a cluster barrier every CTA adds a
+// share of the tile over all ranks in rank order (distributed shared memory), so the sum is
+// deterministic and needs no global scratch.  Bias and residual are applied by the adding CTA.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace {
-constexpr int WARPS = 4;
-constexpr int THREADS = WARPS * 32;
-constexpr int ROWS_PER_WARP = 32;
-constexpr int BLOCK_N = WARPS * ROWS_PER_WARP;  // 128 rows of W per CTA
-constexpr int KC = 256;                         // k chunk staged in shared memory
-constexpr int KB_PER_CHUNK = KC / 32;
-constexpr int A_STRIDE = KC * 2 + 64;           // bytes; 16-byte units = 4 mod 8: conflict-free
+constexpr int KC = 256;                // k chunk of the staged path
+constexpr int A_STRIDE = KC * 2 + 64;  // bytes; in 16-byte units = 4 mod 8: conflict-free
+constexpr int MAX_SPLITS = 8;          // portable cluster size
+
+enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -49,25 +58,100 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ uint4 ldg_cached(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
 
-// MT: number of 8-row tiles of A (rows padded to 8 * MT)
-template <int MT, typename TOut>
-__global__ void __launch_bounds__(THREADS)
-gemm_skinny_kernel(const bf16* __restrict__ A, long lda, const bf16* __restrict__ W,
-                   const bf16* __restrict__ bias, const TOut* __restrict__ residual, long ldr,
-                   TOut* __restrict__ C, long ldc, int M, int N, int K, int chunks_per_split,
-                   float* __restrict__ scratch, int* __restrict__ counters) {
+struct Args {
+  const bf16* A;
+  long lda;
+  const bf16* W;
+  const bf16* bias;
+  const void* residual;
+  long ldr;
+  void* C;
+  long ldc;
+  int M, N, K;
+  int groups_per_split;  // k range of one split, in groups of 128
+  const bf16* gain;      // prologue 1
+  float eps;
+};
+
+// eight bfloat16 values of one A fragment piece, transformed by the prologue
+template <int PRO>
+__device__ __forceinline__ uint4 load_a_piece(const Args& a, int row, int k, const float* rstd) {
+  const bool valid = row < a.M && k < a.K;
+  const int rs = valid ? row : 0, ks = valid ? k : 0;
+  uint4 raw = ldg_cached(a.A + (size_t)rs * a.lda + ks);
+  if (PRO == PRO_RMSNORM) {
+    const uint4 graw = ldg_cached(a.gain + ks);
+    const bf16* x = reinterpret_cast<const bf16*>(&raw);
+    const bf16* gn = reinterpret_cast<const bf16*>(&graw);
+    uint4 out;
+    bf16* o = reinterpret_cast<bf16*>(&out);
+    const float r = rstd[rs];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bf16 n = __float2bfloat16(__bfloat162float(x[j]) * r);
+      o[j] = __float2bfloat16(__bfloat162float(gn[j]) * __bfloat162float(n));
+    }
+    raw = out;
+  } else if (PRO == PRO_SWIGLU) {
+    const uint4 uraw = ldg_cached(a.A + (size_t)rs * a.lda + a.K + ks);
+    const bf16* gt = reinterpret_cast<const bf16*>(&raw);
+    const bf16* up = reinterpret_cast<const bf16*>(&uraw);
+    uint4 out;
+    bf16* o = reinterpret_cast<bf16*>(&out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gv = __bfloat162float(gt[j]);
+      o[j] = __float2bfloat16(gv / (1.f + expf(-gv)) * __bfloat162float(up[j]));
+    }
+    raw = out;
+  }
+  if (!valid) raw = make_uint4(0u, 0u, 0u, 0u);
+  return raw;
+}
+
+// MT: 8-row tiles of A.  WARPS: warps per CTA (32 rows of W each).  STAGED: A through shared memory.
+template <int MT, int WARPS, bool STAGED, int PRO, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(const Args a) {
+  constexpr int THREADS = WARPS * 32;
+  constexpr int R = 2 * MT * 4;  // accumulators per thread
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ int s_last;
+  __shared__ float rstd[16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int nb = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
-  const int n_warp = nb * BLOCK_N + warp * ROWS_PER_WARP;
+  const int nb = blockIdx.x;
+  const int splits = gridDim.y;
+  const int split = blockIdx.y;
+  const int n_warp = nb * (WARPS * 32) + warp * 32;
   const int MP = MT * 8;
 
-  const int chunk_begin = split * chunks_per_split;
-  const int total_chunks = (K + KC - 1) / KC;
-  const int chunk_end = min(total_chunks, chunk_begin + chunks_per_split);
+  const int total_groups = (a.K + 127) / 128;
+  const int group_begin = split * a.groups_per_split;
+  const int group_end = min(total_groups, group_begin + a.groups_per_split);
+
+  // rows of W this lane reads (clamped: rows beyond N are computed but never stored)
+  const bf16* wrow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) wrow[i] = a.W + (size_t)min(n_warp + g + 8 * i, a.N - 1) * a.K;
+
+  auto load_w = [&](uint4 (&w)[4][4], int group) {
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+      const int k = group * 128 + kb * 32 + c * 8;
+      const bool valid = k < a.K;
+      const int ks = valid ? k : 0;  // load unconditionally, discard afterwards
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[kb][i] = ldg_stream(wrow[i] + ks);
+      if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[kb][i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
 
   float acc[2][MT][4];
 #pragma unroll
@@ -77,184 +161,230 @@ gemm_skinny_kernel(const bf16* __restrict__ A, long lda, const bf16* __restrict_
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[s][mt][r] = 0.f;
 
-  // rows of W this lane reads (clamped: rows beyond N are computed but never stored)
-  const bf16* wrow[4];
+  uint4 w0[4][4], w1[4][4];
+  if (group_begin < group_end) load_w(w0, group_begin);  // on its way before anything else
+
+  if (PRO == PRO_RMSNORM) {
+    // row statistics over the whole of K, recomputed by every CTA: warp w takes rows w, w+WARPS, ..
+    for (int row = warp; row < a.M; row += WARPS) {
+      float ss = 0.f;
+      for (int k = lane * 8; k < a.K; k += 256) {
+        const uint4 raw = ldg_cached(a.A + (size_t)row * a.lda + k);
+        const bf16* x = reinterpret_cast<const bf16*>(&raw);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int n = min(n_warp + g + 8 * i, N - 1);
-    wrow[i] = W + (size_t)n * K;
+        for (int j = 0; j < 8; ++j) {
+          const float v = __bfloat162float(x[j]);
+          ss += v * v;
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) rstd[row] = rsqrtf(ss / (float)a.K + a.eps);
+    }
+    __syncthreads();
   }
 
   unsigned char* stage[2] = {smem, smem + MP * A_STRIDE};
   auto load_stage = [&](int chunk, int buf) {
     const int k0 = chunk * KC;
-    // MP rows x 32 sixteen-byte pieces
     for (int i = tid; i < MP * 32; i += THREADS) {
       const int row = i >> 5, piece = i & 31;
       const int k = k0 + piece * 8;
-      const bool valid = row < M && k < K;
-      const bf16* src = valid ? A + (size_t)row * lda + k : A;
+      const bool valid = row < a.M && k < a.K;
+      const bf16* src = valid ? a.A + (size_t)row * a.lda + k : a.A;
       cp_async16(stage[buf] + row * A_STRIDE + piece * 16, src, valid);
     }
     cp_async_commit();
   };
 
-  if (chunk_begin < chunk_end) load_stage(chunk_begin, 0);
-  for (int chunk = chunk_begin; chunk < chunk_end; ++chunk) {
-    const int buf = (chunk - chunk_begin) & 1;
-    if (chunk + 1 < chunk_end) {
-      load_stage(chunk + 1, buf ^ 1);
-      cp_async_wait<1>();
+  auto compute = [&](uint4 (&w)[4][4], int group, const unsigned char* xs) {
+    uint4 x[4][MT];
+    if (!STAGED) {
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          x[kb][mt] = load_a_piece<PRO>(a, mt * 8 + g, group * 128 + kb * 32 + c * 8, rstd);
     } else {
-      cp_async_wait<0>();
+      const int piece0 = (group & 1) * 16 + c;  // two groups per 256-wide chunk
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          x[kb][mt] = *reinterpret_cast<const uint4*>(xs + (mt * 8 + g) * A_STRIDE + (piece0 + kb * 4) * 16);
     }
-    __syncthreads();
-    const int k0 = chunk * KC;
-    const unsigned char* xs = stage[buf];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      // four 32-wide k blocks at a time: 16 loads of 16 bytes in flight per lane
-      uint4 w[4][4];
+    for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb) {
-        const int k = k0 + (half * 4 + kb) * 32 + c * 8;
-        const bool valid = k < K;
-        const int ks = valid ? k : 0;  // load unconditionally, discard afterwards
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[kb][i] = ldg_stream(wrow[i] + ks);
-        if (!valid) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) w[kb][i] = make_uint4(0u, 0u, 0u, 0u);
-        }
+      for (int mt = 0; mt < MT; ++mt) {
+        // strip 0: rows g, g+8; strip 1: rows g+16, g+24
+        mma_bf16(acc[0][mt], w[kb][0].x, w[kb][1].x, w[kb][0].y, w[kb][1].y, x[kb][mt].x, x[kb][mt].y);
+        mma_bf16(acc[0][mt], w[kb][0].z, w[kb][1].z, w[kb][0].w, w[kb][1].w, x[kb][mt].z, x[kb][mt].w);
+        mma_bf16(acc[1][mt], w[kb][2].x, w[kb][3].x, w[kb][2].y, w[kb][3].y, x[kb][mt].x, x[kb][mt].y);
+        mma_bf16(acc[1][mt], w[kb][2].z, w[kb][3].z, w[kb][2].w, w[kb][3].w, x[kb][mt].z, x[kb][mt].w);
       }
-#pragma unroll
-      for (int kb = 0; kb < 4; ++kb) {
-        const int piece = (half * 4 + kb) * 4 + c;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const uint4 x = *reinterpret_cast<const uint4*>(xs + (mt * 8 + g) * A_STRIDE + piece * 16);
-          // strip 0: rows g, g+8; strip 1: rows g+16, g+24
-          mma_bf16(acc[0][mt], w[kb][0].x, w[kb][1].x, w[kb][0].y, w[kb][1].y, x.x, x.y);
-          mma_bf16(acc[0][mt], w[kb][0].z, w[kb][1].z, w[kb][0].w, w[kb][1].w, x.z, x.w);
-          mma_bf16(acc[1][mt], w[kb][2].x, w[kb][3].x, w[kb][2].y, w[kb][3].y, x.x, x.y);
-          mma_bf16(acc[1][mt], w[kb][2].z, w[kb][3].z, w[kb][2].w, w[kb][3].w, x.z, x.w);
-        }
-      }
+  };
+
+  if (!STAGED) {
+    for (int gi = group_begin; gi < group_end; gi += 2) {
+      if (gi + 1 < group_end) load_w(w1, gi + 1);
+      compute(w0, gi, nullptr);
+      if (gi + 2 < group_end) load_w(w0, gi + 2);
+      if (gi + 1 < group_end) compute(w1, gi + 1, nullptr);
     }
-    __syncthreads();
+  } else {
+    // group_begin is even (a split starts on a chunk boundary): chunk = group / 2
+    if (group_begin < group_end) load_stage(group_begin / 2, 0);
+    for (int gi = group_begin; gi < group_end; gi += 2) {
+      const int chunk = gi / 2;
+      const int buf = (chunk - group_begin / 2) & 1;
+      if (gi + 2 < group_end) {
+        load_stage(chunk + 1, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (gi + 1 < group_end) load_w(w1, gi + 1);
+      compute(w0, gi, stage[buf]);
+      if (gi + 2 < group_end) load_w(w0, gi + 2);
+      if (gi + 1 < group_end) compute(w1, gi + 1, stage[buf]);
+      __syncthreads();
+    }
   }
 
-  constexpr int R = 2 * MT * 4;  // accumulators per thread
+  // ---- split-K: add the partial tiles of the cluster through distributed shared memory
+  auto store = [&](int r, float v) {
+    const int s = r / (MT * 4), mt = (r / 4) % MT, e = r & 3;
+    const int n = n_warp + 16 * s + g + 8 * (e >> 1);
+    const int m = 8 * mt + 2 * c + (e & 1);
+    if (n < a.N && m < a.M) {
+      if (a.bias) v += __bfloat162float(a.bias[n]);
+      if (a.residual) v += to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]);
+      reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>(v);
+    }
+  };
   if (splits > 1) {
-    float* mine = scratch + ((size_t)(split * gridDim.x + nb) * R) * THREADS;
+    cg::cluster_group cluster = cg::this_cluster();
+    float* red = reinterpret_cast<float*>(smem);  // [R][THREADS]
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) mine[((s * MT + mt) * 4 + r) * THREADS + tid] = acc[s][mt][r];
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(&counters[nb], 1) == splits - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
+        for (int r = 0; r < 4; ++r) red[((s * MT + mt) * 4 + r) * THREADS + tid] = acc[s][mt][r];
+    cluster.sync();
+    const int rank = (int)cluster.block_rank();
+    for (int r = rank; r < R; r += splits) {
+      float total = 0.f;
+      for (int sp = 0; sp < splits; ++sp) total += cluster.map_shared_rank(red, sp)[r * THREADS + tid];
+      store(r, total);
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+  } else {
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          float total = 0.f;
-          for (int sp = 0; sp < splits; ++sp)
-            total += __ldcg(scratch + ((size_t)(sp * gridDim.x + nb) * R + ((s * MT + mt) * 4 + r)) * THREADS + tid);
-          acc[s][mt][r] = total;
-        }
-    if (tid == 0) counters[nb] = 0;
+        for (int r = 0; r < 4; ++r) store((s * MT + mt) * 4 + r, acc[s][mt][r]);
   }
-
-  // accumulator (s, mt, r): W row n = n_warp + 16 s + g + 8 (r / 2), A row m = 8 mt + 2 c + (r & 1)
-#pragma unroll
-  for (int s = 0; s < 2; ++s)
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int n = n_warp + 16 * s + g + 8 * (r >> 1);
-        const int m = 8 * mt + 2 * c + (r & 1);
-        if (n < N && m < M) {
-          float v = acc[s][mt][r];
-          if (bias) v += __bfloat162float(bias[n]);
-          if (residual) v += to_f32(residual[(size_t)m * ldr + n]);
-          C[(size_t)m * ldc + n] = from_f32<TOut>(v);
-        }
-      }
 }
 
-template <int MT, typename TOut>
-int launch(const void* A, long lda, const void* W, const void* bias, const void* residual, long ldr,
-           void* C, long ldc, int M, int N, int K, int splits, int chunks_per_split, float* scratch,
-           int* counters, cudaStream_t stream) {
-  const size_t smem = 2 * (size_t)(MT * 8) * A_STRIDE;
-  auto kernel = gemm_skinny_kernel<MT, TOut>;
-  DSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
-  kernel<<<grid, THREADS, smem, stream>>>((const bf16*)A, lda, (const bf16*)W, (const bf16*)bias,
-                                          (const TOut*)residual, ldr, (TOut*)C, ldc, M, N, K,
-                                          chunks_per_split, scratch, counters);
-  DSP_CHECK_LAUNCH("dsp_gemm_skinny");
+template <int MT, int WARPS, bool STAGED, int PRO, typename TOut>
+int launch(const Args& a, int splits, cudaStream_t stream) {
+  constexpr int THREADS = WARPS * 32;
+  const size_t stage_bytes = STAGED ? 2 * (size_t)(MT * 8) * A_STRIDE : 0;
+  const size_t red_bytes = splits > 1 ? (size_t)(2 * MT * 4) * THREADS * sizeof(float) : 0;
+  const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+  auto kernel = gemm_skinny_kernel<MT, WARPS, STAGED, PRO, TOut>;
+  static size_t configured = 0;  // per instantiation; not repeated under graph capture
+  if (smem > configured) {
+    DSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + WARPS * 32 - 1) / (WARPS * 32), splits, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = splits;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DSP_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
   return 0;
 }
 
-template <typename TOut>
-int dispatch(const void* A, long lda, const void* W, const void* bias, const void* residual, long ldr,
-             void* C, long ldc, int M, int N, int K, int splits, int cps, float* scratch,
-             int* counters, cudaStream_t stream) {
-  if (M <= 8) return launch<1, TOut>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
-  if (M <= 16) return launch<2, TOut>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
-  if (M <= 32) return launch<4, TOut>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
-  return launch<8, TOut>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
+template <int PRO, typename TOut>
+int dispatch(const Args& a, int splits, bool narrow, cudaStream_t stream) {
+  const int M = a.M;
+  if (M <= 8)
+    return narrow ? launch<1, 2, false, PRO, TOut>(a, splits, stream) : launch<1, 4, false, PRO, TOut>(a, splits, stream);
+  if (M <= 16)
+    return narrow ? launch<2, 2, false, PRO, TOut>(a, splits, stream) : launch<2, 4, false, PRO, TOut>(a, splits, stream);
+  if (PRO != PRO_NONE) {
+    dsp_set_error("dsp_gemm_skinny: a fused prologue takes at most 16 rows, got %d", M);
+    return 2;
+  }
+  if (M <= 32)
+    return narrow ? launch<4, 2, true, PRO_NONE, TOut>(a, splits, stream) : launch<4, 4, true, PRO_NONE, TOut>(a, splits, stream);
+  return narrow ? launch<8, 2, true, PRO_NONE, TOut>(a, splits, stream) : launch<8, 4, true, PRO_NONE, TOut>(a, splits, stream);
 }
 }  // namespace
 
-// Number of K splits the launch below will use (the caller sizes scratch with it).
-extern "C" int dsp_gemm_skinny_splits(int N, int K, int target_ctas) {
-  const int n_blocks = (N + BLOCK_N - 1) / BLOCK_N;
-  const int chunks = (K + KC - 1) / KC;
-  int splits = target_ctas / n_blocks;
-  if (splits < 1) splits = 1;
-  if (splits > chunks) splits = chunks;
-  const int cps = (chunks + splits - 1) / splits;
-  return (chunks + cps - 1) / cps;
-}
-
-// scratch: floats, at least splits * ceil(N/128) * 128 * 8 * ceil8(M) when splits > 1.
-// counters: ceil(N/128) ints, zero before the first call (the kernel leaves them zero).
+// prologue: 0 none; 1 RMSNorm of A's rows with `gain` and `eps` (M <= 16); 2 SwiGLU, A has row
+// length 2K (M <= 16).  target_ctas: CTAs the launch aims for (split-K, at most 8 splits).
 extern "C" int dsp_gemm_skinny(const void* A, long lda, const void* W, const void* bias,
                                const void* residual, long ldr, void* C, long ldc, int M, int N,
-                               int K, int out_dtype, int target_ctas, float* scratch,
-                               long scratch_floats, int* counters, int num_counters,
-                               cudaStream_t stream) {
+                               int K, int out_dtype, int target_ctas, int prologue,
+                               const void* gain, float eps, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   DSP_REQUIRE(M <= 64, "dsp_gemm_skinny: M=%d above 64 rows", M);
   DSP_REQUIRE(K > 0 && K % 8 == 0, "dsp_gemm_skinny: K=%d must be a positive multiple of 8", K);
   DSP_REQUIRE(lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0,
               "dsp_gemm_skinny: operands must be 16-byte aligned with a row stride multiple of 8");
-  const int n_blocks = (N + BLOCK_N - 1) / BLOCK_N;
-  const int chunks = (K + KC - 1) / KC;
-  int splits = dsp_gemm_skinny_splits(N, K, target_ctas);
-  const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-  if (splits > 1) {
-    const long need = (long)splits * n_blocks * THREADS * 8 * mt;
-    if (scratch == nullptr || counters == nullptr || need > scratch_floats || n_blocks > num_counters)
-      splits = 1;  // no room to split: still correct, only slower
+  DSP_REQUIRE(prologue != PRO_RMSNORM || (gain != nullptr && ((uintptr_t)gain % 16) == 0),
+              "dsp_gemm_skinny: the RMSNorm prologue needs a 16-byte aligned gain");
+  Args a;
+  a.A = (const bf16*)A;
+  a.lda = lda;
+  a.W = (const bf16*)W;
+  a.bias = (const bf16*)bias;
+  a.residual = residual;
+  a.ldr = ldr;
+  a.C = C;
+  a.ldc = ldc;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.gain = (const bf16*)gain;
+  a.eps = eps;
+  // narrow CTAs (64 rows of W) when wide ones (128 rows) could not fill the SMs even with all splits
+  const int groups = (K + 127) / 128;
+  const int pairs = (groups + 1) / 2;  // a split covers whole 256-wide chunks
+  const int max_splits = pairs < MAX_SPLITS ? pairs : MAX_SPLITS;
+  const bool narrow = ((N + 127) / 128) * max_splits < 2 * 148;
+  const int n_blocks = narrow ? (N + 63) / 64 : (N + 127) / 128;
+  int splits = target_ctas / n_blocks;
+  if (splits < 1) splits = 1;
+  if (splits > max_splits) splits = max_splits;
+  int pairs_per_split = (pairs + splits - 1) / splits;
+  splits = (pairs + pairs_per_split - 1) / pairs_per_split;
+  a.groups_per_split = pairs_per_split * 2;
+  int rc;
+  if (out_dtype == DSP_BF16) {
+    rc = prologue == PRO_RMSNORM ? dispatch<PRO_RMSNORM, bf16>(a, splits, narrow, stream)
+         : prologue == PRO_SWIGLU ? dispatch<PRO_SWIGLU, bf16>(a, splits, narrow, stream)
+                                  : dispatch<PRO_NONE, bf16>(a, splits, narrow, stream);
+  } else if (out_dtype == DSP_F32) {
+    rc = prologue == PRO_RMSNORM ? dispatch<PRO_RMSNORM, float>(a, splits, narrow, stream)
+         : prologue == PRO_SWIGLU ? dispatch<PRO_SWIGLU, float>(a, splits, narrow, stream)
+                                  : dispatch<PRO_NONE, float>(a, splits, narrow, stream);
+  } else {
+    DSP_REQUIRE(false, "dsp_gemm_skinny: unknown output dtype %d", out_dtype);
   }
-  const int cps = (chunks + splits - 1) / splits;
-  splits = (chunks + cps - 1) / cps;
-  DSP_REQUIRE(splits <= 65535, "dsp_gemm_skinny: too many splits");
-  if (out_dtype == DSP_BF16)
-    return dispatch<bf16>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
-  if (out_dtype == DSP_F32)
-    return dispatch<float>(A, lda, W, bias, residual, ldr, C, ldc, M, N, K, splits, cps, scratch, counters, stream);
-  DSP_REQUIRE(false, "dsp_gemm_skinny: unknown output dtype %d", out_dtype);
+  return rc;
 }

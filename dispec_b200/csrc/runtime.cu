@@ -18,9 +18,16 @@ extern "C" const char* dsp_last_error() { return g_error; }
 __device__ int g_dsp_device_error = 0;
 
 int* dsp_device_error_ptr() {
-  int* p = nullptr;
-  if (cudaGetSymbolAddress((void**)&p, g_dsp_device_error) != cudaSuccess) return nullptr;
-  return p;
+  // looked up once per device (the lookup is not repeated under graph capture)
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_dsp_device_error) != cudaSuccess) return nullptr;
+    cached[dev] = p;
+  }
+  return cached[dev];
 }
 
 // Reads and clears the device error word (synchronises the device).

@@ -53,6 +53,47 @@ argmax_kernel(const float* __restrict__ logits, long stride, int V, int* __restr
   if (threadIdx.x == 0) out[r] = idx;
 }
 
+// Two-stage form for large vocabularies: grid (rows, chunks); each block reduces one chunk of a
+// row to (value, index), a second small kernel reduces the chunks in index order.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, long stride, int V, int chunk,
+                      float* __restrict__ part_val, int* __restrict__ part_idx) {
+  __shared__ ArgMax scratch[32];
+  const int r = blockIdx.x, c = blockIdx.y;
+  const int begin = c * chunk, end = min(V, begin + chunk);
+  const float* x = logits + (size_t)r * stride;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, ArgMax{x[i], i});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) scratch[warp] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ArgMax total = scratch[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) total = better(total, scratch[w]);
+    part_val[(size_t)r * gridDim.y + c] = total.v;
+    part_idx[(size_t)r * gridDim.y + c] = total.i;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int chunks, int* __restrict__ out) {
+  const int r = blockIdx.x;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int c = threadIdx.x; c < chunks; c += 32)
+    best = better(best, ArgMax{part_val[(size_t)r * chunks + c], part_idx[(size_t)r * chunks + c]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
 // inclusive scan over the block in thread order; returns this thread's inclusive value and
 // the block total through *total.  scratch: 32 entries.
 template <typename V>
@@ -271,11 +312,19 @@ sample_kernel(const float* __restrict__ logits, long stride, int V,
 }
 }  // namespace
 
-extern "C" int dsp_argmax(const float* logits, long stride, int n, int V, int* out,
-                          cudaStream_t stream) {
+// chunks > 1 with scratch for n * chunks (value, index) pairs selects the two-stage form.
+extern "C" int dsp_argmax(const float* logits, long stride, int n, int V, int* out, int chunks,
+                          float* part_val, int* part_idx, cudaStream_t stream) {
   if (n == 0) return 0;
   DSP_REQUIRE(V > 0, "dsp_argmax: V=%d", V);
-  argmax_kernel<<<n, THREADS, 0, stream>>>(logits, stride, V, out);
+  if (chunks > 1 && part_val != nullptr && part_idx != nullptr) {
+    DSP_REQUIRE(chunks <= 65535, "dsp_argmax: too many chunks");
+    const int chunk = (V + chunks - 1) / chunks;
+    argmax_partial_kernel<<<dim3(n, chunks), 256, 0, stream>>>(logits, stride, V, chunk, part_val, part_idx);
+    argmax_final_kernel<<<n, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+  } else {
+    argmax_kernel<<<n, THREADS, 0, stream>>>(logits, stride, V, out);
+  }
   DSP_CHECK_LAUNCH("dsp_argmax");
   return 0;
 }

@@ -62,6 +62,7 @@ class StepContext:
         self.ctx_len = None  # [S] int32: stored length after this step
         self.state_slot = None  # [S] int32
         self.logit_rows = None  # [n] int32
+        self.logit_rows_are_all = False  # the wanted rows are 0..T-1 in order
         self.page_tables: list = []  # per cache group [S, max_pages] int32
         self.host_q_len: list = []
         self.host_q_start: list = []
@@ -97,6 +98,7 @@ class HostStaging:
         self._events = []
         self._dev = None
         self._turn = 0
+        self.last_bytes = 0  # bytes of the latest host-to-device copy
         self._grow(capacity)
 
     def _grow(self, n: int) -> None:
@@ -106,9 +108,10 @@ class HostStaging:
         self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.capacity = cap
 
-    def upload(self, n: int, fill) -> torch.Tensor:
+    def upload(self, n: int, fill, into: torch.Tensor | None = None) -> torch.Tensor:
         """``fill(numpy int32 array of length n)`` writes the step's integers; returns the
-        device copy (valid until the next upload)."""
+        device copy (valid until the next upload).  ``into``: a device buffer of fixed address
+        to copy to instead (a captured graph reads it)."""
         if n > self.capacity:
             self._grow(n)
         self._turn ^= 1
@@ -117,8 +120,9 @@ class HostStaging:
             ev.synchronize()
         host = self._host[self._turn]
         fill(host.numpy()[:n])
-        dev = self._dev[:n]
+        dev = self._dev[:n] if into is None else into[:n]
         dev.copy_(host[:n], non_blocking=True)
+        self.last_bytes = 4 * n
         ev = torch.cuda.Event()
         ev.record()
         self._events[self._turn] = ev
@@ -157,99 +161,129 @@ def plan_layout(T: int, S: int, n_rows: int, pages_per_group: list, tiles: dict)
     return layout, off
 
 
-def build_context(entries: list, cache, storage, states, staging: HostStaging, dtype, device,
-                  tile_tokens: list, vocab_size: int) -> tuple[StepContext, list]:
-    """Returns the context and, for each original entry, the index of its first wanted row in
-    the logits the step returns (logit rows follow the original order of entries and wants)."""
-    order = order_entries(entries)
-    sorted_entries = [entries[i] for i in order]
-    S = len(sorted_entries)
-    q_lens = [len(e.tokens) for e in sorted_entries]
-    T = sum(q_lens)
-    ctx_lens = [e.start + len(e.tokens) for e in sorted_entries]
-    n_decode = sum(1 for q in q_lens if q == 1)
-    q_start = np.zeros(S + 1, dtype=np.int64)
-    np.cumsum(q_lens, out=q_start[1:])
+class StepPlanLayout:
+    """Sizes, offsets and host-side values of one step's integer arrays."""
 
-    # logit rows in the original order of the entries
-    first_row = {}
-    for s, e in enumerate(sorted_entries):
-        first_row[id(e)] = int(q_start[s])
-    rows = []
-    row_offsets = []
-    for e in entries:
-        row_offsets.append(len(rows))
-        for w in e.want:
-            if not 0 <= w < len(e.tokens):
-                raise ValueError(f"request {e.req_id!r}: wanted place {w} outside its {len(e.tokens)} tokens")
-            rows.append(first_row[id(e)] + w)
+    def __init__(self, entries: list, cache, tile_tokens: list, vocab_size: int,
+                 pad_seqs: int | None = None, fixed_pages: list | None = None):
+        order = order_entries(entries)
+        self.sorted_entries = [entries[i] for i in order]
+        real = len(self.sorted_entries)
+        q_lens = [len(e.tokens) for e in self.sorted_entries]
+        ctx_lens = [e.start + len(e.tokens) for e in self.sorted_entries]
+        self.num_real_seqs = real
+        self.num_decode = sum(1 for q in q_lens if q == 1)
+        if pad_seqs is not None:
+            # fixed-shape batch of single tokens: padding rows have position -1 and length 0
+            if self.num_decode != real or real > pad_seqs:
+                raise ValueError("a padded batch holds single-token entries only, at most pad_seqs")
+            q_lens = q_lens + [1] * (pad_seqs - real)
+            ctx_lens = ctx_lens + [0] * (pad_seqs - real)
+        self.q_lens, self.ctx_lens = q_lens, ctx_lens
+        S = len(q_lens)
+        self.S, self.T = S, sum(q_lens)
+        self.q_start = np.zeros(S + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=self.q_start[1:])
+        first_row = {id(e): int(self.q_start[s]) for s, e in enumerate(self.sorted_entries)}
+        self.rows, self.row_offsets = [], []
+        for e in entries:
+            self.row_offsets.append(len(self.rows))
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"request {e.req_id!r}: wanted place {w} outside its "
+                                     f"{len(e.tokens)} tokens")
+                self.rows.append(first_row[id(e)] + w)
+        if pad_seqs is not None:
+            self.rows = list(range(S))  # every row, real ones first
+        self.cache = cache
+        self.vocab_size = vocab_size
+        ng = len(cache.groups)
+        if fixed_pages is not None:
+            self.pages_per_group = list(fixed_pages)
+        else:
+            self.pages_per_group = [
+                max([len(cache.block_table(e.req_id, g)) for e in self.sorted_entries] + [1])
+                for g in range(ng)]
+        self.tile_lists = {}
+        for tpt in tile_tokens:
+            ts, t0 = [], []
+            for s, q in enumerate(q_lens):
+                for a in range(0, q, tpt):
+                    ts.append(s)
+                    t0.append(a)
+            self.tile_lists[tpt] = (ts, t0)
+        self.layout, self.total = plan_layout(self.T, S, len(self.rows), self.pages_per_group,
+                                              {t: len(v[0]) for t, v in self.tile_lists.items()})
 
-    ng = len(cache.groups)
-    pages_per_group = []
-    for g in range(ng):
-        mp = max(len(cache.block_table(e.req_id, g)) for e in sorted_entries)
-        pages_per_group.append(max(mp, 1))
-    tiles = {}
-    tile_lists = {}
-    for tpt in tile_tokens:
-        ts, t0 = [], []
-        for s, q in enumerate(q_lens):
-            for a in range(0, q, tpt):
-                ts.append(s)
-                t0.append(a)
-        tile_lists[tpt] = (ts, t0)
-        tiles[tpt] = len(ts)
-    layout, total = plan_layout(T, S, len(rows), pages_per_group, tiles)
+    def fill(self, buf: np.ndarray) -> None:
+        layout, cache = self.layout, self.cache
 
-    def fill(buf: np.ndarray) -> None:
         def view(name):
             o, n = layout[name]
             return buf[o:o + n]
 
-        tok = view("token_ids")
-        pos = view("positions")
-        sot = view("seq_of_token")
-        for s, e in enumerate(sorted_entries):
-            a, b = int(q_start[s]), int(q_start[s + 1])
+        tok, pos, sot = view("token_ids"), view("positions"), view("seq_of_token")
+        tok[:] = 0
+        pos[:] = -1
+        sot[:] = np.repeat(np.arange(self.S), self.q_lens)
+        for s, e in enumerate(self.sorted_entries):
+            a, b = int(self.q_start[s]), int(self.q_start[s + 1])
             tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
             pos[a:b] = np.arange(e.start, e.start + (b - a))
-            sot[a:b] = s
-        if T and (int(tok.min()) < 0 or int(tok.max()) >= vocab_size):
-            raise ValueError(f"token id outside [0, {vocab_size})")
-        view("q_start")[:] = q_start
-        view("ctx_len")[:] = ctx_lens
-        view("state_slot")[:] = [cache.state_slot(e.req_id) for e in sorted_entries]
-        view("logit_rows")[:] = rows
-        for g in range(ng):
-            mp = pages_per_group[g]
-            pt = view(f"page_table{g}").reshape(S, mp)
+        if self.T and (int(tok.min()) < 0 or int(tok.max()) >= self.vocab_size):
+            raise ValueError(f"token id outside [0, {self.vocab_size})")
+        view("q_start")[:] = self.q_start
+        view("ctx_len")[:] = self.ctx_lens
+        slots = view("state_slot")
+        slots[:] = 0
+        slots[:self.num_real_seqs] = [cache.state_slot(e.req_id) for e in self.sorted_entries]
+        view("logit_rows")[:] = self.rows
+        for g, mp in enumerate(self.pages_per_group):
+            pt = view(f"page_table{g}").reshape(self.S, mp)
             pt[:] = -1
-            for s, e in enumerate(sorted_entries):
+            for s, e in enumerate(self.sorted_entries):
                 table = cache.block_table(e.req_id, g)
+                if len(table) > mp:
+                    raise ValueError(f"request {e.req_id!r} holds {len(table)} pages, the batch has "
+                                     f"room for {mp}")
                 pt[s, :len(table)] = table
-        for tpt, (ts, t0) in tile_lists.items():
+        for tpt, (ts, t0) in self.tile_lists.items():
             view(f"tile_seq{tpt}")[:] = ts
             view(f"tile_tok0{tpt}")[:] = t0
 
-    dev = staging.upload(total, fill)
+    def context(self, dev: torch.Tensor, storage, states, dtype, device) -> "StepContext":
+        layout = self.layout
 
-    def dview(name):
-        o, n = layout[name]
-        return dev[o:o + n]
+        def dview(name):
+            o, n = layout[name]
+            return dev[o:o + n]
 
-    ctx = StepContext()
-    ctx.dtype, ctx.device = dtype, device
-    ctx.num_tokens, ctx.num_seqs, ctx.num_decode_seqs = T, S, n_decode
-    ctx.token_ids, ctx.positions, ctx.seq_of_token = dview("token_ids"), dview("positions"), dview("seq_of_token")
-    ctx.q_start, ctx.ctx_len, ctx.state_slot = dview("q_start"), dview("ctx_len"), dview("state_slot")
-    ctx.logit_rows = dview("logit_rows")
-    ctx.page_tables = [dview(f"page_table{g}").view(S, pages_per_group[g]) for g in range(ng)]
-    ctx.host_q_len, ctx.host_ctx_len = q_lens, ctx_lens
-    ctx.host_q_start = [int(v) for v in q_start]
-    ctx.host_state_slot = [cache.state_slot(e.req_id) for e in sorted_entries]
-    ctx.max_ctx_len = max(ctx_lens) if ctx_lens else 0
-    for tpt in tile_tokens:
-        ctx.attention_tiles[tpt] = (dview(f"tile_seq{tpt}"), dview(f"tile_tok0{tpt}"), tiles[tpt])
-    ctx.storage, ctx.states = storage, states
-    ctx.cache_groups, ctx.page_size = cache.groups, cache.page_size
-    return ctx, row_offsets
+        ctx = StepContext()
+        ctx.dtype, ctx.device = dtype, device
+        ctx.num_tokens, ctx.num_seqs = self.T, self.S
+        ctx.num_decode_seqs = self.S if len(self.q_lens) > self.num_real_seqs else self.num_decode
+        ctx.token_ids, ctx.positions = dview("token_ids"), dview("positions")
+        ctx.seq_of_token = dview("seq_of_token")
+        ctx.q_start, ctx.ctx_len, ctx.state_slot = dview("q_start"), dview("ctx_len"), dview("state_slot")
+        ctx.logit_rows = dview("logit_rows")
+        ctx.logit_rows_are_all = self.rows == list(range(self.T))
+        ctx.page_tables = [dview(f"page_table{g}").view(self.S, mp)
+                           for g, mp in enumerate(self.pages_per_group)]
+        ctx.host_q_len, ctx.host_ctx_len = self.q_lens, self.ctx_lens
+        ctx.host_q_start = [int(v) for v in self.q_start]
+        ctx.host_state_slot = [self.cache.state_slot(e.req_id) for e in self.sorted_entries]
+        ctx.max_ctx_len = max(self.ctx_lens) if self.ctx_lens else 0
+        for tpt, (ts, _) in self.tile_lists.items():
+            ctx.attention_tiles[tpt] = (dview(f"tile_seq{tpt}"), dview(f"tile_tok0{tpt}"), len(ts))
+        ctx.storage, ctx.states = storage, states
+        ctx.cache_groups, ctx.page_size = self.cache.groups, self.cache.page_size
+        return ctx
+
+
+def build_context(entries: list, cache, storage, states, staging: HostStaging, dtype, device,
+                  tile_tokens: list, vocab_size: int) -> tuple[StepContext, list]:
+    """Returns the context and, for each original entry, the index of its first wanted row in
+    the logits the step returns (logit rows follow the original order of entries and wants)."""
+    plan = StepPlanLayout(entries, cache, tile_tokens, vocab_size)
+    dev = staging.upload(plan.total, plan.fill)
+    return plan.context(dev, storage, states, dtype, device), plan.row_offsets

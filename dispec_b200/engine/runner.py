@@ -15,7 +15,8 @@ import torch
 from dispec_b200 import ops
 from dispec_b200.cache.manager import CacheManager
 from dispec_b200.cache.storage import CacheStorage, StateStorage
-from dispec_b200.engine.batch import HostStaging, SeqEntry, build_context
+from dispec_b200.engine.batch import HostStaging, SeqEntry, StepPlanLayout, build_context
+from dispec_b200.ops import library as _library
 from dispec_b200.models.model import DecoderModel
 
 
@@ -37,7 +38,15 @@ class ModelRunner:
         self.poison = poison  # tests: pages given back are filled with NaN
         self.vocab_size = model.spec.vocab_size
         self.num_steps = 0
-        self.cuda_graph = bool(cuda_graph) and self.dtype == torch.bfloat16
+        self.cuda_graph = (bool(cuda_graph) and self.dtype == torch.bfloat16
+                           and all(getattr(p, "graph_safe", True) for p in model._parts))
+        # captured decode steps, one per padded batch size; the page tables of a captured step
+        # have room for the longest sequence the pools or the model allow
+        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_num_seqs]
+        limit = model.spec.max_position or (1 << 30)
+        self.max_model_len = min(limit, self.cache.capacity_tokens())
+        self._graph_pages = [max(1, min(c, -(-self.max_model_len // page_size))) for c in counts]
+        self._graphs: dict = {}
 
     # ---------------------------------------------------------------- request lifecycle
     def admit(self, req_id, prompt_len: int = 0, max_total_len: int = 0, max_chunk: int = 1) -> None:
@@ -75,6 +84,9 @@ class ModelRunner:
                                  f"{stored} tokens are stored")
         for e in entries:  # may raise OutOfPagesError before anything ran
             self.cache.extend(e.req_id, e.start + len(e.tokens))
+        if (self.cuda_graph and self.graph_buckets and len(entries) <= self.graph_buckets[-1]
+                and all(len(e.tokens) == 1 for e in entries)):
+            return self._graph_step(entries)
         ctx, _ = build_context(entries, self.cache, self.storage, self.states, self.staging,
                                self.dtype, self.device, self.model.attention_tile_tokens,
                                self.vocab_size)
@@ -87,6 +99,59 @@ class ModelRunner:
         for e in entries:
             self._poison(self.cache.commit(e.req_id, e.start + len(e.tokens)))
         self.num_steps += 1
+        return logits
+
+    # -------------------------------------------------------- captured all-decode steps
+    def _capture(self, bucket: int) -> dict:
+        """Captures one decode step of ``bucket`` single-token rows as a CUDA graph.  Every
+        integer input lives in one device buffer of fixed address and layout; a replay copies
+        the step's values there first.  Rows beyond the live requests carry position -1 and
+        length 0, which the kernels skip."""
+        plan = StepPlanLayout([], self.cache, self.model.attention_tile_tokens, self.vocab_size,
+                              pad_seqs=bucket, fixed_pages=self._graph_pages)
+        buffer = torch.empty(plan.total, dtype=torch.int32, device=self.device)
+        self.staging.upload(plan.total, plan.fill, into=buffer)
+        ctx = plan.context(buffer, self.storage, self.states, self.dtype, self.device)
+        ctx.max_ctx_len = self.max_model_len  # choices made on the host must not vary per step
+        ctx.graph_capture = True
+
+        def run():
+            x, pending = self.model.forward(ctx)
+            return self.model.logits(ctx, x, pending, ctx.logit_rows)
+
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = _library.LaunchCounter.n
+        with torch.cuda.graph(graph):
+            logits = run()
+        entry = dict(graph=graph, buffer=buffer, total=plan.total, logits=logits,
+                     launches=_library.LaunchCounter.n - before)
+        self._graphs[bucket] = entry
+        return entry
+
+    def _graph_step(self, entries: list) -> torch.Tensor:
+        bucket = next(b for b in self.graph_buckets if b >= len(entries))
+        g = self._graphs.get(bucket) or self._capture(bucket)
+        plan = StepPlanLayout(entries, self.cache, self.model.attention_tile_tokens, self.vocab_size,
+                              pad_seqs=bucket, fixed_pages=self._graph_pages)
+        assert plan.total == g["total"]
+        self.staging.upload(plan.total, plan.fill, into=g["buffer"])
+        g["graph"].replay()
+        _library.LaunchCounter.n += g["launches"]
+        for e in entries:
+            self._poison(self.cache.commit(e.req_id, e.start + len(e.tokens)))
+        self.num_steps += 1
+        # rows of the padded batch follow the sorted (= given) order of the single-token entries
+        wanted = [i for i, e in enumerate(entries) if e.want]
+        logits = g["logits"][:len(entries)]
+        if len(wanted) != len(entries):
+            logits = logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
         return logits
 
     def check_device(self, where: str = "step") -> None:

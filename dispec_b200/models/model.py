@@ -141,6 +141,11 @@ class DecoderModel:
 
     def logits(self, ctx, x, pending, rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits at the given flat token rows (int32 device tensor)."""
+        if (pending is None and ctx.logit_rows_are_all and hasattr(self.head, "forward_normed")
+                and hasattr(self.final_norm, "as_linear_prologue")):
+            out = self.head.forward_normed(ctx, x, self.final_norm)
+            if out is not None:
+                return out
         if pending is None:
             h = self.final_norm.forward(ctx, x, rows=rows)
         else:

@@ -101,6 +101,7 @@ def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_
             tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml),
             H, KVH, tpt, page_size, num_pages, window, splits, L.f32(scale),
             ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
+    L.LaunchCounter.n += 1
     if rc != 0:
         raise L.KernelError(f"dsp_attn_mma_d{D}: {_MMA_ERRORS.get(rc, rc)}")
 

@@ -15,10 +15,7 @@ import torch
 from dispec_b200.ops import library as L
 
 SKINNY_MAX_ROWS = 64  # rows the weight-streaming kernel takes
-SKINNY_TARGET_CTAS = 148 * 4  # CTAs a weight-streaming launch aims for (split-K fills the SMs)
-_WORKSPACE_FLOATS = 8 << 20  # 32 MB of split-K partials
-_NUM_COUNTERS = 4096
-_workspaces: dict = {}
+SKINNY_TARGET_CTAS = 148 * 3  # CTAs a weight-streaming launch aims for (split-K fills the SMs)
 LARGE_BACKEND = "library"  # "library" | "simt"
 
 
@@ -32,32 +29,50 @@ def _simt(x, w, bias, residual, out):
     return out
 
 
-def workspace(device):
-    """Scratch for split-K partials and the per-block arrival counters (zero between calls),
-    one pair per device.  Launches that overlap on the device must not share it; the engine
-    runs on one stream."""
-    key = torch.device(device).index or 0
-    if key not in _workspaces:
-        _workspaces[key] = (torch.empty(_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
-                            torch.zeros(_NUM_COUNTERS, dtype=torch.int32, device=device))
-    return _workspaces[key]
+PRO_NONE, PRO_RMSNORM, PRO_SWIGLU = 0, 1, 2
+FUSED_MAX_ROWS = 16  # rows up to which the weight-streaming kernel can fuse a prologue
 
 
-def _skinny(x, w, bias, residual, out, target_ctas=None):
-    M, K = x.shape
-    N = w.shape[0]
-    scratch, counters = workspace(x.device)
+def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain=None, eps=0.0):
+    M = x.shape[0]
+    N, K = w.shape
     L.check(L.core().dsp_gemm_skinny(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
         M, N, K, L.dtype_code(out.dtype), SKINNY_TARGET_CTAS if target_ctas is None else target_ctas,
-        L.ptr(scratch), L.i64(scratch.numel()), L.ptr(counters), counters.numel(), L.stream_handle()))
+        prologue, L.ptr(gain), L.f32(eps), L.stream_handle()))
     return out
 
 
 def skinny_supported(M: int, N: int, K: int, x: torch.Tensor, w: torch.Tensor) -> bool:
     return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def fused_prologue_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``linear_rms_norm`` / ``linear_swiglu`` may be used for these operands."""
+    M = x.shape[0]
+    return (x.dtype == torch.bfloat16 and 0 < M <= FUSED_MAX_ROWS and w.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0)
+
+
+def linear_rms_norm(x, gain, eps, w, bias=None, residual=None, out_dtype=None, out=None):
+    """linear(rms_norm(x, gain, eps), w, ...) in one kernel (bfloat16, at most 16 rows)."""
+    assert fused_prologue_supported(x, w) and x.shape[1] == w.shape[1]
+    assert gain.dtype == x.dtype and gain.shape == (x.shape[1],) and gain.is_contiguous()
+    out_dtype = out_dtype or (out.dtype if out is not None else x.dtype)
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    return _skinny(x, w, bias, residual, out, prologue=PRO_RMSNORM, gain=gain, eps=eps)
+
+
+def linear_swiglu(gate_up, w, bias=None, residual=None, out_dtype=None, out=None):
+    """linear(swiglu(gate_up), w, ...) in one kernel; gate_up is [M, 2K] (bfloat16, M <= 16)."""
+    assert gate_up.shape[1] == 2 * w.shape[1] and fused_prologue_supported(gate_up, w)
+    out_dtype = out_dtype or (out.dtype if out is not None else gate_up.dtype)
+    if out is None:
+        out = torch.empty((gate_up.shape[0], w.shape[0]), dtype=out_dtype, device=gate_up.device)
+    return _skinny(gate_up, w, bias, residual, out, prologue=PRO_SWIGLU)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,

@@ -56,7 +56,13 @@ def loaded_libraries() -> list[str]:
     return out + [lib._name for lib in _special.values()]
 
 
-def check(rc: int, lib: ctypes.CDLL | None = None) -> None:
+class LaunchCounter:
+    """Counts kernels of this package launched (or replayed from a captured graph)."""
+    n = 0
+
+
+def check(rc: int, lib: ctypes.CDLL | None = None, launches: int = 1) -> None:
+    LaunchCounter.n += launches
     if rc != 0:
         msg = core().dsp_last_error()
         raise KernelError(msg.decode() if msg else f"kernel library returned {rc}")

@@ -13,7 +13,16 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     n, v = logits.shape
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
-    L.check(L.core().dsp_argmax(L.ptr(logits), L.i64(logits.stride(0)), n, v, L.ptr(out), L.stream_handle()))
+    # a large vocabulary is cut into chunks so that a few rows still fill the SMs
+    chunks = 1 if v < 16384 else max(1, min(v // 4096, 64))
+    if chunks > 1:
+        part_val = torch.empty((n, chunks), dtype=torch.float32, device=logits.device)
+        part_idx = torch.empty((n, chunks), dtype=torch.int32, device=logits.device)
+    else:
+        part_val = part_idx = None
+    L.check(L.core().dsp_argmax(L.ptr(logits), L.i64(logits.stride(0)), n, v, L.ptr(out), chunks,
+                                L.ptr(part_val), L.ptr(part_idx), L.stream_handle()),
+            launches=2 if chunks > 1 else 1)
     return out
 
 

@@ -13,6 +13,7 @@ import torch
 
 from dispec_b200 import ops
 from dispec_b200.ops import attention as attn_ops
+from dispec_b200.ops import gemm as gemm_ops
 from dispec_b200.parts.base import KVNeed, Mixer, TensorSpec
 from dispec_b200.registry import register_part
 
@@ -66,9 +67,17 @@ class GQAAttention(Mixer):
     def tokens_per_attention_tile(self):
         return attn_ops.tokens_per_tile(self.num_heads // self.num_kv_heads)
 
-    def forward(self, ctx, x, cache, state):
+    fuses_norm_and_residual = True
+
+    def forward(self, ctx, x, cache, state, pre_norm=None, residual=None):
+        """``pre_norm``: x is not normalised yet and this norm is applied on the way into the first
+        product.  ``residual``: added by the last product, so that the sum comes back."""
         H, KVH, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        if pre_norm is not None:
+            gain, eps = pre_norm.as_linear_prologue()
+            qkv = gemm_ops.linear_rms_norm(x, gain, eps, self.w_qkv, self.b_qkv)
+        else:
+            qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         pe = self.position_encoding
         ops.rope_kv_store(qkv, ctx.positions, ctx.seq_of_token, cache.page_table,
                           cache.key_pool if cache.write else None,
@@ -77,4 +86,4 @@ class GQAAttention(Mixer):
         out = torch.empty((x.shape[0], H * D), dtype=x.dtype, device=x.device)
         attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
                                  self.scale)
-        return ops.linear(out, self.w_o, self.b_o)
+        return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual)

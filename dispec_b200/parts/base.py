@@ -72,6 +72,9 @@ class StateNeed:
 class Part:
     role = ""
     kind = ""
+    # False for a part whose forward decides things on the host from the step's values (such a
+    # part cannot be replayed from a captured graph; the runner then runs every step eagerly)
+    graph_safe = True
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}

@@ -20,7 +20,21 @@ class PreNormBlock(Block):
         self.ffn_norm = ffn_norm
         self.feed_forward = feed_forward
 
+    def _fusable(self, x) -> bool:
+        """Few rows of bfloat16 and parts that can take a norm on their way in and a residual on
+        their way out: the block then runs without a norm or an add kernel of its own."""
+        from dispec_b200.ops import gemm
+        return (gemm.fused_prologue_supported(x, x)
+                and getattr(self.mixer, "fuses_norm_and_residual", False)
+                and getattr(self.feed_forward, "fuses_norm_and_residual", False)
+                and hasattr(self.mixer_norm, "as_linear_prologue")
+                and hasattr(self.ffn_norm, "as_linear_prologue"))
+
     def forward(self, ctx, x, pending, cache, state):
+        if pending is None and self._fusable(x):
+            x = self.mixer.forward(ctx, x, cache, state, pre_norm=self.mixer_norm, residual=x)
+            x = self.feed_forward.forward(ctx, x, pre_norm=self.ffn_norm, residual=x)
+            return x, None
         if pending is None:
             h = self.mixer_norm.forward(ctx, x)
         else:

@@ -41,6 +41,55 @@ def random_tensors(config, seed: int, std: float, dtype: str = "bfloat16",
     return out
 
 
+class RandomSource:
+    """A tensor source that draws each tensor when it is asked for (same values as
+    ``random_tensors``: one generator, checkpoint-name order), so that a large model reaches
+    the device without a file in between."""
+
+    def __init__(self, config, seed: int, std: float, dtype: str = "bfloat16",
+                 overrides: dict | None = None):
+        self._req = build_model(config).tensor_requirements()
+        self._gen = torch.Generator().manual_seed(seed)
+        self._std, self._store, self._overrides = std, _STORE[dtype], overrides or {}
+        self._order = list(self._req)
+        self._next = 0
+
+    def names(self):
+        return list(self._req)
+
+    def shape(self, name):
+        return tuple(self._req[name].shape)
+
+    def dtype(self, name):
+        spec = self._req[name]
+        return torch.int32 if spec.dtype == "int32" else (torch.float32 if spec.dtype == "float32" else self._store)
+
+    def get(self, name):
+        if self._order[self._next] != name:
+            raise RuntimeError("RandomSource hands tensors out once, in checkpoint-name order")
+        self._next += 1
+        spec = self._req[name]
+        if spec.dtype == "int32":
+            return torch.zeros(spec.shape, dtype=torch.int32)
+        if spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=torch.float32)
+        else:
+            t = torch.randn(spec.shape, generator=self._gen, dtype=torch.float32) * self._overrides.get(name, self._std)
+            if spec.init == "one_plus_normal":
+                t = t + 1.0
+        return t.to(self.dtype(name))
+
+
+def load_random_model(config, seed: int, std: float = 0.02, dtype="bfloat16", device="cuda:0",
+                      overrides: dict | None = None):
+    """A model with random weights on the device, equal to writing the folder with
+    ``write_random_model`` (stored as bfloat16) and loading it."""
+    from dispec_b200.weights.loader import load_into
+    model = build_model(config)
+    return load_into(model, RandomSource(config, seed, std, "bfloat16", overrides), dtype, device,
+                     where="random weights")
+
+
 def write_random_model(config, folder: str, seed: int, std: float = 0.02, dtype: str = "bfloat16",
                        overrides: dict | None = None) -> str:
     os.makedirs(folder, exist_ok=True)

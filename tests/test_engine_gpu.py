@@ -174,3 +174,39 @@ def test_step_refuses_bad_input(folders):
     with pytest.raises(OutOfPagesError):
         runner.step([SeqEntry("s", list(range(40)), 0, [])])
     assert runner.step([SeqEntry("s", [1, 2, 3], 0, [])]).shape == (0, config["vocab_size"])
+
+
+def test_captured_decode_steps_match_eager_steps(folders):
+    """All-decode steps replayed from a captured graph (padded to 1, 2, 4 rows) give the logits of
+    the eager path, while requests come and go."""
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    folder, config, weights = folders["c"]
+    model = load(folder, "bfloat16")
+    prompts = {r: ru.random_ids(n, config["vocab_size"], 600 + n) for r, n in (("x", 37), ("y", 12), ("z", 70))}
+    results = []
+    for graphs in (False, True):
+        runner = ModelRunner(model, page_size=16, num_pages=24, max_num_seqs=4, cuda_graph=graphs, poison=True)
+        rows = []
+        pos = {}
+        for r, p in prompts.items():
+            runner.admit(r)
+            runner.step([SeqEntry(r, p[:-8], 0, [])])
+            pos[r] = len(p) - 8
+        live = ["x", "y", "z"]
+        for i in range(8):
+            if i == 5:
+                runner.release("y")
+                live.remove("y")
+            entries = [SeqEntry(r, [prompts[r][pos[r]]], pos[r], [0]) for r in live]
+            rows.append(runner.step(entries).float().cpu().clone())
+            for r in live:
+                pos[r] += 1
+        if graphs:
+            assert set(runner._graphs) == {2, 4}
+        runner.check_device()
+        results.append(torch.cat(rows))
+    refs = {r: plain.forward_logits(weights, config, p) for r, p in prompts.items()}
+    scale = max(v.abs().max().item() for v in refs.values())
+    assert (results[0] - results[1]).abs().max().item() < 0.03 * scale
+    # and both are right: the first decoded row of x
+    assert (results[1][0] - refs["x"][len(prompts["x"]) - 8]).abs().max().item() < 0.03 * scale + 0.02

@@ -394,3 +394,29 @@ def test_attention_tensor_core_mixed_batch_matches_alone():
                                   D ** -0.5, q_lens=q_lens, ctx_lens=ctx_lens, splits=4)
     got = out.float().cpu().view(-1, H, D).double()
     torch.testing.assert_close(got, torch.cat(refs), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 96), (8, 2048, 1536), (13, 300, 776), (16, 1536, 8960)])
+def test_gemm_weight_streaming_with_fused_norm_and_swiglu(M, N, K):
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm
+    x = rnd((M, K), torch.bfloat16, 31, 2.0)
+    gain = (1 + rnd((K,), torch.float32, 32, 0.1)).to(torch.bfloat16).to(dev())
+    w = rnd((N, K), torch.bfloat16, 33, 0.1)
+    b = rnd((N,), torch.bfloat16, 34)
+    r = rnd((M, N), torch.bfloat16, 35)
+    eps = 1e-5
+    # the fused form against the two kernels it replaces (same rounding points), and against float64
+    normed = ops.rms_norm(x, gain, eps)
+    fused = gemm.linear_rms_norm(x, gain, eps, w, b, residual=r.clone())
+    ref = normed.double() @ w.double().T + b.double() + r.double()
+    torch.testing.assert_close(fused.double(), ref, atol=3e-2, rtol=2e-2)
+    logits = gemm.linear_rms_norm(x, gain, eps, w, out_dtype=torch.float32)
+    torch.testing.assert_close(logits.double(), normed.double() @ w.double().T, atol=3e-3, rtol=3e-3)
+    # SwiGLU on the way in: gate_up is [M, 2K]
+    gu = rnd((M, 2 * K), torch.bfloat16, 36, 1.5)
+    act = ops.swiglu(gu)
+    resid = r.clone()
+    out = gemm.linear_swiglu(gu, w, residual=resid, out=resid)
+    assert out.data_ptr() == resid.data_ptr()  # the residual is updated in place
+    torch.testing.assert_close(out.double(), act.double() @ w.double().T + r.double(), atol=3e-2, rtol=2e-2)
