@@ -7,6 +7,8 @@
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, long out_stride, int H, int D, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;  // t * H + h
   const size_t t = row / H;
   const int h = (int)(row % H);
@@ -37,9 +39,9 @@ extern "C" int dsp_attn_combine(const float* part_o, const float* part_ml, void*
   const int rows = num_tokens * H;
   const int threads = D >= 128 ? 128 : 64;
   if (dtype == DSP_BF16)
-    attn_combine_kernel<bf16><<<rows, threads, 0, stream>>>(part_o, part_ml, (bf16*)out, out_stride, H, D, splits);
+    DSP_CUDA(launch_pdl(attn_combine_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, part_o, part_ml, (bf16*)out, out_stride, H, D, splits));
   else if (dtype == DSP_F32)
-    attn_combine_kernel<float><<<rows, threads, 0, stream>>>(part_o, part_ml, (float*)out, out_stride, H, D, splits);
+    DSP_CUDA(launch_pdl(attn_combine_kernel<float>, dim3(rows), dim3(threads), 0, stream, part_o, part_ml, (float*)out, out_stride, H, D, splits));
   else
     DSP_REQUIRE(false, "dsp_attn_combine: unknown dtype %d", dtype);
   DSP_CHECK_LAUNCH("dsp_attn_combine");

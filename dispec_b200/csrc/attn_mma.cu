@@ -92,6 +92,8 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
   const uint32_t k_s[2] = {s_base + TILE_BYTES, s_base + 2 * TILE_BYTES};
   const uint32_t v_s[2] = {s_base + 3 * TILE_BYTES, s_base + 4 * TILE_BYTES};
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
   const int tile = blockIdx.x + tile_offset, kvh = blockIdx.y, split = blockIdx.z;
@@ -327,6 +329,5 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     configured = true;
   }
   dim3 grid(num_tiles, KVH, num_splits);
-  attn_mma_kernel<<<grid, THREADS, smem, stream>>>(p, tile_offset);
-  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+  return launch_pdl(attn_mma_kernel, grid, dim3(THREADS), (size_t)smem, stream, p, tile_offset) == cudaSuccess ? 0 : 1;
 }

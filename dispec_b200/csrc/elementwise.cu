@@ -8,6 +8,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              T* __restrict__ out, int hidden, int vocab, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   T* dst = out + (size_t)t * hidden;
@@ -33,9 +35,9 @@ extern "C" int dsp_embed(const void* table, const int* ids, void* out, int T, in
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_embed: no device error word");
   if (dtype == DSP_F32)
-    embed_kernel<float><<<T, 128, 0, stream>>>((const float*)table, ids, (float*)out, hidden, vocab, err);
+    DSP_CUDA(launch_pdl(embed_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)table, ids, (float*)out, hidden, vocab, err));
   else if (dtype == DSP_BF16)
-    embed_kernel<bf16><<<T, 128, 0, stream>>>((const bf16*)table, ids, (bf16*)out, hidden, vocab, err);
+    DSP_CUDA(launch_pdl(embed_kernel<bf16>, dim3(T), dim3(128), 0, stream, (const bf16*)table, ids, (bf16*)out, hidden, vocab, err));
   else
     DSP_REQUIRE(false, "dsp_embed: unknown dtype %d", dtype);
   DSP_CHECK_LAUNCH("dsp_embed");
@@ -195,31 +197,40 @@ extern "C" int dsp_rmsnorm(void* x, const void* delta, const void* w, void* y, c
 }
 
 // ------------------------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g)), in 32-bit.
+// out[t, i] = silu(gate(t, i)) * up(t, i), silu(g) = g / (1 + exp(-g)), in 32-bit.
+// block == 0: gu row = [all gates | all ups].  block == b > 0: gates and ups interleaved in blocks
+// of b columns: gate(t, i) at column (i / b) * 2b + i % b, up(t, i) b columns further.
+__device__ __forceinline__ size_t gate_column(int i, int inter, int block) {
+  return block ? (size_t)(i / block) * 2 * block + i % block : (size_t)i;
+}
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block) {
   const size_t t = blockIdx.x;
-  const T* g = gu + t * 2 * (size_t)inter;
-  const T* u = g + inter;
+  const T* row = gu + t * 2 * (size_t)inter;
+  const int up_off = block ? block : inter;
   T* o = out + t * (size_t)inter;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
-    const float gv = to_f32(g[i]);
-    const float uv = to_f32(u[i]);
+    const size_t gc = gate_column(i, inter, block);
+    const float gv = to_f32(row[gc]);
+    const float uv = to_f32(row[gc + up_off]);
     o[i] = from_f32<T>(gv / (1.f + expf(-gv)) * uv);
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs) {
+swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs,
+                  int block) {
   constexpr int N = Vec16<T>::N;
   const int vec_per_row = inter / N;
+  const int up_off = block ? block : inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / vec_per_row;
     const int c = (int)(i % vec_per_row);
-    const uint4 graw = reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter)[c];
-    const uint4 uraw = reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + inter)[c];
+    const T* gp = gu + t * 2 * (size_t)inter + gate_column(c * N, inter, block);
+    const uint4 graw = *reinterpret_cast<const uint4*>(gp);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gp + up_off);
     const T* g = reinterpret_cast<const T*>(&graw);
     const T* u = reinterpret_cast<const T*>(&uraw);
     uint4 oraw;
@@ -233,27 +244,30 @@ swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size
   }
 }
 
-extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int dtype,
+extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int block, int dtype,
                           cudaStream_t stream) {
   if (T == 0) return 0;
+  DSP_REQUIRE(block >= 0 && (block == 0 || inter % block == 0),
+              "dsp_swiglu: interleave block %d does not divide %d", block, inter);
   DSP_REQUIRE(dtype == DSP_F32 || dtype == DSP_BF16, "dsp_swiglu: unknown dtype %d", dtype);
   const int N = dtype == DSP_F32 ? 4 : 8;
-  if (inter % N == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+  if (inter % N == 0 && (block == 0 || block % N == 0) && ((uintptr_t)gate_up % 16) == 0 &&
+      ((uintptr_t)out % 16) == 0) {
     const size_t total = (size_t)T * (inter / N);
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
     if (dtype == DSP_F32)
-      swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+      swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, block);
     else
-      swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+      swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total, block);
     DSP_CHECK_LAUNCH("dsp_swiglu");
     return 0;
   }
   const int chunks = (inter + 255) / 256;
   dim3 grid(T, chunks > 64 ? 64 : chunks);
   if (dtype == DSP_F32)
-    swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+    swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
   else
-    swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+    swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, block);
   DSP_CHECK_LAUNCH("dsp_swiglu");
   return 0;
 }
@@ -330,6 +344,8 @@ rope_kv_store_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
                            int rotary_dim, int page_size, int num_pages, int write_kv, int* err) {
   constexpr int N = Vec16<T>::N;
   extern __shared__ float cs[];  // cos[half], sin[half]
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
@@ -412,13 +428,15 @@ extern "C" int dsp_rope_kv_store(void* qkv, const int* positions, const int* seq
     const size_t smem = (size_t)rotary_dim * sizeof(float);
     const int threads = (H + KVH) * (rotary_dim / 2 / N) >= 256 ? 256 : 128;
     if (dtype == DSP_F32)
-      rope_kv_store_token_kernel<float><<<T, threads, smem, stream>>>(
-          (float*)qkv, positions, seq_of_token, page_table, pt_stride, (float*)k_pool, (float*)v_pool,
-          inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+      DSP_CUDA(launch_pdl(rope_kv_store_token_kernel<float>, dim3(T), dim3(threads), smem, stream,
+                          (float*)qkv, positions, seq_of_token, page_table, pt_stride, (float*)k_pool,
+                          (float*)v_pool, inv_freq, H, KVH, D, rotary_dim, page_size, num_pages,
+                          write_kv, err));
     else
-      rope_kv_store_token_kernel<bf16><<<T, threads, smem, stream>>>(
-          (bf16*)qkv, positions, seq_of_token, page_table, pt_stride, (bf16*)k_pool, (bf16*)v_pool,
-          inv_freq, H, KVH, D, rotary_dim, page_size, num_pages, write_kv, err);
+      DSP_CUDA(launch_pdl(rope_kv_store_token_kernel<bf16>, dim3(T), dim3(threads), smem, stream,
+                          (bf16*)qkv, positions, seq_of_token, page_table, pt_stride, (bf16*)k_pool,
+                          (bf16*)v_pool, inv_freq, H, KVH, D, rotary_dim, page_size, num_pages,
+                          write_kv, err));
     DSP_CHECK_LAUNCH("dsp_rope_kv_store");
     return 0;
   }

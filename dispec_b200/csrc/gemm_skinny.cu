@@ -2,17 +2,21 @@
 // accumulation: the matrix product of decoding, bound by streaming W once from HBM.
 //
 // Roles are swapped for the tensor cores: W is the 16-row operand of mma.m16n8k16, the few rows
-// of A are its 8-column operand.  Each warp streams 32 rows of W straight from global memory
-// into registers in groups of four 32-wide k blocks (16 loads of 16 bytes per lane), two groups
-// in flight (register double buffer), so that a warp always has 16 KB of W on its way.  The k
-// index inside a 32-wide block is permuted identically for both operands so that every lane's
-// 16-byte load lands in its own fragments without a shuffle.
+// of A are its 8-column operand.  Each warp streams 32 rows of W in groups of four 32-wide k
+// blocks (16 pieces of 16 bytes per lane, 8 KB per warp).  The pieces travel by cp.async into a
+// ring in shared memory that is private to the lane that asked for them: the lane reads back
+// exactly what it copied, so the ring needs no barrier, only cp.async.wait_group, and serves as a
+// deep prefetch queue (five groups, 40 KB per warp, on their way at any time) that registers
+// could not hold.  The k index inside a 32-wide block is permuted identically for both operands
+// so that every lane's 16-byte piece lands in its own fragments without a shuffle.
 //
 // A comes from global memory directly for up to 16 rows (it stays in L1/L2), optionally
 // transformed on the way in:
 //   prologue 1: RMSNorm, a = round(gain[k] * round(x * rsqrt(mean(x^2) + eps))), the row
 //               statistics recomputed by every CTA (a few KB of reads);
-//   prologue 2: SwiGLU, a = silu(x[m, k]) * x[m, K + k] with x of row length 2K.
+// Epilogue SwiGLU: W holds gate and up rows interleaved in blocks of 16 (16 gate rows, then the
+// 16 up rows of the same outputs), so a warp's 32-row strip has both halves of 16 outputs and
+// writes silu(gate) * up, [M, N/2], instead of the raw products.
 // For 17..64 rows A is staged through shared memory in 256-wide k chunks (cp.async, two stages).
 //
 // Split-K: the CTAs that share one block of W rows form a thread-block cluster (up to 8); each
@@ -30,7 +34,8 @@ constexpr int KC = 256;                // k chunk of the staged path
 constexpr int A_STRIDE = KC * 2 + 64;  // bytes; in 16-byte units = 4 mod 8: conflict-free
 constexpr int MAX_SPLITS = 8;          // portable cluster size
 
-enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
+enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1 };
+enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -75,6 +80,7 @@ struct Args {
   int groups_per_split;  // k range of one split, in groups of 128
   const bf16* gain;      // prologue 1
   float eps;
+  int epilogue;
 };
 
 // eight bfloat16 values of one A fragment piece, transformed by the prologue
@@ -96,18 +102,6 @@ __device__ __forceinline__ uint4 load_a_piece(const Args& a, int row, int k, con
       o[j] = __float2bfloat16(__bfloat162float(gn[j]) * __bfloat162float(n));
     }
     raw = out;
-  } else if (PRO == PRO_SWIGLU) {
-    const uint4 uraw = ldg_cached(a.A + (size_t)rs * a.lda + a.K + ks);
-    const bf16* gt = reinterpret_cast<const bf16*>(&raw);
-    const bf16* up = reinterpret_cast<const bf16*>(&uraw);
-    uint4 out;
-    bf16* o = reinterpret_cast<bf16*>(&out);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float gv = __bfloat162float(gt[j]);
-      o[j] = __float2bfloat16(gv / (1.f + expf(-gv)) * __bfloat162float(up[j]));
-    }
-    raw = out;
   }
   if (!valid) raw = make_uint4(0u, 0u, 0u, 0u);
   return raw;
@@ -119,6 +113,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const Args a) {
   constexpr int THREADS = WARPS * 32;
   constexpr int R = 2 * MT * 4;  // accumulators per thread
+  constexpr int STAGES = STAGED ? 3 : 6;
+  constexpr int RING_BYTES = WARPS * STAGES * 8192;  // 8 KB per warp and stage
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ float rstd[16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -138,19 +134,25 @@ gemm_skinny_kernel(const Args a) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) wrow[i] = a.W + (size_t)min(n_warp + g + 8 * i, a.N - 1) * a.K;
 
-  auto load_w = [&](uint4 (&w)[4][4], int group) {
+  // the lane's slots of the ring: [stage][k block][row i][lane], 16 bytes each
+  unsigned char* ring = smem + warp * (STAGES * 8192) + lane * 16;
+  auto issue_w = [&](int group, int stage) {
 #pragma unroll
     for (int kb = 0; kb < 4; ++kb) {
       const int k = group * 128 + kb * 32 + c * 8;
       const bool valid = k < a.K;
-      const int ks = valid ? k : 0;  // load unconditionally, discard afterwards
+      const int ks = valid ? k : 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) w[kb][i] = ldg_stream(wrow[i] + ks);
-      if (!valid) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[kb][i] = make_uint4(0u, 0u, 0u, 0u);
-      }
+      for (int i = 0; i < 4; ++i)
+        cp_async16(ring + ((stage * 4 + kb) * 4 + i) * 512, wrow[i] + ks, valid);
     }
+  };
+  auto read_w = [&](uint4 (&w)[4][4], int stage) {
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        w[kb][i] = *reinterpret_cast<const uint4*>(ring + ((stage * 4 + kb) * 4 + i) * 512);
   };
 
   float acc[2][MT][4];
@@ -161,8 +163,15 @@ gemm_skinny_kernel(const Args a) {
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[s][mt][r] = 0.f;
 
-  uint4 w0[4][4], w1[4][4];
-  if (group_begin < group_end) load_w(w0, group_begin);  // on its way before anything else
+  // the first groups are on their way before anything else happens
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (group_begin + st < group_end) issue_w(group_begin + st, st);
+    cp_async_commit();
+  }
+  // weights do not depend on the kernel before this one; everything below does
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (PRO == PRO_RMSNORM) {
     // row statistics over the whole of K, recomputed by every CTA: warp w takes rows w, w+WARPS, ..
@@ -183,7 +192,7 @@ gemm_skinny_kernel(const Args a) {
     __syncthreads();
   }
 
-  unsigned char* stage[2] = {smem, smem + MP * A_STRIDE};
+  unsigned char* stage[2] = {smem + RING_BYTES, smem + RING_BYTES + MP * A_STRIDE};
   auto load_stage = [&](int chunk, int buf) {
     const int k0 = chunk * KC;
     for (int i = tid; i < MP * 32; i += THREADS) {
@@ -196,15 +205,17 @@ gemm_skinny_kernel(const Args a) {
     cp_async_commit();
   };
 
-  auto compute = [&](uint4 (&w)[4][4], int group, const unsigned char* xs) {
-    uint4 x[4][MT];
-    if (!STAGED) {
+  auto load_x = [&](uint4 (&x)[4][MT], int group) {
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb)
+    for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-          x[kb][mt] = load_a_piece<PRO>(a, mt * 8 + g, group * 128 + kb * 32 + c * 8, rstd);
-    } else {
+      for (int mt = 0; mt < MT; ++mt)
+        x[kb][mt] = load_a_piece<PRO>(a, mt * 8 + g, group * 128 + kb * 32 + c * 8, rstd);
+  };
+  auto compute = [&](uint4 (&x)[4][MT], int group, int w_stage, const unsigned char* xs) {
+    uint4 w[4][4];
+    read_w(w, w_stage);
+    if (STAGED) {
       const int piece0 = (group & 1) * 16 + c;  // two groups per 256-wide chunk
 #pragma unroll
       for (int kb = 0; kb < 4; ++kb)
@@ -225,32 +236,48 @@ gemm_skinny_kernel(const Args a) {
   };
 
   if (!STAGED) {
-    for (int gi = group_begin; gi < group_end; gi += 2) {
-      if (gi + 1 < group_end) load_w(w1, gi + 1);
-      compute(w0, gi, nullptr);
-      if (gi + 2 < group_end) load_w(w0, gi + 2);
-      if (gi + 1 < group_end) compute(w1, gi + 1, nullptr);
+    uint4 x_cur[4][MT], x_next[4][MT];
+    if (group_begin < group_end) load_x(x_cur, group_begin);
+    for (int gi = group_begin; gi < group_end; ++gi) {
+      const int j = gi - group_begin;
+      const int nxt = gi + STAGES - 1;
+      if (nxt < group_end) issue_w(nxt, (j + STAGES - 1) % STAGES);
+      cp_async_commit();
+      if (gi + 1 < group_end) load_x(x_next, gi + 1);  // one group ahead, behind the L2 latency
+      cp_async_wait<STAGES - 1>();                     // group gi has landed
+      compute(x_cur, gi, j % STAGES, nullptr);
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) x_cur[kb][mt] = x_next[kb][mt];
     }
   } else {
     // group_begin is even (a split starts on a chunk boundary): chunk = group / 2
+    uint4 x_unused[4][MT];
     if (group_begin < group_end) load_stage(group_begin / 2, 0);
     for (int gi = group_begin; gi < group_end; gi += 2) {
       const int chunk = gi / 2;
       const int buf = (chunk - group_begin / 2) & 1;
       if (gi + 2 < group_end) {
         load_stage(chunk + 1, buf ^ 1);
-        cp_async_wait<1>();
+        cp_async_wait<1>();  // all but the next A chunk: W groups gi, gi+1 and this A chunk are in
       } else {
         cp_async_wait<0>();
       }
       __syncthreads();
-      if (gi + 1 < group_end) load_w(w1, gi + 1);
-      compute(w0, gi, stage[buf]);
-      if (gi + 2 < group_end) load_w(w0, gi + 2);
-      if (gi + 1 < group_end) compute(w1, gi + 1, stage[buf]);
+      const int j = gi - group_begin;
+      // a W group is asked for as soon as the stage it goes to has been read
+      if (gi + 2 < group_end) issue_w(gi + 2, (j + 2) % STAGES);
+      cp_async_commit();
+      compute(x_unused, gi, j % STAGES, stage[buf]);
+      if (gi + 3 < group_end) issue_w(gi + 3, j % STAGES);
+      cp_async_commit();
+      if (gi + 1 < group_end) compute(x_unused, gi + 1, (j + 1) % STAGES, stage[buf]);
       __syncthreads();
     }
   }
+  cp_async_wait<0>();
+  __syncthreads();
 
   // ---- split-K: add the partial tiles of the cluster through distributed shared memory
   auto store = [&](int r, float v) {
@@ -263,6 +290,17 @@ gemm_skinny_kernel(const Args a) {
       reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>(v);
     }
   };
+  // strip 0 of the warp holds gate rows, strip 1 the up rows of the same 16 outputs
+  auto store_swiglu = [&](int r, float gate, float up) {
+    const int mt = (r / 4) % MT, e = r & 3;
+    const int n = n_warp + g + 8 * (e >> 1);  // gate row; its up row is n + 16
+    const int m = 8 * mt + 2 * c + (e & 1);
+    if (n + 16 < a.N && m < a.M) {
+      const int j = (n_warp >> 1) + g + 8 * (e >> 1);
+      reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + j] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+    }
+  };
+  const bool swiglu = a.epilogue == EPI_SWIGLU;
   if (splits > 1) {
     cg::cluster_group cluster = cg::this_cluster();
     float* red = reinterpret_cast<float*>(smem);  // [R][THREADS]
@@ -274,12 +312,22 @@ gemm_skinny_kernel(const Args a) {
         for (int r = 0; r < 4; ++r) red[((s * MT + mt) * 4 + r) * THREADS + tid] = acc[s][mt][r];
     cluster.sync();
     const int rank = (int)cluster.block_rank();
-    for (int r = rank; r < R; r += splits) {
+    auto total_of = [&](int r) {
       float total = 0.f;
       for (int sp = 0; sp < splits; ++sp) total += cluster.map_shared_rank(red, sp)[r * THREADS + tid];
-      store(r, total);
+      return total;
+    };
+    if (swiglu) {
+      for (int r = rank; r < MT * 4; r += splits) store_swiglu(r, total_of(r), total_of(r + MT * 4));
+    } else {
+      for (int r = rank; r < R; r += splits) store(r, total_of(r));
     }
     cluster.sync();  // nobody leaves while its shared memory may still be read
+  } else if (swiglu) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) store_swiglu(mt * 4 + r, acc[0][mt][r], acc[1][mt][r]);
   } else {
 #pragma unroll
     for (int s = 0; s < 2; ++s)
@@ -293,9 +341,11 @@ gemm_skinny_kernel(const Args a) {
 template <int MT, int WARPS, bool STAGED, int PRO, typename TOut>
 int launch(const Args& a, int splits, cudaStream_t stream) {
   constexpr int THREADS = WARPS * 32;
+  const size_t ring_bytes = (size_t)WARPS * (STAGED ? 3 : 6) * 8192;
   const size_t stage_bytes = STAGED ? 2 * (size_t)(MT * 8) * A_STRIDE : 0;
   const size_t red_bytes = splits > 1 ? (size_t)(2 * MT * 4) * THREADS * sizeof(float) : 0;
-  const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+  const size_t main_bytes = ring_bytes + stage_bytes;
+  const size_t smem = main_bytes > red_bytes ? main_bytes : red_bytes;
   auto kernel = gemm_skinny_kernel<MT, WARPS, STAGED, PRO, TOut>;
   static size_t configured = 0;  // per instantiation; not repeated under graph capture
   if (smem > configured) {
@@ -307,13 +357,15 @@ int launch(const Args& a, int splits, cudaStream_t stream) {
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = splits;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   DSP_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
   return 0;
 }
@@ -335,12 +387,13 @@ int dispatch(const Args& a, int splits, bool narrow, cudaStream_t stream) {
 }
 }  // namespace
 
-// prologue: 0 none; 1 RMSNorm of A's rows with `gain` and `eps` (M <= 16); 2 SwiGLU, A has row
-// length 2K (M <= 16).  target_ctas: CTAs the launch aims for (split-K, at most 8 splits).
+// prologue: 0 none; 1 RMSNorm of A's rows with `gain` and `eps` (M <= 16).
+// epilogue: 0 plain; 1 SwiGLU over W rows interleaved in blocks of 16 (C is [M, N/2], no bias or
+// residual).  target_ctas: resident CTA slots the launch may fill by splitting K (at most 8 ways).
 extern "C" int dsp_gemm_skinny(const void* A, long lda, const void* W, const void* bias,
                                const void* residual, long ldr, void* C, long ldc, int M, int N,
                                int K, int out_dtype, int target_ctas, int prologue,
-                               const void* gain, float eps, cudaStream_t stream) {
+                               const void* gain, float eps, int epilogue, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   DSP_REQUIRE(M <= 64, "dsp_gemm_skinny: M=%d above 64 rows", M);
   DSP_REQUIRE(K > 0 && K % 8 == 0, "dsp_gemm_skinny: K=%d must be a positive multiple of 8", K);
@@ -362,11 +415,16 @@ extern "C" int dsp_gemm_skinny(const void* A, long lda, const void* W, const voi
   a.K = K;
   a.gain = (const bf16*)gain;
   a.eps = eps;
-  // narrow CTAs (64 rows of W) when wide ones (128 rows) could not fill the SMs even with all splits
+  a.epilogue = epilogue;
+  DSP_REQUIRE(epilogue == EPI_PLAIN || (N % 32 == 0 && bias == nullptr && residual == nullptr),
+              "dsp_gemm_skinny: the SwiGLU epilogue needs N in whole blocks of 32 and no bias or residual");
+  // CTAs of 64 rows of W, two resident per SM; the K range is split (cluster of up to 8) only as
+  // far as the CTAs still fit the resident slots at once.  A negative target selects 128-row CTAs.
   const int groups = (K + 127) / 128;
   const int pairs = (groups + 1) / 2;  // a split covers whole 256-wide chunks
   const int max_splits = pairs < MAX_SPLITS ? pairs : MAX_SPLITS;
-  const bool narrow = ((N + 127) / 128) * max_splits < 2 * 148;
+  const bool narrow = target_ctas >= 0;
+  if (target_ctas < 0) target_ctas = -target_ctas;
   const int n_blocks = narrow ? (N + 63) / 64 : (N + 127) / 128;
   int splits = target_ctas / n_blocks;
   if (splits < 1) splits = 1;
@@ -377,12 +435,10 @@ extern "C" int dsp_gemm_skinny(const void* A, long lda, const void* W, const voi
   int rc;
   if (out_dtype == DSP_BF16) {
     rc = prologue == PRO_RMSNORM ? dispatch<PRO_RMSNORM, bf16>(a, splits, narrow, stream)
-         : prologue == PRO_SWIGLU ? dispatch<PRO_SWIGLU, bf16>(a, splits, narrow, stream)
-                                  : dispatch<PRO_NONE, bf16>(a, splits, narrow, stream);
+                                 : dispatch<PRO_NONE, bf16>(a, splits, narrow, stream);
   } else if (out_dtype == DSP_F32) {
     rc = prologue == PRO_RMSNORM ? dispatch<PRO_RMSNORM, float>(a, splits, narrow, stream)
-         : prologue == PRO_SWIGLU ? dispatch<PRO_SWIGLU, float>(a, splits, narrow, stream)
-                                  : dispatch<PRO_NONE, float>(a, splits, narrow, stream);
+                                 : dispatch<PRO_NONE, float>(a, splits, narrow, stream);
   } else {
     DSP_REQUIRE(false, "dsp_gemm_skinny: unknown output dtype %d", out_dtype);
   }

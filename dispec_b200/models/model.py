@@ -41,6 +41,8 @@ def build_part(spec: PartSpec, built: dict, bindings: list, prefix: str = "") ->
 
 
 class DecoderModel:
+    fuse_final_norm = False  # final norm inside the head's product: measured slower than two kernels
+
     def __init__(self, spec: ModelSpec, config=None):
         self.spec = spec
         self.config = config
@@ -141,7 +143,8 @@ class DecoderModel:
 
     def logits(self, ctx, x, pending, rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits at the given flat token rows (int32 device tensor)."""
-        if (pending is None and ctx.logit_rows_are_all and hasattr(self.head, "forward_normed")
+        if (self.fuse_final_norm and pending is None and ctx.logit_rows_are_all
+                and hasattr(self.head, "forward_normed")
                 and hasattr(self.final_norm, "as_linear_prologue")):
             out = self.head.forward_normed(ctx, x, self.final_norm)
             if out is not None:

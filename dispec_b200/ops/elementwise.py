@@ -52,14 +52,15 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.Ten
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int = 0) -> torch.Tensor:
+    """out[t, i] = silu(gate(t, i)) * up(t, i).  ``block`` 0: a row is [gates | ups]; b > 0: gates
+    and ups alternate in blocks of b columns (b gates, their b ups, the next b gates, ...)."""
     _cuda(gate_up)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
     n, inter = gate_up.shape[0], gate_up.shape[1] // 2
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
-    L.check(L.core().dsp_swiglu(L.ptr(gate_up), L.ptr(out), n, inter, L.dtype_code(gate_up.dtype),
+    L.check(L.core().dsp_swiglu(L.ptr(gate_up), L.ptr(out), n, inter, block, L.dtype_code(gate_up.dtype),
                                 L.stream_handle()))
     return out
 

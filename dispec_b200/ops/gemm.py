@@ -15,7 +15,7 @@ import torch
 from dispec_b200.ops import library as L
 
 SKINNY_MAX_ROWS = 64  # rows the weight-streaming kernel takes
-SKINNY_TARGET_CTAS = 148 * 3  # CTAs a weight-streaming launch aims for (split-K fills the SMs)
+SKINNY_TARGET_CTAS = 148 * 2  # resident CTA slots a weight-streaming launch may fill by splitting K
 LARGE_BACKEND = "library"  # "library" | "simt"
 
 
@@ -29,18 +29,21 @@ def _simt(x, w, bias, residual, out):
     return out
 
 
-PRO_NONE, PRO_RMSNORM, PRO_SWIGLU = 0, 1, 2
+PRO_NONE, PRO_RMSNORM = 0, 1
+EPI_PLAIN, EPI_SWIGLU = 0, 1
+SWIGLU_BLOCK = 16  # gate/up rows alternate in blocks of this many for the fused epilogue
 FUSED_MAX_ROWS = 16  # rows up to which the weight-streaming kernel can fuse a prologue
 
 
-def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain=None, eps=0.0):
+def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain=None, eps=0.0,
+            epilogue=EPI_PLAIN):
     M = x.shape[0]
     N, K = w.shape
     L.check(L.core().dsp_gemm_skinny(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
         M, N, K, L.dtype_code(out.dtype), SKINNY_TARGET_CTAS if target_ctas is None else target_ctas,
-        prologue, L.ptr(gain), L.f32(eps), L.stream_handle()))
+        prologue, L.ptr(gain), L.f32(eps), epilogue, L.stream_handle()))
     return out
 
 
@@ -66,13 +69,23 @@ def linear_rms_norm(x, gain, eps, w, bias=None, residual=None, out_dtype=None, o
     return _skinny(x, w, bias, residual, out, prologue=PRO_RMSNORM, gain=gain, eps=eps)
 
 
-def linear_swiglu(gate_up, w, bias=None, residual=None, out_dtype=None, out=None):
-    """linear(swiglu(gate_up), w, ...) in one kernel; gate_up is [M, 2K] (bfloat16, M <= 16)."""
-    assert gate_up.shape[1] == 2 * w.shape[1] and fused_prologue_supported(gate_up, w)
-    out_dtype = out_dtype or (out.dtype if out is not None else gate_up.dtype)
+def gate_up_swiglu_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    M, K = x.shape
+    return x.dtype == torch.bfloat16 and skinny_supported(M, w.shape[0], K, x, w) and w.shape[0] % 32 == 0
+
+
+def linear_gate_up_swiglu(x, w_interleaved, norm=None, out=None):
+    """silu(x Wg^T) * (x Wu^T) in one kernel: ``w_interleaved`` holds 16 gate rows, the 16 up
+    rows of the same outputs, the next 16 gate rows, ...  Returns [M, N/2].  ``norm`` = (gain, eps)
+    applies an RMSNorm to x on the way in (at most 16 rows)."""
+    assert gate_up_swiglu_supported(x, w_interleaved)
+    M, N = x.shape[0], w_interleaved.shape[0]
     if out is None:
-        out = torch.empty((gate_up.shape[0], w.shape[0]), dtype=out_dtype, device=gate_up.device)
-    return _skinny(gate_up, w, bias, residual, out, prologue=PRO_SWIGLU)
+        out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
+    if norm is not None:
+        return _skinny(x, w_interleaved, None, None, out, prologue=PRO_RMSNORM, gain=norm[0], eps=norm[1],
+                       epilogue=EPI_SWIGLU)
+    return _skinny(x, w_interleaved, None, None, out, epilogue=EPI_SWIGLU)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,

@@ -23,20 +23,31 @@ class SwiGLUFeedForward(FeedForward):
                 "down_proj.weight": TensorSpec((h, i))}
 
     def load(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]],
-                                   dim=0).contiguous()
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        i, h = self.intermediate_size, self.hidden_size
+        # gate and up rows alternate in blocks of 16 when the width allows, so that one warp of the
+        # decoding kernel holds both halves of an output and applies the activation itself
+        self.block = gemm_ops.SWIGLU_BLOCK if i % gemm_ops.SWIGLU_BLOCK == 0 else 0
+        if self.block:
+            b = self.block
+            self.w_gate_up = torch.stack([gate.view(i // b, b, h), up.view(i // b, b, h)],
+                                         dim=1).reshape(2 * i, h).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
     fuses_norm_and_residual = True
 
     def forward(self, ctx, x, pre_norm=None, residual=None):
-        """``pre_norm`` / ``residual``: as for the attention mixer.  With few rows the activation
-        is applied on the way into the down projection instead of by a kernel of its own."""
-        if pre_norm is not None:
-            gain, eps = pre_norm.as_linear_prologue()
-            gate_up = gemm_ops.linear_rms_norm(x, gain, eps, self.w_gate_up)
+        """``pre_norm``: x is not normalised yet, the norm is applied on the way into the first
+        product.  ``residual``: added by the last product, so that the sum comes back."""
+        norm = pre_norm.as_linear_prologue() if pre_norm is not None else None
+        if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up):
+            act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up, norm)
         else:
-            gate_up = ops.linear(x, self.w_gate_up)
-        if gemm_ops.fused_prologue_supported(gate_up, self.w_down):
-            return gemm_ops.linear_swiglu(gate_up, self.w_down, residual=residual, out=residual)
-        return ops.linear(ops.swiglu(gate_up), self.w_down, residual=residual, out=residual)
+            if norm is not None:
+                gate_up = gemm_ops.linear_rms_norm(x, norm[0], norm[1], self.w_gate_up)
+            else:
+                gate_up = ops.linear(x, self.w_gate_up)
+            act = ops.swiglu(gate_up, block=self.block)
+        return ops.linear(act, self.w_down, residual=residual, out=residual)

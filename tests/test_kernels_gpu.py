@@ -73,6 +73,12 @@ def test_swiglu(dtype):
     g, u = gu[:, :224].float(), gu[:, 224:].float()
     ref = (g * torch.sigmoid(g) * u).to(dtype)
     torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+    # gates and ups alternating in blocks of 16 columns
+    inter = gu.view(5, 2, 14, 16).permute(0, 2, 1, 3).reshape(5, 448).contiguous()
+    torch.testing.assert_close(ops.swiglu(inter, block=16).float(), ref.float(), **tol(dtype))
+    odd = rnd((3, 2 * 50), dtype, 7)  # a width the 16-byte path does not take
+    g, u = odd[:, :50].float(), odd[:, 50:].float()
+    torch.testing.assert_close(ops.swiglu(odd).float(), (g * torch.sigmoid(g) * u).to(dtype).float(), **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -397,7 +403,7 @@ def test_attention_tensor_core_mixed_batch_matches_alone():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 130, 96), (8, 2048, 1536), (13, 300, 776), (16, 1536, 8960)])
-def test_gemm_weight_streaming_with_fused_norm_and_swiglu(M, N, K):
+def test_gemm_weight_streaming_with_fused_norm(M, N, K):
     from dispec_b200 import ops
     from dispec_b200.ops import gemm
     x = rnd((M, K), torch.bfloat16, 31, 2.0)
@@ -413,10 +419,113 @@ def test_gemm_weight_streaming_with_fused_norm_and_swiglu(M, N, K):
     torch.testing.assert_close(fused.double(), ref, atol=3e-2, rtol=2e-2)
     logits = gemm.linear_rms_norm(x, gain, eps, w, out_dtype=torch.float32)
     torch.testing.assert_close(logits.double(), normed.double() @ w.double().T, atol=3e-3, rtol=3e-3)
-    # SwiGLU on the way in: gate_up is [M, 2K]
-    gu = rnd((M, 2 * K), torch.bfloat16, 36, 1.5)
-    act = ops.swiglu(gu)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 96), (8, 8960, 1536), (13, 176, 80), (40, 224, 96), (64, 512, 776)])
+def test_gate_up_product_with_swiglu_epilogue(M, I, K):
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm
+    x = rnd((M, K), torch.bfloat16, 41)
+    wg, wu = rnd((I, K), torch.bfloat16, 42, 0.15), rnd((I, K), torch.bfloat16, 43, 0.15)
+    b = gemm.SWIGLU_BLOCK
+    w = torch.stack([wg.view(I // b, b, K), wu.view(I // b, b, K)], dim=1).reshape(2 * I, K).contiguous()
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    ref = g * torch.sigmoid(g) * u
+    out = gemm.linear_gate_up_swiglu(x, w)
+    torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=3e-2)
+    # the unfused pair of kernels on the same interleaved weight
+    unfused = ops.swiglu(gemm.linear(x, w, backend="simt"), block=b)
+    torch.testing.assert_close(unfused.double(), ref, atol=3e-2, rtol=3e-2)
+    if M <= 16:
+        gain = (1 + rnd((K,), torch.float32, 44, 0.1)).to(torch.bfloat16).to(dev())
+        normed = ops.rms_norm(x, gain, 1e-5)
+        g, u = normed.double() @ wg.double().T, normed.double() @ wu.double().T
+        fused = gemm.linear_gate_up_swiglu(x, w, norm=(gain, 1e-5))
+        torch.testing.assert_close(fused.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("case", ATTN_CASES + [(28, 4, 128, 16, 1200, 1, 0), (5, 5, 80, 16, 130, 64, 0),
+                                               (8, 1, 256, 16, 100, 9, 0), (12, 2, 128, 16, 700, 300, 0)])
+def test_attention_tensor_core(case):
+    out, ref = run_attention("tensor_core", torch.bfloat16, *case)
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("plant", [0, 15, 16, 63, 64, 65, 255, 256, 511, 600])
+@pytest.mark.parametrize("q_len", [1, 37])
+def test_attention_tensor_core_far_key_stands_out(plant, q_len):
+    out, ref = run_attention("tensor_core", torch.bfloat16, 12, 2, 64, 16, 700, q_len, 0, plant=plant,
+                             seed=plant)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("offset", [-1, 0, 1])
+@pytest.mark.parametrize("q_len", [1, 20])
+def test_attention_tensor_core_window_edge(offset, q_len):
+    ctx, window = 333, 100
+    plant = ctx - 1 - window + 1 + offset
+    out, ref = run_attention("tensor_core", torch.bfloat16, 6, 2, 32, 8, ctx, q_len, window, plant=plant,
+                             seed=9)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+def test_attention_tensor_core_mixed_batch_matches_alone():
+    """Single tokens (with key splits) beside a portion of a prompt, ragged lengths."""
+    from dispec_b200.ops import attention as A
+    H, KVH, D, page = 6, 2, 64, 16
+    q_lens = [1, 1, 1, 23, 70]
+    ctx_lens = [17, 300, 64, 23, 200]
+    g = torch.Generator().manual_seed(11)
+    num_pages = sum((c + page - 1) // page for c in ctx_lens) + 2
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=torch.bfloat16)
+    vp = kp.clone()
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    maxp = max((c + page - 1) // page for c in ctx_lens)
+    table = torch.full((len(q_lens), maxp), -1, dtype=torch.int32)
+    qs, refs, positions, seqs = [], [], [], []
+    for s, (ql, cl) in enumerate(zip(q_lens, ctx_lens)):
+        k = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
+        v = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
+        q = torch.randn(ql, H, D, generator=g).bfloat16().float()
+        for j in range((cl + page - 1) // page):
+            table[s, j] = perm.pop()
+        for b in range(cl):
+            kp[table[s, b // page], :, b % page] = k[b].bfloat16()
+            vp[table[s, b // page], :, b % page] = v[b].bfloat16()
+        pos = torch.arange(cl - ql, cl, dtype=torch.int32)
+        refs.append(_attention_reference(q.double(), k.double(), v.double(), pos, 0, D ** -0.5))
+        qs.append(q)
+        positions.append(pos)
+        seqs += [s] * ql
+    qd = torch.cat(qs).bfloat16().reshape(-1, H * D).to(dev())
+    out = torch.empty_like(qd)
+    A.paged_attention_tensor_core(qd, H * D, kp.to(dev()), vp.to(dev()), table.to(dev()),
+                                  torch.cat(positions).to(dev()),
+                                  torch.tensor(seqs, dtype=torch.int32, device=dev()), out, H, KVH, D, 0,
+                                  D ** -0.5, q_lens=q_lens, ctx_lens=ctx_lens, splits=4)
+    got = out.float().cpu().view(-1, H, D).double()
+    torch.testing.assert_close(got, torch.cat(refs), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 96), (8, 2048, 1536), (13, 300, 776), (16, 1536, 8960)])
+def test_gemm_weight_streaming_with_fused_norm(M, N, K):
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm
+    x = rnd((M, K), torch.bfloat16, 31, 2.0)
+    gain = (1 + rnd((K,), torch.float32, 32, 0.1)).to(torch.bfloat16).to(dev())
+    w = rnd((N, K), torch.bfloat16, 33, 0.1)
+    b = rnd((N,), torch.bfloat16, 34)
+    r = rnd((M, N), torch.bfloat16, 35)
+    eps = 1e-5
+    # the fused form against the two kernels it replaces (same rounding points), and against float64
+    normed = ops.rms_norm(x, gain, eps)
+    fused = gemm.linear_rms_norm(x, gain, eps, w, b, residual=r.clone())
+    ref = normed.double() @ w.double().T + b.double() + r.double()
+    torch.testing.assert_close(fused.double(), ref, atol=3e-2, rtol=2e-2)
+    logits = gemm.linear_rms_norm(x, gain, eps, w, out_dtype=torch.float32)
+    torch.testing.assert_close(logits.double(), normed.double() @ w.double().T, atol=3e-3, rtol=3e-3)
+    # a residual that is also the output is updated in place
     resid = r.clone()
-    out = gemm.linear_swiglu(gu, w, residual=resid, out=resid)
-    assert out.data_ptr() == resid.data_ptr()  # the residual is updated in place
-    torch.testing.assert_close(out.double(), act.double() @ w.double().T + r.double(), atol=3e-2, rtol=2e-2)
+    out = gemm.linear(normed, w, residual=resid, out=resid)
+    assert out.data_ptr() == resid.data_ptr()
+    torch.testing.assert_close(out.double(), normed.double() @ w.double().T + r.double(), atol=3e-2, rtol=2e-2)
