@@ -341,3 +341,49 @@ extern "C" int dsp_sample(const float* logits, long stride, int n, int V, const 
   DSP_CHECK_LAUNCH("dsp_sample");
   return 0;
 }
+
+// ------------------------------------------------------------------ argmax without allocation
+// The two-stage argmax with its scratch inside the library image; see no_alloc.h for who needs
+// it and for the rules (size limit, first call, sharing).
+#include "no_alloc.h"
+
+namespace {
+constexpr int STATIC_MAX_ROWS = 1024;
+constexpr int STATIC_MAX_CHUNKS = 64;
+}  // namespace
+
+// [STATIC_MAX_ROWS * STATIC_MAX_CHUNKS] floats, then as many ints.  In host code this name is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char
+    g_argmax_static_scratch[STATIC_MAX_ROWS * STATIC_MAX_CHUNKS * (sizeof(float) + sizeof(int))];
+
+extern "C" int dsp_argmax_static_max_rows(void) { return STATIC_MAX_ROWS; }
+
+extern "C" int dsp_argmax_static(const float* logits, long stride, int n, int V, int* out,
+                                 cudaStream_t stream) {
+  if (n == 0) return 0;
+  DSP_REQUIRE(n > 0 && n <= STATIC_MAX_ROWS,
+              "dsp_argmax_static: %d rows, the built-in scratch holds at most %d", n, STATIC_MAX_ROWS);
+  DSP_REQUIRE(V > 0, "dsp_argmax_static: V=%d", V);
+  DSP_REQUIRE(logits != nullptr && out != nullptr, "dsp_argmax_static: null pointer");
+  // set-up, once per device, with that device current
+  static unsigned char* address[64] = {nullptr};
+  int dev = 0;
+  DSP_CUDA(cudaGetDevice(&dev));
+  DSP_REQUIRE(dev >= 0 && dev < 64, "dsp_argmax_static: device index %d out of range", dev);
+  if (address[dev] == nullptr) {
+    unsigned char* p = nullptr;
+    DSP_CUDA(cudaGetSymbolAddress((void**)&p, g_argmax_static_scratch));
+    DSP_REQUIRE(p != nullptr, "dsp_argmax_static: the scratch array has no device address");
+    address[dev] = p;
+  }
+  float* part_val = reinterpret_cast<float*>(address[dev]);
+  int* part_idx = reinterpret_cast<int*>(address[dev] + (size_t)STATIC_MAX_ROWS * STATIC_MAX_CHUNKS * sizeof(float));
+  int chunks = (V + 4095) / 4096;
+  if (chunks > STATIC_MAX_CHUNKS) chunks = STATIC_MAX_CHUNKS;
+  const int chunk = (V + chunks - 1) / chunks;
+  argmax_partial_kernel<<<dim3(n, chunks), 256, 0, stream>>>(logits, stride, V, chunk, part_val, part_idx);
+  argmax_final_kernel<<<n, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+  DSP_CHECK_LAUNCH("dsp_argmax_static");
+  return 0;
+}
