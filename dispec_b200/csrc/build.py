@@ -28,6 +28,7 @@ CORE_SOURCES = [
     "elementwise.cu",
     "gemm_simt.cu",
     "gemm_skinny.cu",
+    "gemm_tcgen05.cu",
     "attn_generic.cu",
     "attn_combine.cu",
     "sampling.cu",

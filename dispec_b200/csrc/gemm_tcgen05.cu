@@ -1,0 +1,320 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for many rows (prefill), bfloat16 in, 32-bit
+// accumulation on the fifth-generation tensor cores.
+//
+// One CTA computes a 128 x 256 tile of C.  A and W tiles of 64 k (128 bytes a row) come by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage ring in shared
+// memory; one thread issues tcgen05.mma (M 128, N 256, K 16, operands described by shared-memory
+// descriptors, K-major) into a 128-lane x 256-column accumulator in tensor memory;
+// tcgen05.commit hands each stage back to the TMA thread through an mbarrier and, after the last
+// k block, tells the four epilogue warps that the accumulator is complete.  They read it with
+// tcgen05.ld (each warp its own 32 lanes), add bias and residual in 32-bit, round once and store.
+//
+// Every wait on an mbarrier is bounded: if it runs out, the kernel records it in the device error
+// word, lets copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 256;
+constexpr int THREADS = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;  // tries; each try blocks for a while in hardware
+
+struct Epilogue {
+  const bf16* bias;
+  const void* residual;
+  long ldr;
+  void* C;
+  long ldc;
+  int M, N, K;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// true when the phase with this parity has completed; false when the bounded wait ran out
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle: groups of 8 rows are 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle): 1
+  d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                             // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                             // layout type: 128-byte swizzle
+  return d;
+}
+
+// kind::f16: D float32, A and B bfloat16, both K-major, M 128, N 256
+__device__ __forceinline__ uint32_t umma_idesc() {
+  uint32_t d = 0;
+  d |= 1u << 4;                   // D format: F32
+  d |= 1u << 7;                   // A format: BF16
+  d |= 1u << 10;                  // B format: BF16
+  d |= (uint32_t)(BN >> 3) << 17; // N
+  d |= (uint32_t)(BM >> 4) << 24; // M
+  return d;
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const Epilogue e, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int num_kb = (e.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+        failed = 1;
+        break;
+      }
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      unsigned char* a_dst = smem + s * STAGE_BYTES;
+      tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+      tma_load_2d(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    const uint32_t idesc = umma_idesc();
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(&full_bar[s], phase)) {
+        failed = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+      const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        // the next 16 k of a 128-byte swizzled row: 32 bytes further
+        umma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+      }
+      umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
+    }
+    if (ok) umma_commit(&accum_bar);
+  }
+  __syncwarp();
+
+  // ---- epilogue: warp w owns accumulator lanes 32w..32w+31 = rows m0 + 32w + lane
+  bool ready = mbar_wait(&accum_bar, 0);
+  ready = __syncthreads_and(ready && !failed) != 0;  // one verdict for the whole CTA
+  if (!ready) {
+    if (threadIdx.x == 0) atomicOr(err, DSP_ERR_WAIT_LIMIT);
+    // let copies that are still on their way land before the shared memory goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  tc_fence_after();
+  if (ready) {
+    const int row = m0 + warp * 32 + lane;
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      const int col = n0 + c0;
+      if (row < e.M && col < e.N) {
+        TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
+        const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
+        const int valid = min(32, e.N - col);
+        if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
+            if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
+            const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
+            uint4 oraw;
+            bf16* ob = reinterpret_cast<bf16*>(&oraw);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              float x = __uint_as_float(v[j * 8 + t]);
+              if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
+              if (res) x += __bfloat162float(rb[t]);
+              ob[t] = __float2bfloat16(x);
+            }
+            reinterpret_cast<uint4*>(dst)[j] = oraw;
+          }
+        } else {
+          for (int t = 0; t < valid; ++t) {
+            float x = __uint_as_float(v[t]);
+            if (e.bias) x += __bfloat162float(e.bias[col + t]);
+            if (res) x += to_f32(res[t]);
+            dst[t] = from_f32<TOut>(x);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+
+// rows x K bfloat16, row stride ld elements; box 64 k x box_rows rows, 128-byte swizzle, zero fill
+bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+  EncodeTiled fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+// bfloat16 A [M, K] (row stride lda) and W [N, K] (contiguous); C and residual bfloat16 or float32.
+extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const void* bias, const void* residual,
+                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype,
+                                cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_tcgen05: K=%d and the row stride must be multiples of 8", K);
+  DSP_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "dsp_gemm_tcgen05: operands must be 16-byte aligned");
+  DSP_REQUIRE(out_dtype == DSP_BF16 || out_dtype == DSP_F32, "dsp_gemm_tcgen05: unknown output dtype %d", out_dtype);
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_gemm_tcgen05: no device error word");
+  CUtensorMap map_a, map_w;
+  DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
+  DSP_REQUIRE(make_map(&map_w, W, N, K, K, BN), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+  Epilogue e;
+  e.bias = (const bf16*)bias;
+  e.residual = residual;
+  e.ldr = ldr;
+  e.C = C;
+  e.ldc = ldc;
+  e.M = M;
+  e.N = N;
+  e.K = K;
+  const int smem = STAGES * STAGE_BYTES + 1024;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  DSP_REQUIRE(grid.y <= 65535, "dsp_gemm_tcgen05: M=%d too large for one launch", M);
+  if (out_dtype == DSP_BF16) {
+    static bool configured = false;
+    if (!configured) {
+      DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      configured = true;
+    }
+    gemm_tcgen05_kernel<bf16><<<grid, THREADS, smem, stream>>>(map_a, map_w, e, err);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      configured = true;
+    }
+    gemm_tcgen05_kernel<float><<<grid, THREADS, smem, stream>>>(map_a, map_w, e, err);
+  }
+  DSP_CHECK_LAUNCH("dsp_gemm_tcgen05");
+  return 0;
+}

@@ -16,7 +16,7 @@ from dispec_b200.ops import library as L
 
 SKINNY_MAX_ROWS = 64  # rows the weight-streaming kernel takes
 SKINNY_TARGET_CTAS = 148 * 2  # resident CTA slots a weight-streaming launch may fill by splitting K
-LARGE_BACKEND = "library"  # "library" | "simt"
+LARGE_BACKEND = "library"  # "tcgen05" | "library" | "simt"
 
 
 def _simt(x, w, bias, residual, out):
@@ -45,6 +45,21 @@ def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain
         M, N, K, L.dtype_code(out.dtype), SKINNY_TARGET_CTAS if target_ctas is None else target_ctas,
         prologue, L.ptr(gain), L.f32(eps), epilogue, L.stream_handle()))
     return out
+
+
+def _tcgen05(x, w, bias, residual, out):
+    M, K = x.shape
+    N = w.shape[0]
+    L.check(L.core().dsp_gemm_tcgen05(
+        L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
+        L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
+        M, N, K, L.dtype_code(out.dtype), L.stream_handle()))
+    return out
+
+
+def tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def skinny_supported(M: int, N: int, K: int, x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -116,12 +131,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     if backend is None:
         if skinny_supported(M, N, K, x, w):
             backend = "skinny"
-        elif out_dtype == torch.bfloat16 and M > SKINNY_MAX_ROWS:
+        elif M > SKINNY_MAX_ROWS and (out_dtype == torch.bfloat16 or LARGE_BACKEND == "tcgen05"):
             backend = LARGE_BACKEND
         else:
             backend = "simt"
     if backend == "skinny":
         return _skinny(x, w, bias, residual, out)
+    if backend == "tcgen05":
+        if tcgen05_supported(x, w):
+            return _tcgen05(x, w, bias, residual, out)
+        backend = "library" if out_dtype == torch.bfloat16 else "simt"
     if backend == "library":
         # the library matrix product; bias and residual are folded in by the library as well
         assert out_dtype == torch.bfloat16
