@@ -1,13 +1,15 @@
 // C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for many rows (prefill), bfloat16 in, 32-bit
 // accumulation on the fifth-generation tensor cores.
 //
-// One CTA computes a 128 x 256 tile of C.  A and W tiles of 64 k (128 bytes a row) come by TMA
-// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage ring in shared
-// memory; one thread issues tcgen05.mma (M 128, N 256, K 16, operands described by shared-memory
-// descriptors, K-major) into a 128-lane x 256-column accumulator in tensor memory;
-// tcgen05.commit hands each stage back to the TMA thread through an mbarrier and, after the last
-// k block, tells the four epilogue warps that the accumulator is complete.  They read it with
-// tcgen05.ld (each warp its own 32 lanes), add bias and residual in 32-bit, round once and store.
+// Persistent: one CTA per SM walks over 128 x 256 tiles of C.  A and W tiles of 64 k (128 bytes a
+// row) come by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage ring
+// in shared memory that never drains between tiles; one thread issues tcgen05.mma (M 128, N 256,
+// K 16, operands described by shared-memory descriptors, K-major) into one of two 128-lane x
+// 256-column accumulators in tensor memory; tcgen05.commit hands each stage back to the TMA
+// thread through an mbarrier and, after a tile's last k block, tells the four epilogue warps that
+// the accumulator is complete.  They read it with tcgen05.ld (each warp its own 32 lanes), add
+// bias and residual in 32-bit, round once and store, while the products of the next tile already
+// run into the other accumulator.
 //
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records it in the device error
 // word, lets copies in flight land, frees its tensor memory and returns.
@@ -18,8 +20,8 @@
 namespace {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 256;
-constexpr int THREADS = 128;
+constexpr int TMEM_COLS = 512;  // two accumulators of 256 columns
+constexpr int THREADS = 192;    // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
 constexpr uint32_t WAIT_LIMIT = 1u << 20;  // tries; each try blocks for a while in hardware
 
 struct Epilogue {
@@ -123,24 +125,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
-  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ __align__(8) uint64_t accum_full[2];
+  __shared__ __align__(8) uint64_t accum_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int num_kb = (e.K + BK - 1) / BK;
+  const int n_tiles = (e.N + BN - 1) / BN, m_tiles = (e.M + BM - 1) / BM;
+  const int num_tiles = n_tiles * m_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&accum_full[b], 1);
+      mbar_init(&accum_empty[b], 4);  // one arrival per epilogue warp
+    }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 2) {
+  if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"(TMEM_COLS)
                  : "memory");
@@ -151,97 +158,351 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  if (warp == 0 && lane == 0) {
-    // ---- TMA producer
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
-      if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
-        failed = 1;
-        break;
+  if (warp == 0) {
+    // ---- TMA producer: the ring runs on across tiles
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+            failed = 1;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          unsigned char* a_dst = smem + s * STAGE_BYTES;
+          tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+          tma_load_2d(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+        }
       }
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      unsigned char* a_dst = smem + s * STAGE_BYTES;
-      tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
-      tma_load_2d(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---- MMA issuer
-    const uint32_t idesc = umma_idesc();
-    bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
-      if (!mbar_wait(&full_bar[s], phase)) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc();
+      int it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have emptied this accumulator (two tiles ago)
+        if (!mbar_wait(&accum_empty[buf], ((local >> 1) & 1) ^ 1)) {
+          failed = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], phase)) {
+            failed = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // the next 16 k of a 128-byte swizzled row: 32 bytes further
+            umma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
+        }
+        if (failed) break;
+        umma_commit(&accum_full[buf]);
+      }
+    }
+  } else {
+    // ---- epilogue warps 2..5: warp w owns accumulator lanes 32 (w % 4) .. +31
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      // every lane waits (the barrier's completion orders its own reads); the warp decides as one
+      if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[buf], (local >> 1) & 1))) {
         failed = 1;
-        ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-      const uint32_t b_addr = a_addr + A_BYTES;
+      const int row = m0 + quarter * 32 + lane;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+        const int col = n0 + c0;
+        if (row < e.M && col < e.N) {
+          TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
+          const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
+          const int valid = min(32, e.N - col);
+          if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
 #pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k) {
-        // the next 16 k of a 128-byte swizzled row: 32 bytes further
-        umma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+            for (int j = 0; j < 4; ++j) {
+              uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
+              if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
+              const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
+              uint4 oraw;
+              bf16* ob = reinterpret_cast<bf16*>(&oraw);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                float x = __uint_as_float(v[j * 8 + t]);
+                if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
+                if (res) x += __bfloat162float(rb[t]);
+                ob[t] = __float2bfloat16(x);
+              }
+              reinterpret_cast<uint4*>(dst)[j] = oraw;
+            }
+          } else {
+            for (int t = 0; t < valid; ++t) {
+              float x = __uint_as_float(v[t]);
+              if (e.bias) x += __bfloat162float(e.bias[col + t]);
+              if (res) x += to_f32(res[t]);
+              dst[t] = from_f32<TOut>(x);
+            }
+          }
+        }
       }
-      umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
+      // the accumulator has been read: hand it back to the MMA thread
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
     }
-    if (ok) umma_commit(&accum_bar);
   }
-  __syncwarp();
 
-  // ---- epilogue: warp w owns accumulator lanes 32w..32w+31 = rows m0 + 32w + lane
-  bool ready = mbar_wait(&accum_bar, 0);
-  ready = __syncthreads_and(ready && !failed) != 0;  // one verdict for the whole CTA
-  if (!ready) {
+  __syncthreads();
+  if (failed) {
     if (threadIdx.x == 0) atomicOr(err, DSP_ERR_WAIT_LIMIT);
     // let copies that are still on their way land before the shared memory goes away
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
   tc_fence_after();
-  if (ready) {
-    const int row = m0 + warp * 32 + lane;
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      uint32_t v[32];
-      tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-      const int col = n0 + c0;
-      if (row < e.M && col < e.N) {
-        TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
-        const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
-        const int valid = min(32, e.N - col);
-        if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The same product on CTA pairs (cta_group::2): a cluster of two CTAs computes a 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and its own 128 rows (half) of the W tile, so a k block
+// costs 32 KB of shared-memory traffic per CTA instead of 48 KB and the ring is six stages deep;
+// the leader CTA's thread issues tcgen05.mma.cta_group::2 (M 256) for both, which reads the two
+// halves of the W tile from both CTAs' shared memory and writes each CTA's 128 rows into its own
+// tensor memory.  Both CTAs' TMA loads complete on the leader's "full" barrier; tcgen05.commit
+// with multicast frees the stage in both CTAs and announces the finished accumulator to both;
+// both CTAs' epilogue warps arrive on the leader's "accumulator empty" barrier.  No TMA load is
+// multicast.
+constexpr int STAGES2 = 6;
+constexpr int HALF_B_BYTES = (BN / 2) * BK * 2;
+constexpr int STAGE2_BYTES = A_BYTES + HALF_B_BYTES;  // 32 KB per CTA
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* leader_bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+        "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_on_leader(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(0u)
+      : "memory");
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_t (&v)[32], int row, int col) {
+  if (row >= e.M || col >= e.N) return;
+  TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
+  const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
+  const int valid = min(32, e.N - col);
+  if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
-            if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
-            const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
-            uint4 oraw;
-            bf16* ob = reinterpret_cast<bf16*>(&oraw);
+    for (int j = 0; j < 4; ++j) {
+      uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
+      if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
+      const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
+      uint4 oraw;
+      bf16* ob = reinterpret_cast<bf16*>(&oraw);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              float x = __uint_as_float(v[j * 8 + t]);
-              if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
-              if (res) x += __bfloat162float(rb[t]);
-              ob[t] = __float2bfloat16(x);
-            }
-            reinterpret_cast<uint4*>(dst)[j] = oraw;
-          }
-        } else {
-          for (int t = 0; t < valid; ++t) {
-            float x = __uint_as_float(v[t]);
-            if (e.bias) x += __bfloat162float(e.bias[col + t]);
-            if (res) x += to_f32(res[t]);
-            dst[t] = from_f32<TOut>(x);
-          }
-        }
+      for (int t = 0; t < 8; ++t) {
+        float x = __uint_as_float(v[j * 8 + t]);
+        if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
+        if (res) x += __bfloat162float(rb[t]);
+        ob[t] = __float2bfloat16(x);
       }
+      reinterpret_cast<uint4*>(dst)[j] = oraw;
     }
+  } else {
+    for (int t = 0; t < valid; ++t) {
+      float x = __uint_as_float(v[t]);
+      if (e.bias) x += __bfloat162float(e.bias[col + t]);
+      if (res) x += to_f32(res[t]);
+      dst[t] = from_f32<TOut>(x);
+    }
+  }
+}
+
+template <typename TOut>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const Epilogue e, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES2];   // used in the leader: both CTAs' loads land here
+  __shared__ __align__(8) uint64_t empty_bar[STAGES2];  // one per CTA, freed by the multicast commit
+  __shared__ __align__(8) uint64_t accum_full[2];       // one per CTA
+  __shared__ __align__(8) uint64_t accum_empty[2];      // used in the leader: 8 epilogue warps arrive
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int num_kb = (e.K + BK - 1) / BK;
+  const int n_tiles = (e.N + BN - 1) / BN, m_tiles = (e.M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = n_tiles * m_tiles;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&accum_full[b], 1);
+      mbar_init(&accum_empty[b], 8);
+    }
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
+        const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
+        const int w0 = (tile % n_tiles) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t phase = (it / STAGES2) & 1;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+            failed = 1;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE2_BYTES);
+          unsigned char* a_dst = smem + s * STAGE2_BYTES;
+          tma_load_2d_pair(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+          tma_load_2d_pair(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, w0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      uint32_t idesc = 0;
+      idesc |= 1u << 4;
+      idesc |= 1u << 7;
+      idesc |= 1u << 10;
+      idesc |= (uint32_t)(BN >> 3) << 17;
+      idesc |= (uint32_t)((2 * BM) >> 4) << 24;  // M 256 across the pair
+      int it = 0, local = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(&accum_empty[buf], ((local >> 1) & 1) ^ 1)) {
+          failed = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t phase = (it / STAGES2) & 1;
+          if (!mbar_wait(&full_bar[s], phase)) {
+            failed = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE2_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+          umma_commit_pair(&empty_bar[s]);
+        }
+        if (failed) break;
+        umma_commit_pair(&accum_full[buf]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM, n0 = (tile % n_tiles) * BN;
+      if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[buf], (local >> 1) & 1))) {
+        failed = 1;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+        store_row_chunk<TOut>(e, v, row, n0 + c0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_on_leader(&accum_empty[buf]);
+    }
+  }
+
+  __syncthreads();
+  if (failed) {
+    if (threadIdx.x == 0) atomicOr(err, DSP_ERR_WAIT_LIMIT);
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  cluster_sync_all();  // the peer is done with this CTA's shared memory and barriers
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -277,7 +538,7 @@ bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, in
 
 // bfloat16 A [M, K] (row stride lda) and W [N, K] (contiguous); C and residual bfloat16 or float32.
 extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const void* bias, const void* residual,
-                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype,
+                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int pair_mode,
                                 cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_tcgen05: K=%d and the row stride must be multiples of 8", K);
@@ -287,7 +548,8 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
   DSP_REQUIRE(err != nullptr, "dsp_gemm_tcgen05: no device error word");
   CUtensorMap map_a, map_w;
   DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
-  DSP_REQUIRE(make_map(&map_w, W, N, K, K, BN), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+  DSP_REQUIRE(make_map(&map_w, W, N, K, K, pair_mode ? BN / 2 : BN),
+              "dsp_gemm_tcgen05: cannot encode the tensor map of W");
   Epilogue e;
   e.bias = (const bf16*)bias;
   e.residual = residual;
@@ -298,8 +560,37 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
   e.N = N;
   e.K = K;
   const int smem = STAGES * STAGE_BYTES + 1024;
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  DSP_REQUIRE(grid.y <= 65535, "dsp_gemm_tcgen05: M=%d too large for one launch", M);
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    DSP_CUDA(cudaGetDevice(&dev));
+    DSP_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (pair_mode) {
+    const int smem2 = STAGES2 * STAGE2_BYTES + 1024;
+    const long tiles2 = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+    const long pairs = tiles2 < num_sms / 2 ? tiles2 : num_sms / 2;
+    dim3 grid2((unsigned)(2 * pairs));
+    if (out_dtype == DSP_BF16) {
+      static bool configured = false;
+      if (!configured) {
+        DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+        configured = true;
+      }
+      gemm_tcgen05_pair_kernel<bf16><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);
+    } else {
+      static bool configured = false;
+      if (!configured) {
+        DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+        configured = true;
+      }
+      gemm_tcgen05_pair_kernel<float><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);
+    }
+    DSP_CHECK_LAUNCH("dsp_gemm_tcgen05 (CTA pairs)");
+    return 0;
+  }
+  const long tiles = (long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  dim3 grid((unsigned)(tiles < num_sms ? tiles : num_sms));
   if (out_dtype == DSP_BF16) {
     static bool configured = false;
     if (!configured) {

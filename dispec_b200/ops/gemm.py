@@ -3,10 +3,11 @@
 float32: the FMA kernel (``dsp_gemm_simt``), always; no tensor cores, no reduced-precision
 mode, one FMA chain per output so that a row does not depend on its batch.
 bfloat16: the weight-streaming tensor-core kernel for up to 64 rows (decoding and the
-rows whose logits are wanted); above that, ``LARGE_BACKEND`` picks the tensor-core kernel
-of this package or the library matrix product (cuBLAS through torch.matmul), which is where
-the reference engine itself calls a library (puneethgv/DiSpec
-dispec/engine/model_runner.py:132,158,225-226,231).
+rows whose logits are wanted); above that the tcgen05/TMA kernel of this package
+(``LARGE_BACKEND = "tcgen05"``).  ``"library"`` selects the library matrix product instead
+(cuBLAS through torch.mm), which is where the reference engine itself calls a library
+(puneethgv/DiSpec dispec/engine/model_runner.py:132,158,225-226,231); it is kept for
+comparison and is not on the default path.
 """
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ from dispec_b200.ops import library as L
 
 SKINNY_MAX_ROWS = 64  # rows the weight-streaming kernel takes
 SKINNY_TARGET_CTAS = 148 * 2  # resident CTA slots a weight-streaming launch may fill by splitting K
-LARGE_BACKEND = "library"  # "tcgen05" | "library" | "simt"
+LARGE_BACKEND = "tcgen05"  # "tcgen05" | "library" | "simt"
 
 
 def _simt(x, w, bias, residual, out):
@@ -47,13 +48,16 @@ def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain
     return out
 
 
-def _tcgen05(x, w, bias, residual, out):
+TCGEN05_PAIRS = True  # CTA pairs (cta_group::2) for the tensor-core product
+
+
+def _tcgen05(x, w, bias, residual, out, pairs=None):
     M, K = x.shape
     N = w.shape[0]
     L.check(L.core().dsp_gemm_tcgen05(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
-        M, N, K, L.dtype_code(out.dtype), L.stream_handle()))
+        M, N, K, L.dtype_code(out.dtype), int(TCGEN05_PAIRS if pairs is None else pairs), L.stream_handle()))
     return out
 
 

@@ -529,3 +529,42 @@ def test_gemm_weight_streaming_with_fused_norm(M, N, K):
     out = gemm.linear(normed, w, residual=resid, out=resid)
     assert out.data_ptr() == resid.data_ptr()
     torch.testing.assert_close(out.double(), normed.double() @ w.double().T + r.double(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("pairs", [0, 1])
+@pytest.mark.parametrize("M,N,K,bias,resid,out_dtype", [
+    (128, 256, 64, False, False, torch.bfloat16),     # one tile, one k block
+    (65, 100, 96, True, False, torch.bfloat16),       # ragged in every direction, k tail of 32
+    (300, 777, 776, True, True, torch.bfloat16),
+    (2048, 2048, 1536, False, True, torch.bfloat16),  # more tiles than SMs: the ring runs across tiles
+    (257, 384, 224, False, False, torch.float32),     # 32-bit output (logits)
+    (1000, 8960, 1536, False, False, torch.bfloat16),
+])
+def test_gemm_tcgen05(pairs, M, N, K, bias, resid, out_dtype):
+    from dispec_b200.ops import gemm, library
+    x = rnd((M, K), torch.bfloat16, 51)
+    w = rnd((N, K), torch.bfloat16, 52, 0.1)
+    b = rnd((N,), torch.bfloat16, 53) if bias else None
+    r = rnd((M, N), out_dtype, 54) if resid else None
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev())
+    gemm._tcgen05(x, w, b, r, out, pairs=pairs)
+    assert library.device_error() == 0  # no bounded wait ran out
+    ref = x.double() @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if resid:
+        ref = ref + r.double()
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.double(), ref, atol=1e-3, rtol=1e-4)
+    else:
+        torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
+
+
+def test_gemm_tcgen05_rows_do_not_depend_on_the_batch_and_repeat_exactly():
+    from dispec_b200.ops import gemm
+    x = rnd((700, 1536), torch.bfloat16, 55)
+    w = rnd((2048, 1536), torch.bfloat16, 56, 0.05)
+    full = gemm.linear(x, w, backend="tcgen05")
+    assert torch.equal(full, gemm.linear(x, w, backend="tcgen05"))
+    part = gemm.linear(x[300:500].contiguous(), w, backend="tcgen05")
+    assert torch.equal(full[300:500], part)
