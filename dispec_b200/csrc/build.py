@@ -29,6 +29,7 @@ CORE_SOURCES = [
     "gemm_simt.cu",
     "gemm_skinny.cu",
     "gemm_tcgen05.cu",
+    "gemm_stream.cu",
     "attn_generic.cu",
     "attn_combine.cu",
     "sampling.cu",

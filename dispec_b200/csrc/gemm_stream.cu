@@ -1,0 +1,357 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for up to 64 rows of A, bfloat16 in, 32-bit
+// accumulation: the matrix product of decoding, bound by streaming W once from HBM, on TMA and
+// the fifth-generation tensor cores.
+//
+// Roles are swapped: 128 rows of W are the M side of tcgen05.mma, the few rows of A (padded to
+// 16, 32 or 64) its N side, so the accumulator in tensor memory is 128 lanes (rows of W) by a
+// few columns (rows of A).  One thread streams W tiles of 128 rows x 64 k (16 KB a request)
+// and the matching slice of A by TMA into a ring of 4 to 5 stages (two CTAs per SM, about 180 KB
+// on its way per SM, which plain loads cannot keep in flight); one thread issues the products; four warps read
+// the accumulator, apply the epilogue and store.  With programmatic dependent launch the first
+// W tiles are requested before the kernel waits for its predecessor.
+//
+// K is split across a thread-block cluster (up to 8 CTAs) when there are too few 128-row blocks
+// of W to fill the SMs: each CTA leaves its partial tile in shared memory and, after a cluster
+// barrier, adds its share over all ranks in rank order through distributed shared memory
+// (deterministic, no global scratch).  Without a split a CTA walks over several blocks of W and
+// the accumulator is double-buffered, so the epilogue of one block overlaps the next.
+//
+// Epilogues: bias[n], residual[m, n] (32-bit sum, rounded once), or SwiGLU over W rows that
+// alternate in blocks of 16 (16 gate rows, the 16 up rows of the same outputs): C is [M, N/2].
+// Every wait on an mbarrier is bounded; a wait that runs out is recorded in the device error word.
+#include <cooperative_groups.h>
+
+#include "tcgen05_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+using namespace tc;
+constexpr int ROWS_W = 128, BK = 64, UMMA_K = 16;
+constexpr int W_BYTES = ROWS_W * BK * 2;
+constexpr int THREADS = 192;  // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
+constexpr int MAX_SPLITS = 8;
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+
+template <int NB> struct Cfg {
+  static constexpr int X_BYTES = NB * BK * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  // about 100 KB of ring per CTA, so that two CTAs fit an SM: the next kernel's CTA (programmatic
+  // dependent launch) fills its ring with W while this kernel's CTA is still streaming
+  static constexpr int STAGES = NB == 16 ? 5 : NB == 32 ? 5 : 4;
+  static constexpr int TMEM_COLS = 2 * NB < 32 ? 32 : 2 * NB;
+};
+
+struct Args {
+  const bf16* bias;
+  const void* residual;
+  long ldr;
+  void* C;
+  long ldc;
+  int M, N, K;
+  int kb_per_split;
+  int epilogue;
+};
+
+template <typename TOut>
+__device__ __forceinline__ void finish(const Args& a, float v, int m, int n) {
+  if (a.bias) v += __bfloat162float(a.bias[n]);
+  if (a.residual) v += to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]);
+  reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>(v);
+}
+
+template <int NB, typename TOut>
+__global__ void __launch_bounds__(THREADS, 2)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const Args a, int* err) {
+  using C = Cfg<NB>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
+  __shared__ __align__(8) uint64_t accum_full[2];
+  __shared__ __align__(8) uint64_t accum_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int splits = gridDim.y, split = blockIdx.y;
+  const int n_blocks = (a.N + ROWS_W - 1) / ROWS_W;
+  const int kb_total = (a.K + BK - 1) / BK;
+  const int kb_begin = split * a.kb_per_split;
+  const int kb_end = min(kb_total, kb_begin + a.kb_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&accum_full[b], 1);
+      mbar_init(&accum_empty[b], 4);
+    }
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the CTA's work as one flat sequence of (block of W, k block) items
+      const int my_tiles = blockIdx.x < n_blocks ? (n_blocks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const int total = my_tiles * num_kb;
+      const int first = total < C::STAGES ? total : C::STAGES;
+      auto w_row = [&](int it) { return ((int)blockIdx.x + (it / num_kb) * (int)gridDim.x) * ROWS_W; };
+      auto k_of = [&](int it) { return (kb_begin + it % num_kb) * BK; };
+      // W does not depend on the kernel before this one: the ring is filled with W tiles first,
+      // then the kernel waits for its predecessor and sends the matching slices of A after them
+      for (int it = 0; it < first; ++it) {
+        mbar_expect_tx(&full_bar[it], C::STAGE_BYTES);
+        tma_load_2d(smem + it * C::STAGE_BYTES, &map_w, &full_bar[it], k_of(it), w_row(it));
+      }
+      pdl_wait();
+      for (int it = 0; it < first; ++it)
+        tma_load_2d(smem + it * C::STAGE_BYTES + W_BYTES, &map_x, &full_bar[it], k_of(it), 0);
+      for (int it = first; it < total; ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t phase = (it / C::STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+          failed = 1;
+          break;
+        }
+        mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+        unsigned char* dst = smem + s * C::STAGE_BYTES;
+        tma_load_2d(dst, &map_w, &full_bar[s], k_of(it), w_row(it));
+        tma_load_2d(dst + W_BYTES, &map_x, &full_bar[s], k_of(it), 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(ROWS_W, NB);
+      int it = 0, local = 0;
+      for (int nb = blockIdx.x; nb < n_blocks && !failed; nb += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(&accum_empty[buf], ((local >> 1) & 1) ^ 1)) {
+          failed = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * NB);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t phase = (it / C::STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], phase)) {
+            failed = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t x_addr = w_addr + W_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem_d, umma_desc(w_addr + k * 32), umma_desc(x_addr + k * 32), idesc, (kb | k) != 0);
+          umma_commit(&empty_bar[s]);
+        }
+        if (failed) break;
+        umma_commit(&accum_full[buf]);
+      }
+    }
+  }
+
+  // ---- epilogue.  Thread (quarter, lane) of warps 2..5 owns W row 32 * quarter + lane of the block.
+  const int quarter = warp & 3;
+  const int row = quarter * 32 + lane;
+  const bool swiglu = a.epilogue == EPI_SWIGLU;
+  if (splits == 1) {
+    if (warp >= 2) {
+      pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+      int local = 0;
+      for (int nb = blockIdx.x; nb < n_blocks; nb += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[buf], (local >> 1) & 1))) {
+          failed = 1;
+          break;
+        }
+        tc_fence_after();
+        uint32_t v[NB];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * NB);
+        if constexpr (NB == 16) {
+          tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(v));
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < NB; c0 += 32) tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
+        const int n = nb * ROWS_W + row;
+#pragma unroll
+        for (int m = 0; m < NB; ++m) {
+          const float x = __uint_as_float(v[m]);
+          if (swiglu) {
+            const float up = __shfl_down_sync(0xffffffffu, x, 16);
+            // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs
+            if (lane < 16 && m < a.M && n + 16 < a.N)
+              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
+                  from_f32<TOut>(x / (1.f + expf(-x)) * up);
+          } else if (m < a.M && n < a.N) {
+            finish<TOut>(a, x, m, n);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  } else {
+    // one block per CTA; the cluster adds the partial tiles
+    float* red = reinterpret_cast<float*>(smem);  // [NB][128], reuses the ring once it has drained
+    bool ok = true;
+    if (warp >= 2) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
+      if (!ok) failed = 1;
+      tc_fence_after();
+      if (ok) {
+        uint32_t v[NB];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if constexpr (NB == 16) {
+          tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(v));
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < NB; c0 += 32) tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+        }
+#pragma unroll
+        for (int m = 0; m < NB; ++m) red[m * ROWS_W + row] = __uint_as_float(v[m]);
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (warp >= 2 && !failed) {
+      pdl_wait();
+      const int rank = (int)cluster.block_rank();
+      const int n = blockIdx.x * ROWS_W + row;
+      for (int m = rank; m < a.M; m += splits) {
+        float total = 0.f, total_up = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+          const float* remote = cluster.map_shared_rank(red, sp);
+          total += remote[m * ROWS_W + row];
+          if (swiglu && lane < 16) total_up += remote[m * ROWS_W + row + 16];
+        }
+        if (swiglu) {
+          if (lane < 16 && n + 16 < a.N)
+            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
+                from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+        } else if (n < a.N) {
+          finish<TOut>(a, total, m, n);
+        }
+      }
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+  }
+
+  if (failed) {
+    if (threadIdx.x == 0) atomicOr(err, DSP_ERR_WAIT_LIMIT);
+    // let copies that are still on their way land before the shared memory goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+template <int NB, typename TOut>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, int n_blocks, int splits, int num_sms,
+           int* err, cudaStream_t stream) {
+  using C = Cfg<NB>;
+  const size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 1024;
+  auto kernel = gemm_stream_kernel<NB, TOut>;
+  static bool configured = false;
+  if (!configured) {
+    DSP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits > 1 ? n_blocks : (n_blocks < 2 * num_sms ? n_blocks : 2 * num_sms), splits, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = splits;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  DSP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, a, err));
+  return 0;
+}
+}  // namespace
+
+// epilogue: 0 plain (bias, residual allowed); 1 SwiGLU over W rows alternating in blocks of 16
+// (C is [M, N/2]; no bias, no residual).  target_ctas: SMs the launch may fill by splitting K.
+extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const void* bias, const void* residual,
+                               long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int target_ctas,
+                               int epilogue, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  DSP_REQUIRE(M <= 64, "dsp_gemm_stream: M=%d above 64 rows", M);
+  DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_stream: K=%d and the row stride must be multiples of 8", K);
+  DSP_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "dsp_gemm_stream: operands must be 16-byte aligned");
+  DSP_REQUIRE(out_dtype == DSP_BF16 || out_dtype == DSP_F32, "dsp_gemm_stream: unknown output dtype %d", out_dtype);
+  DSP_REQUIRE(epilogue == EPI_PLAIN || (N % 32 == 0 && bias == nullptr && residual == nullptr),
+              "dsp_gemm_stream: the SwiGLU epilogue needs N in whole blocks of 32 and no bias or residual");
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_gemm_stream: no device error word");
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    DSP_CUDA(cudaGetDevice(&dev));
+    DSP_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int nb_rows = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  CUtensorMap map_w, map_x;
+  DSP_REQUIRE(make_map(&map_w, W, N, K, K, ROWS_W), "dsp_gemm_stream: cannot encode the tensor map of W");
+  DSP_REQUIRE(make_map(&map_x, A, M, K, lda, nb_rows), "dsp_gemm_stream: cannot encode the tensor map of A");
+  const int n_blocks = (N + ROWS_W - 1) / ROWS_W;
+  const int kb_total = (K + BK - 1) / BK;
+  if (target_ctas <= 0) target_ctas = num_sms;
+  int splits = target_ctas / n_blocks;
+  if (splits < 1) splits = 1;
+  if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+  if (splits > kb_total) splits = kb_total;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per_split - 1) / kb_per_split;
+  Args a;
+  a.bias = (const bf16*)bias;
+  a.residual = residual;
+  a.ldr = ldr;
+  a.C = C;
+  a.ldc = ldc;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.kb_per_split = kb_per_split;
+  a.epilogue = epilogue;
+  if (out_dtype == DSP_BF16) {
+    if (nb_rows == 16) return launch<16, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+    if (nb_rows == 32) return launch<32, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+    return launch<64, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+  }
+  if (nb_rows == 16) return launch<16, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+  if (nb_rows == 32) return launch<32, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+  return launch<64, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+}

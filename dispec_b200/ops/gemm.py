@@ -88,6 +88,19 @@ def linear_rms_norm(x, gain, eps, w, bias=None, residual=None, out_dtype=None, o
     return _skinny(x, w, bias, residual, out, prologue=PRO_RMSNORM, gain=gain, eps=eps)
 
 
+STREAM_BACKEND = "tcgen05"  # weight streaming for up to 64 rows: "tcgen05" (TMA + tensor memory) | "mma"
+
+
+def _stream(x, w, bias, residual, out, epilogue=EPI_PLAIN, target_ctas=0):
+    M = x.shape[0]
+    N, K = w.shape
+    L.check(L.core().dsp_gemm_stream(
+        L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
+        L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
+        M, N, K, L.dtype_code(out.dtype), target_ctas, epilogue, L.stream_handle()))
+    return out
+
+
 def gate_up_swiglu_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     M, K = x.shape
     return x.dtype == torch.bfloat16 and skinny_supported(M, w.shape[0], K, x, w) and w.shape[0] % 32 == 0
@@ -104,6 +117,8 @@ def linear_gate_up_swiglu(x, w_interleaved, norm=None, out=None):
     if norm is not None:
         return _skinny(x, w_interleaved, None, None, out, prologue=PRO_RMSNORM, gain=norm[0], eps=norm[1],
                        epilogue=EPI_SWIGLU)
+    if STREAM_BACKEND == "tcgen05":
+        return _stream(x, w_interleaved, None, None, out, epilogue=EPI_SWIGLU)
     return _skinny(x, w_interleaved, None, None, out, epilogue=EPI_SWIGLU)
 
 
@@ -140,6 +155,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         else:
             backend = "simt"
     if backend == "skinny":
+        if STREAM_BACKEND == "tcgen05":
+            return _stream(x, w, bias, residual, out)
+        return _skinny(x, w, bias, residual, out)
+    if backend == "stream":
+        return _stream(x, w, bias, residual, out)
+    if backend == "mma":
         return _skinny(x, w, bias, residual, out)
     if backend == "tcgen05":
         if tcgen05_supported(x, w):

@@ -568,3 +568,50 @@ def test_gemm_tcgen05_rows_do_not_depend_on_the_batch_and_repeat_exactly():
     assert torch.equal(full, gemm.linear(x, w, backend="tcgen05"))
     part = gemm.linear(x[300:500].contiguous(), w, backend="tcgen05")
     assert torch.equal(full[300:500], part)
+
+
+@pytest.mark.parametrize("M,N,K,bias,resid,out_dtype,target", [
+    (8, 128, 64, False, False, torch.bfloat16, 0),       # one block, one k block
+    (1, 256, 1536, True, False, torch.bfloat16, 0),
+    (8, 2048, 1536, True, True, torch.bfloat16, 0),      # K split across a cluster
+    (16, 1536, 8960, False, True, torch.bfloat16, 148),
+    (13, 300, 96, True, True, torch.bfloat16, 0),        # ragged rows of W, k tail of 32
+    (40, 384, 776, False, False, torch.bfloat16, 0),     # 32 < M <= 64 columns
+    (64, 1000, 1536, True, False, torch.bfloat16, 0),
+    (5, 40000, 1536, False, False, torch.float32, 0),    # more blocks than CTAs: double-buffered accumulator
+])
+def test_gemm_stream_tcgen05(M, N, K, bias, resid, out_dtype, target):
+    from dispec_b200.ops import gemm, library
+    x = rnd((M, K), torch.bfloat16, 61)
+    w = rnd((N, K), torch.bfloat16, 62, 0.1)
+    b = rnd((N,), torch.bfloat16, 63) if bias else None
+    r = rnd((M, N), out_dtype, 64) if resid else None
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev())
+    gemm._stream(x, w, b, r, out, target_ctas=target)
+    assert library.device_error() == 0
+    ref = x.double() @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if resid:
+        ref = ref + r.double()
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.double(), ref, atol=1e-3, rtol=1e-4)
+    else:
+        torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
+    again = torch.empty_like(out)
+    gemm._stream(x, w, b, r, again, target_ctas=target)
+    assert torch.equal(out, again)  # the cluster sum runs in a fixed order
+
+
+@pytest.mark.parametrize("M,I,K,target", [(8, 8960, 1536, 0), (3, 224, 96, 148), (33, 2048, 1536, 0), (64, 176, 80, 0)])
+def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
+    from dispec_b200.ops import gemm, library
+    x = rnd((M, K), torch.bfloat16, 65)
+    wg, wu = rnd((I, K), torch.bfloat16, 66, 0.15), rnd((I, K), torch.bfloat16, 67, 0.15)
+    b = gemm.SWIGLU_BLOCK
+    w = torch.stack([wg.view(I // b, b, K), wu.view(I // b, b, K)], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=dev())
+    gemm._stream(x, w, None, None, out, epilogue=gemm.EPI_SWIGLU, target_ctas=target)
+    assert library.device_error() == 0
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
