@@ -47,7 +47,7 @@ struct Params {
   long out_stride;
   float* part_o;   // [(t * H + h) * splits + split][D]
   float* part_ml;  // [(t * H + h) * splits + split][2]
-  int H, KVH, G, tokens_per_tile, page_size, num_pages, window, num_splits;
+  int H, KVH, G, tokens_per_tile, page_size, page_shift, num_pages, window, num_splits;
   float scale_log2;
   int* err;
 };
@@ -96,7 +96,8 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
-  const int tile = blockIdx.x + tile_offset, kvh = blockIdx.y, split = blockIdx.z;
+  // later tiles of a prompt see more keys: the longest work is scheduled first
+  const int tile = ((int)gridDim.x - 1 - (int)blockIdx.x) + tile_offset, kvh = blockIdx.y, split = blockIdx.z;
   const int seq = p.tile_seq[tile], tok0 = p.tile_tok0[tile];
   const int qs = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - qs;
@@ -114,34 +115,38 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
   const int my_end = min(kt_end, my_begin + per);
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
 
-  // ---- Q tile
-  for (int i = tid; i < BM * CHUNKS; i += THREADS) {
-    const int row = i / CHUNKS, chunk = i % CHUNKS;
-    const bool valid = row < nrows;
+  // ---- Q tile: two threads per row
+  {
+    const int r = tid >> 1, half = tid & 1;
+    const bool valid = r < nrows;
     const bf16* src = p.q;
-    if (valid)
-      src = p.q + (size_t)(qs + tok0 + row / G) * p.q_stride + (size_t)(kvh * G + row % G) * D + chunk * 8;
-    cp_async16(q_s + sw(row, chunk), src, valid);
+    if (valid) src = p.q + (size_t)(qs + tok0 + r / G) * p.q_stride + (size_t)(kvh * G + r % G) * D;
+#pragma unroll
+    for (int chunk = half; chunk < CHUNKS; chunk += 2) cp_async16(q_s + sw(r, chunk), src + chunk * 8, valid);
+    cp_async_commit();
   }
-  cp_async_commit();
 
+  // two threads per key row: one page lookup per thread and tile, then 16-byte pieces of the row
   auto load_kv = [&](int kt, int buf) {
-    for (int i = tid; i < BN * CHUNKS; i += THREADS) {
-      const int r = i / CHUNKS, chunk = i % CHUNKS;
-      const int b = kt * BN + r;
-      bool valid = b < ctx && b <= pos_last;
-      size_t off = 0;
-      if (valid) {
-        const int page = table[b / p.page_size];
-        if (page < 0 || page >= p.num_pages) {
-          if (b >= lo && chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          valid = false;
-        } else {
-          off = (((size_t)page * p.KVH + kvh) * p.page_size + (b % p.page_size)) * D + chunk * 8;
-        }
+    const int r = tid >> 1, half = tid & 1;
+    const int b = kt * BN + r;
+    bool valid = b < ctx && b <= pos_last;
+    size_t off = 0;
+    if (valid) {
+      const int lp = p.page_shift >= 0 ? (b >> p.page_shift) : (b / p.page_size);
+      const int within = p.page_shift >= 0 ? (b & (p.page_size - 1)) : (b % p.page_size);
+      const int page = table[lp];
+      if (page < 0 || page >= p.num_pages) {
+        if (b >= lo && half == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        valid = false;
+      } else {
+        off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D;
       }
-      cp_async16(k_s[buf] + sw(r, chunk), p.k_pool + off, valid);
-      cp_async16(v_s[buf] + sw(r, chunk), p.v_pool + off, valid);
+    }
+#pragma unroll
+    for (int chunk = half; chunk < CHUNKS; chunk += 2) {
+      cp_async16(k_s[buf] + sw(r, chunk), p.k_pool + off + chunk * 8, valid);
+      cp_async16(v_s[buf] + sw(r, chunk), p.v_pool + off + chunk * 8, valid);
     }
     cp_async_commit();
   };
@@ -316,6 +321,7 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   p.G = H / KVH;
   p.tokens_per_tile = tokens_per_tile;
   p.page_size = page_size;
+  p.page_shift = (page_size > 0 && (page_size & (page_size - 1)) == 0) ? __builtin_ctz(page_size) : -1;
   p.num_pages = num_pages;
   p.window = window;
   p.num_splits = num_splits;

@@ -22,7 +22,10 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 columns
 constexpr int THREADS = 192;    // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
 
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+
 struct Epilogue {
+  int epilogue;
   const bf16* bias;
   const void* residual;
   long ldr;
@@ -30,6 +33,63 @@ struct Epilogue {
   long ldc;
   int M, N, K;
 };
+
+template <typename TOut>
+__device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_t (&v)[32], int row, int col) {
+  if (row >= e.M || col >= e.N) return;
+  if (e.epilogue == EPI_SWIGLU) {
+    // W rows alternate in blocks of 16: this chunk holds 16 gates and the 16 ups of the same outputs
+    if (col + 32 > e.N) return;
+    TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + (col >> 1);
+    if (sizeof(TOut) == 2 && ((uintptr_t)dst % 16) == 0) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint4 oraw;
+        bf16* ob = reinterpret_cast<bf16*>(&oraw);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float g = __uint_as_float(v[j * 8 + t]), u = __uint_as_float(v[16 + j * 8 + t]);
+          ob[t] = __float2bfloat16(g / (1.f + expf(-g)) * u);
+        }
+        reinterpret_cast<uint4*>(dst)[j] = oraw;
+      }
+    } else {
+      for (int t = 0; t < 16; ++t) {
+        const float g = __uint_as_float(v[t]), u = __uint_as_float(v[16 + t]);
+        dst[t] = from_f32<TOut>(g / (1.f + expf(-g)) * u);
+      }
+    }
+    return;
+  }
+  TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
+  const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
+  const int valid = min(32, e.N - col);
+  if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
+      if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
+      const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
+      uint4 oraw;
+      bf16* ob = reinterpret_cast<bf16*>(&oraw);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        float x = __uint_as_float(v[j * 8 + t]);
+        if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
+        if (res) x += __bfloat162float(rb[t]);
+        ob[t] = __float2bfloat16(x);
+      }
+      reinterpret_cast<uint4*>(dst)[j] = oraw;
+    }
+  } else {
+    for (int t = 0; t < valid; ++t) {
+      float x = __uint_as_float(v[t]);
+      if (e.bias) x += __bfloat162float(e.bias[col + t]);
+      if (res) x += to_f32(res[t]);
+      dst[t] = from_f32<TOut>(x);
+    }
+  }
+}
 
 template <typename TOut>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -145,37 +205,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
-        const int col = n0 + c0;
-        if (row < e.M && col < e.N) {
-          TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
-          const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
-          const int valid = min(32, e.N - col);
-          if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
-              if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
-              const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
-              uint4 oraw;
-              bf16* ob = reinterpret_cast<bf16*>(&oraw);
-#pragma unroll
-              for (int t = 0; t < 8; ++t) {
-                float x = __uint_as_float(v[j * 8 + t]);
-                if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
-                if (res) x += __bfloat162float(rb[t]);
-                ob[t] = __float2bfloat16(x);
-              }
-              reinterpret_cast<uint4*>(dst)[j] = oraw;
-            }
-          } else {
-            for (int t = 0; t < valid; ++t) {
-              float x = __uint_as_float(v[t]);
-              if (e.bias) x += __bfloat162float(e.bias[col + t]);
-              if (res) x += to_f32(res[t]);
-              dst[t] = from_f32<TOut>(x);
-            }
-          }
-        }
+        store_row_chunk<TOut>(e, v, row, n0 + c0);
       }
       // the accumulator has been read: hand it back to the MMA thread
       tc_fence_before();
@@ -250,39 +280,6 @@ __device__ __forceinline__ void mbar_arrive_on_leader(uint64_t* bar) {
       "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}"
       ::"r"(smem_u32(bar)), "r"(0u)
       : "memory");
-}
-
-template <typename TOut>
-__device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_t (&v)[32], int row, int col) {
-  if (row >= e.M || col >= e.N) return;
-  TOut* dst = reinterpret_cast<TOut*>(e.C) + (size_t)row * e.ldc + col;
-  const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
-  const int valid = min(32, e.N - col);
-  if (valid == 32 && sizeof(TOut) == 2 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 rraw = make_uint4(0u, 0u, 0u, 0u);
-      if (res) rraw = reinterpret_cast<const uint4*>(res)[j];
-      const bf16* rb = reinterpret_cast<const bf16*>(&rraw);
-      uint4 oraw;
-      bf16* ob = reinterpret_cast<bf16*>(&oraw);
-#pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        float x = __uint_as_float(v[j * 8 + t]);
-        if (e.bias) x += __bfloat162float(e.bias[col + j * 8 + t]);
-        if (res) x += __bfloat162float(rb[t]);
-        ob[t] = __float2bfloat16(x);
-      }
-      reinterpret_cast<uint4*>(dst)[j] = oraw;
-    }
-  } else {
-    for (int t = 0; t < valid; ++t) {
-      float x = __uint_as_float(v[t]);
-      if (e.bias) x += __bfloat162float(e.bias[col + t]);
-      if (res) x += to_f32(res[t]);
-      dst[t] = from_f32<TOut>(x);
-    }
-  }
 }
 
 template <typename TOut>
@@ -419,9 +416,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }  // namespace
 
 // bfloat16 A [M, K] (row stride lda) and W [N, K] (contiguous); C and residual bfloat16 or float32.
+// epilogue 1: SwiGLU over W rows alternating in blocks of 16 (16 gate rows, their 16 up rows):
+// C is [M, N/2], no bias, no residual.
 extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const void* bias, const void* residual,
                                 long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int pair_mode,
-                                cudaStream_t stream) {
+                                int epilogue, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_tcgen05: K=%d and the row stride must be multiples of 8", K);
   DSP_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "dsp_gemm_tcgen05: operands must be 16-byte aligned");
@@ -432,7 +431,10 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
   DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
   DSP_REQUIRE(make_map(&map_w, W, N, K, K, pair_mode ? BN / 2 : BN),
               "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+  DSP_REQUIRE(epilogue == EPI_PLAIN || (N % 32 == 0 && bias == nullptr && residual == nullptr),
+              "dsp_gemm_tcgen05: the SwiGLU epilogue needs N in whole blocks of 32 and no bias or residual");
   Epilogue e;
+  e.epilogue = epilogue;
   e.bias = (const bf16*)bias;
   e.residual = residual;
   e.ldr = ldr;

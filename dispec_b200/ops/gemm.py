@@ -51,13 +51,14 @@ def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain
 TCGEN05_PAIRS = True  # CTA pairs (cta_group::2) for the tensor-core product
 
 
-def _tcgen05(x, w, bias, residual, out, pairs=None):
+def _tcgen05(x, w, bias, residual, out, pairs=None, epilogue=0):
     M, K = x.shape
     N = w.shape[0]
     L.check(L.core().dsp_gemm_tcgen05(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
-        M, N, K, L.dtype_code(out.dtype), int(TCGEN05_PAIRS if pairs is None else pairs), L.stream_handle()))
+        M, N, K, L.dtype_code(out.dtype), int(TCGEN05_PAIRS if pairs is None else pairs), epilogue,
+        L.stream_handle()))
     return out
 
 
@@ -102,8 +103,13 @@ def _stream(x, w, bias, residual, out, epilogue=EPI_PLAIN, target_ctas=0):
 
 
 def gate_up_swiglu_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether silu(gate) * up can be formed in the epilogue of the gate/up product."""
     M, K = x.shape
-    return x.dtype == torch.bfloat16 and skinny_supported(M, w.shape[0], K, x, w) and w.shape[0] % 32 == 0
+    if x.dtype != torch.bfloat16 or w.shape[0] % 32:
+        return False
+    if M <= SKINNY_MAX_ROWS:
+        return skinny_supported(M, w.shape[0], K, x, w)
+    return LARGE_BACKEND == "tcgen05" and tcgen05_supported(x, w)
 
 
 def linear_gate_up_swiglu(x, w_interleaved, norm=None, out=None):
@@ -114,6 +120,9 @@ def linear_gate_up_swiglu(x, w_interleaved, norm=None, out=None):
     M, N = x.shape[0], w_interleaved.shape[0]
     if out is None:
         out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
+    if M > SKINNY_MAX_ROWS:
+        assert norm is None
+        return _tcgen05(x, w_interleaved, None, None, out, epilogue=EPI_SWIGLU)
     if norm is not None:
         return _skinny(x, w_interleaved, None, None, out, prologue=PRO_RMSNORM, gain=norm[0], eps=norm[1],
                        epilogue=EPI_SWIGLU)

@@ -42,7 +42,8 @@ class SwiGLUFeedForward(FeedForward):
         """``pre_norm``: x is not normalised yet, the norm is applied on the way into the first
         product.  ``residual``: added by the last product, so that the sum comes back."""
         norm = pre_norm.as_linear_prologue() if pre_norm is not None else None
-        if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up):
+        if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up) and (
+                norm is None or x.shape[0] <= gemm_ops.FUSED_MAX_ROWS):
             act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up, norm)
         else:
             if norm is not None:

@@ -421,7 +421,8 @@ def test_gemm_weight_streaming_with_fused_norm(M, N, K):
     torch.testing.assert_close(logits.double(), normed.double() @ w.double().T, atol=3e-3, rtol=3e-3)
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 64, 96), (8, 8960, 1536), (13, 176, 80), (40, 224, 96), (64, 512, 776)])
+@pytest.mark.parametrize("M,I,K", [(1, 64, 96), (8, 8960, 1536), (13, 176, 80), (40, 224, 96), (64, 512, 776),
+                                   (300, 512, 776), (2048, 1024, 1536)])
 def test_gate_up_product_with_swiglu_epilogue(M, I, K):
     from dispec_b200 import ops
     from dispec_b200.ops import gemm
