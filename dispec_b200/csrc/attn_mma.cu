@@ -7,13 +7,20 @@
 // (cp.async, two stages).  S = Q K^T and O += P V are mma.m16n8k16; the softmax is the online
 // form (running max and sum per row, base 2).  The query at position p sees keys b with
 // max(0, p - window + 1) <= b <= p.  With num_splits > 1 the key tiles of a query tile are
-// divided among grid.z CTAs, each writing an unnormalised partial (o, m, l) per row; a second
-// kernel (dsp_attn_combine) merges them.
+// divided among grid.z CTAs, each producing an unnormalised partial (o, m, l) per row.  With up to
+// 8 splits those CTAs form a thread-block cluster and merge their partials through distributed
+// shared memory (each CTA finishes a share of the rows, reading every rank's partial in rank
+// order); with more splits the partials go to global scratch and a second kernel
+// (dsp_attn_combine) merges them.
 //
 // Shared memory rows are 16-byte pieces XOR-swizzled by the row index, so ldmatrix reads are
 // conflict-free for head sizes of 64 and above.  Keys at or beyond the sequence length, and keys
 // on pages that were given back, are zero-filled, never read.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 #ifndef DSP_HEAD_DIM
 #error "compile with -DDSP_HEAD_DIM=<head size>"
@@ -48,6 +55,7 @@ struct Params {
   float* part_o;   // [(t * H + h) * splits + split][D]
   float* part_ml;  // [(t * H + h) * splits + split][2]
   int H, KVH, G, tokens_per_tile, page_size, page_shift, num_pages, window, num_splits;
+  int cluster_combine;  // the splits of a tile are one cluster and merge on chip
   float scale_log2;
   int* err;
 };
@@ -257,6 +265,60 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
+  if (p.cluster_combine) {
+    // partials of this CTA into its shared memory (the key/value tiles are no longer needed)
+    __syncthreads();
+    float* part_o = reinterpret_cast<float*>(smem);            // [64][D]
+    float* part_ml = part_o + BM * D;                          // [64][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r == 0 ? row0 : row1;
+      if (row < nrows) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<float2*>(part_o + row * D + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+        if (c4 == 0) {
+          part_ml[row * 2] = m_run[r];
+          part_ml[row * 2 + 1] = l_run[r];
+        }
+      }
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rank = (int)cluster.block_rank(), nsplit = p.num_splits;
+    // rows are dealt to the CTAs of the cluster; a warp finishes one row at a time
+    for (int row = rank * 4 + warp; row < nrows; row += nsplit * 4) {
+      float M = -INFINITY;
+      for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, cluster.map_shared_rank(part_ml, sp)[row * 2]);
+      float L = 0.f;
+      float acc[(D + 31) / 32];
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) acc[j] = 0.f;
+      for (int sp = 0; sp < nsplit; ++sp) {
+        const float* ml = cluster.map_shared_rank(part_ml, sp);
+        const float m = ml[row * 2];
+        if (m == -INFINITY) continue;
+        const float w = exp2f(m - M);
+        L += w * ml[row * 2 + 1];
+        const float* po = cluster.map_shared_rank(part_o, sp) + row * D;
+#pragma unroll
+        for (int j = 0; j < (D + 31) / 32; ++j) {
+          const int d = lane + 32 * j;
+          if (d < D) acc[j] += w * po[d];
+        }
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      const size_t t = (size_t)qs + tok0 + row / G;
+      bf16* dst = p.out + t * p.out_stride + (size_t)(kvh * G + row % G) * D;
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) dst[d] = __float2bfloat16(acc[j] * inv);
+      }
+    }
+    cluster.sync();  // nobody leaves while its partials may still be read
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = r == 0 ? row0 : row1;
@@ -284,6 +346,230 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
     }
   }
 }
+
+// ------------------------------------------------------------------------------------------
+// Single decoded tokens (the G rows of one KV head fit one 16-row mma tile): the key tiles of a
+// sequence are spread over the CTAs of a cluster (grid.z) and, inside a CTA, over its four warps,
+// each warp loading and processing whole 64-key tiles on its own (private shared memory, no CTA
+// barrier in the loop).  With 8 CTAs a context of 2048 keys is one tile per warp: one load
+// latency, one tile of arithmetic, then the 4 x grid.z partials are merged through distributed
+// shared memory, a row per warp.
+constexpr int DBN = 32;  // keys per warp tile: small enough that two or three CTAs share an SM and
+                        // every cluster of the launch is resident at once
+constexpr int DEC_Q_BYTES = 16 * ROW_BYTES;
+constexpr int DEC_TILE_BYTES = DBN * ROW_BYTES;
+constexpr int DEC_PART_BYTES = (16 * D + 32) * 4;  // a warp's partial: [16][D] outputs and [16][2] (m, l)
+constexpr int DEC_WARP_BYTES = 2 * DEC_TILE_BYTES > DEC_PART_BYTES ? 2 * DEC_TILE_BYTES : DEC_PART_BYTES;
+constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES;
+
+__global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g4 = lane >> 2, c4 = lane & 3;
+  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  const int seq = p.tile_seq[tile];
+  const int qs = p.q_start[seq];
+  const int ctx = p.ctx_len[seq];
+  if (ctx <= 0) return;  // a padding row: the whole cluster leaves
+  const int G = p.G;
+  const int pos = ctx - 1;
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int kt_begin = lo / DBN, kt_end = pos / DBN + 1;
+  const int per = (kt_end - kt_begin + nsplit - 1) / nsplit;
+  const int my_begin = kt_begin + split * per;
+  const int my_end = min(kt_end, my_begin + per);
+  const int* table = p.page_table + (size_t)seq * p.pt_stride;
+  const uint32_t q_s = s_base;
+  const uint32_t k_s = s_base + DEC_Q_BYTES + warp * DEC_WARP_BYTES, v_s = k_s + DEC_TILE_BYTES;
+
+  // Q: the G heads of this KV head, one row each
+  for (int i = tid; i < 16 * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, chunk = i % CHUNKS;
+    const bool valid = r < G;
+    const bf16* src = valid ? p.q + (size_t)qs * p.q_stride + (size_t)(kvh * G + r) * D + chunk * 8 : p.q;
+    cp_async16(q_s + sw(r, chunk), src, valid);
+  }
+  cp_async_commit();
+
+  auto load_tile = [&](int kt) {  // by one warp: consecutive lanes take consecutive 16-byte pieces of a row
+#pragma unroll 4
+    for (int i = lane; i < DBN * CHUNKS; i += 32) {
+      const int r = i / CHUNKS, chunk = i % CHUNKS;
+      const int b = kt * DBN + r;
+      bool valid = b <= pos;
+      size_t off = 0;
+      if (valid) {
+        const int lp = p.page_shift >= 0 ? (b >> p.page_shift) : (b / p.page_size);
+        const int within = p.page_shift >= 0 ? (b & (p.page_size - 1)) : (b % p.page_size);
+        const int page = table[lp];
+        if (page < 0 || page >= p.num_pages) {
+          if (b >= lo && chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          valid = false;
+        } else {
+          off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D + chunk * 8;
+        }
+      }
+      cp_async16(k_s + sw(r, chunk), p.k_pool + off, valid);
+      cp_async16(v_s + sw(r, chunk), p.v_pool + off, valid);
+    }
+    cp_async_commit();
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const bool row_ok[2] = {g4 < G, g4 + 8 < G};
+
+  const int first = my_begin + warp;
+  if (first < my_end) load_tile(first);
+  cp_async_wait<0>();
+  __syncthreads();  // Q is complete for every warp
+  const int m8 = lane >> 3, l8 = lane & 7;
+  for (int kt = first; kt < my_end; kt += 4) {
+    if (kt != first) {
+      __syncwarp();
+      load_tile(kt);
+      cp_async_wait<0>();
+      __syncwarp();
+    }
+    float s[DBN / 8][4];
+#pragma unroll
+    for (int i = 0; i < DBN / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + sw((m8 & 1) * 8 + l8, kk * 2 + (m8 >> 1)));
+#pragma unroll
+      for (int nn = 0; nn < DBN / 16; ++nn) {
+        uint32_t b[4];
+        ldmatrix_x4(b, k_s + sw(nn * 16 + (m8 >> 1) * 8 + l8, kk * 2 + (m8 & 1)));
+        mma_bf16(s[2 * nn], a, b[0], b[1]);
+        mma_bf16(s[2 * nn + 1], a, b[2], b[3]);
+      }
+    }
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < DBN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int key = kt * DBN + nt * 8 + 2 * c4 + (e & 1);
+        const bool vis = row_ok[r] && key <= pos && key >= lo;
+        const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][e] = v;
+        tmax[r] = fmaxf(tmax[r], v);
+      }
+    float alpha[2], m_safe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      const float m_new = fmaxf(m_run[r], tmax[r]);
+      m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_safe[r]);
+      m_run[r] = m_new;
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < DBN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = exp2f(s[nt][e] - m_safe[e >> 1]);
+        s[nt][e] = pv;
+        l_run[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int j = 0; j < DBN / 16; ++j) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+      a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+      a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+      a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+      for (int dd = 0; dd < D / 16; ++dd) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_s + sw(j * 16 + (m8 & 1) * 8 + l8, dd * 2 + (m8 >> 1)));
+        mma_bf16(o[2 * dd], a, b[0], b[1]);
+        mma_bf16(o[2 * dd + 1], a, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  // the warp's partial over its own tiles, in its own (now free) tile memory: [16][D] and [16][2]
+  __syncwarp();
+  float* part_o = reinterpret_cast<float*>(smem + DEC_Q_BYTES + warp * DEC_WARP_BYTES);
+  float* part_ml = part_o + 16 * D;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g4 + 8 * r;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+      *reinterpret_cast<float2*>(part_o + row * D + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+    if (c4 == 0) {
+      part_ml[row * 2] = m_run[r];
+      part_ml[row * 2 + 1] = l_run[r];
+    }
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  float* base0 = reinterpret_cast<float*>(smem + DEC_Q_BYTES);
+  const int np = nsplit * 4;  // partials of a row: one per warp of the cluster (at most 32)
+  // lane i looks at partial i (CTA i / 4, warp i % 4): one round of remote reads for all (m, l)
+  const float* mine = nullptr;
+  if (lane < np) mine = cluster.map_shared_rank(base0, lane >> 2) + (lane & 3) * (DEC_WARP_BYTES / 4);
+  for (int row = split * 4 + warp; row < G; row += nsplit * 4) {
+    float m_i = -INFINITY, l_i = 0.f;
+    if (mine) {
+      m_i = mine[16 * D + row * 2];
+      l_i = mine[16 * D + row * 2 + 1];
+    }
+    const float M = warp_max(m_i);
+    const float w_i = (m_i == -INFINITY) ? 0.f : exp2f(m_i - M);
+    const float L = warp_sum(w_i * l_i);
+    float acc[(D + 31) / 32];
+#pragma unroll
+    for (int j = 0; j < (D + 31) / 32; ++j) acc[j] = 0.f;
+    // the weights are known: the reads of the partial outputs do not depend on one another
+#pragma unroll 4
+    for (int i = 0; i < np; ++i) {
+      const float wgt = __shfl_sync(0xffffffffu, w_i, i);
+      if (wgt == 0.f) continue;  // a warp that had no tile
+      const float* po = cluster.map_shared_rank(base0, i >> 2) + (i & 3) * (DEC_WARP_BYTES / 4) + row * D;
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) acc[j] += wgt * po[d];
+      }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
+#pragma unroll
+    for (int j = 0; j < (D + 31) / 32; ++j) {
+      const int d = lane + 32 * j;
+      if (d < D) dst[d] = __float2bfloat16(acc[j] * inv);
+    }
+  }
+  cluster.sync();  // nobody leaves while its partials may still be read
+}
 }  // namespace
 
 // Runs tiles [tile_offset, tile_offset + num_tiles) of the tile list.  With num_splits > 1 the
@@ -293,11 +579,12 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     int pt_stride, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0,
     int tile_offset, int num_tiles, void* out, long out_stride, float* part_o, float* part_ml, int H,
     int KVH, int tokens_per_tile, int page_size, int num_pages, int window, int num_splits,
-    float scale, int* err, cudaStream_t stream) {
+    int cluster_combine, int decode_only, float scale, int* err, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (KVH <= 0 || H % KVH != 0 || (H / KVH) * tokens_per_tile > BM || tokens_per_tile < 1) return 2;
   if (num_splits < 1 || num_splits > 65535 || KVH > 65535) return 2;
-  if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return 2;
+  if (num_splits > 1 && !cluster_combine && (part_o == nullptr || part_ml == nullptr)) return 2;
+  if (cluster_combine && !decode_only && (num_splits < 2 || num_splits > 8)) return 2;
   if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) ||
       ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4))
     return 3;
@@ -325,6 +612,7 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   p.num_pages = num_pages;
   p.window = window;
   p.num_splits = num_splits;
+  p.cluster_combine = cluster_combine;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = err;
   const int smem = 5 * TILE_BYTES;
@@ -335,5 +623,49 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     configured = true;
   }
   dim3 grid(num_tiles, KVH, num_splits);
+  // single decoded tokens whose group fits one 16-row tile: the warp-parallel kernel
+  if (decode_only && p.G <= 16 && num_splits <= 8 && DEC_SMEM <= 227 * 1024) {
+    static bool dec_configured = false;
+    if (!dec_configured) {
+      if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM) != cudaSuccess)
+        return 4;
+      dec_configured = true;
+    }
+    if (tile_offset != 0) return 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = (size_t)DEC_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = num_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    prefer_max_shared(reinterpret_cast<const void*>(attn_decode_kernel));
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel, p) == cudaSuccess ? 0 : 1;
+  }
+  if (cluster_combine) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = num_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    prefer_max_shared(reinterpret_cast<const void*>(attn_mma_kernel));
+    return cudaLaunchKernelEx(&cfg, attn_mma_kernel, p, tile_offset) == cudaSuccess ? 0 : 1;
+  }
   return launch_pdl(attn_mma_kernel, grid, dim3(THREADS), (size_t)smem, stream, p, tile_offset) == cudaSuccess ? 0 : 1;
 }

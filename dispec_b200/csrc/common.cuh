@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 enum DspDtype { DSP_F32 = 0, DSP_BF16 = 1 };
 
@@ -61,9 +62,32 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// DISPEC_B200_PDL=0 in the environment switches the launch attribute off (for measurements).
+inline bool pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* v = getenv("DISPEC_B200_PDL");
+    state = (v != nullptr && v[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
+}
+
+// Asks, once per kernel, for the largest shared-memory carveout.  The kernels of a step differ
+// widely in the shared memory they use; with one carveout for all of them the SMs are not
+// reconfigured between consecutive kernels.
+inline void prefer_max_shared(const void* kernel) {
+  static const void* seen[128];
+  static int count = 0;
+  for (int i = 0; i < count; ++i)
+    if (seen[i] == kernel) return;
+  if (count < 128) seen[count++] = kernel;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -71,7 +95,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);

@@ -95,6 +95,8 @@ rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __re
                    int write_back) {
   constexpr int N = Vec16<T>::N;
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t in_row = rows ? (size_t)rows[r] : (size_t)r;
   const int nvec = hidden / N;
@@ -159,11 +161,11 @@ static bool launch_rmsnorm_vec(void* x, const void* delta, const void* w, void* 
   if (bits % 16 != 0) return false;
   const int nvec = hidden / N;
   if (nvec <= 256)
-    rmsnorm_vec_kernel<T, 1><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+    launch_pdl(rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(256), 0, stream, (T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
   else if (nvec <= 512)
-    rmsnorm_vec_kernel<T, 2><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+    launch_pdl(rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(256), 0, stream, (T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
   else if (nvec <= 1024)
-    rmsnorm_vec_kernel<T, 4><<<n_rows, 256, 0, stream>>>((T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
+    launch_pdl(rmsnorm_vec_kernel<T, 4>, dim3(n_rows), dim3(256), 0, stream, (T*)x, (const T*)delta, (const T*)w, (T*)y, rows, hidden, eps, write_back);
   else
     return false;
   return true;
@@ -222,6 +224,8 @@ __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs,
                   int block) {
   constexpr int N = Vec16<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = inter / N;
   const int up_off = block ? block : inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
@@ -256,9 +260,9 @@ extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int 
     const size_t total = (size_t)T * (inter / N);
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
     if (dtype == DSP_F32)
-      swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, block);
+      launch_pdl(swiglu_vec_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, inter, total, block);
     else
-      swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total, block);
+      launch_pdl(swiglu_vec_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total, block);
     DSP_CHECK_LAUNCH("dsp_swiglu");
     return 0;
   }

@@ -363,9 +363,10 @@ int launch(const Args& a, int splits, cudaStream_t stream) {
   attr[0].val.clusterDim.y = splits;
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   DSP_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
   return 0;
 }

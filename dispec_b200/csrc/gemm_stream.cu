@@ -294,9 +294,10 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, in
   attr[0].val.clusterDim.y = splits;
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   DSP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, a, err));
   return 0;
 }

@@ -461,6 +461,7 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
         DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
         configured = true;
       }
+      prefer_max_shared(reinterpret_cast<const void*>(gemm_tcgen05_pair_kernel<bf16>));
       gemm_tcgen05_pair_kernel<bf16><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);
     } else {
       static bool configured = false;

@@ -47,6 +47,9 @@ _MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
                3: "operands must be 16-byte aligned with strides in whole 16-byte pieces",
                4: "shared memory opt-in failed"}
 MAX_SPLITS = 32
+USE_CLUSTER_COMBINE = True
+USE_DECODE_KERNEL = True  # warp-parallel kernel for single tokens whose group fits 16 rows
+DECODE_KERNEL_MAX_SPLITS = 4  # measured: it wins for larger batches (few splits), the tile kernel for small ones
 TARGET_CTAS = 148 * 2
 _partials: dict = {}
 _err_addr: dict = {}
@@ -88,18 +91,24 @@ def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int) -> int
     if num_decode_tiles <= 0:
         return 1
     want = -(-TARGET_CTAS // (num_decode_tiles * num_kv_heads))
-    return max(1, min(want, MAX_SPLITS, -(-max_ctx // 256)))
+    limit = CLUSTER_MAX_SPLITS if USE_CLUSTER_COMBINE else MAX_SPLITS
+    return max(1, min(want, limit, -(-max_ctx // 256)))
+
+
+CLUSTER_MAX_SPLITS = 8  # splits that merge on chip (one thread-block cluster per tile)
 
 
 def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
-                tile_offset, num_tiles, out, part_o, part_ml, H, KVH, D, tpt, window, splits, scale):
+                tile_offset, num_tiles, out, part_o, part_ml, H, KVH, D, tpt, window, splits, scale,
+                cluster_combine=False, decode_only=False):
     num_pages, _, page_size, _ = k_pool.shape
     lib = L.attention_library(D)
     fn = getattr(lib, f"dsp_attn_mma_d{D}")
     rc = fn(L.ptr(q), L.i64(q_stride), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table),
             page_table.stride(0), L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0),
             tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml),
-            H, KVH, tpt, page_size, num_pages, window, splits, L.f32(scale),
+            H, KVH, tpt, page_size, num_pages, window, splits, int(cluster_combine), int(decode_only),
+            L.f32(scale),
             ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
     L.LaunchCounter.n += 1
     if rc != 0:
@@ -115,7 +124,14 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
     tpt = tokens_per_tile(H // KVH)
     if num_decode_tiles > 0:
-        if splits > 1:
+        if splits <= CLUSTER_MAX_SPLITS and USE_CLUSTER_COMBINE and (
+                (USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS) or splits > 1):
+            # single tokens: the cluster kernels (warp-parallel keys when the group fits 16 rows)
+            _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
+                        tile_tok0, 0, num_decode_tiles, out, None, None, H, KVH, D, tpt, window,
+                        splits, scale, cluster_combine=splits > 1,
+                        decode_only=USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS)
+        elif splits > 1:
             rows = num_decode_tiles * H  # decode tokens are the first rows of the flat batch
             part_o, part_ml = _partial_buffers(q.device, rows, splits, D)
             _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,

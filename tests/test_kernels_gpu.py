@@ -616,3 +616,25 @@ def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
     assert library.device_error() == 0
     g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
     torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("decode_kernel", [True, False])
+@pytest.mark.parametrize("splits", [1, 3, 8, 12])
+def test_attention_tensor_core_single_token_splits(splits, decode_kernel, monkeypatch):
+    """One decoded token over 900 keys: no split, splits merged on chip by the cluster (up to 8),
+    and splits merged from global scratch by the combine kernel (above 8)."""
+    from dispec_b200.ops import attention as A
+    # the warp-parallel kernel (any number of splits up to 8 here) or the tile kernel
+    monkeypatch.setattr(A, "USE_DECODE_KERNEL", decode_kernel)
+    monkeypatch.setattr(A, "DECODE_KERNEL_MAX_SPLITS", 8)
+    H, KVH, D, page, ctx = 12, 2, 128, 16, 900
+    g = torch.Generator().manual_seed(70 + splits)
+    q = torch.randn(1, H, D, generator=g).bfloat16().float()
+    k = torch.randn(ctx, KVH, D, generator=g).bfloat16().float()
+    v = torch.randn(ctx, KVH, D, generator=g).bfloat16().float()
+    ref = _attention_reference(q.double(), k.double(), v.double(), torch.tensor([ctx - 1]), 0, D ** -0.5)
+    kp, vp, perm = _paged(k, v, page, (ctx + page - 1) // page + 2, torch.bfloat16, splits)
+    out = torch.empty((1, H * D), dtype=torch.bfloat16, device=dev())
+    A.paged_attention_tensor_core(q.bfloat16().reshape(1, H * D).to(dev()), H * D, kp, vp, perm.view(1, -1).to(dev()),
+                                  None, None, out, H, KVH, D, 0, D ** -0.5, q_lens=[1], ctx_lens=[ctx], splits=splits)
+    torch.testing.assert_close(out.float().cpu().view(1, H, D).double(), ref, atol=2e-2, rtol=2e-2)
