@@ -30,10 +30,18 @@ CONFIG_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 use_sliding_window=True, sliding_window=24,
                 layer_types=["full_attention", "sliding_attention", "sliding_attention",
                              "full_attention"])
+# sizes that no fast path takes: a width that is no multiple of 8, an intermediate size that is
+# no multiple of 16, one query head per KV head, a prime vocabulary
+CONFIG_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+                hidden_size=100, num_attention_heads=4, num_key_value_heads=4, head_dim=16,
+                intermediate_size=150, vocab_size=211, rope_theta=777.0, rms_norm_eps=2e-6,
+                hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=512,
+                use_sliding_window=False)
 TINY = {
     "a": dict(config=CONFIG_A, seed=0, std=0.02, page_size=16),
     "b": dict(config=CONFIG_B, seed=1, std=0.05, page_size=8),
     "c": dict(config=CONFIG_C, seed=7, std=0.04, page_size=16),
+    "d": dict(config=CONFIG_D, seed=9, std=0.06, page_size=32),
 }
 
 

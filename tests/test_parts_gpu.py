@@ -139,6 +139,60 @@ def test_attention_part_in_two_portions(dtype, window):
     torch.testing.assert_close(got, ref, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pre_norm_block_alone(dtype):
+    """The arrangement of a layer (two norms, mixer, feed-forward, residual sums) against the
+    plain layer function, a sequence in two portions."""
+    from dispec_b200.cache import CacheGroupSpec
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.models.model import CachePlacement
+    from dispec_b200.parts.attention import GQAAttention
+    from dispec_b200.parts.block import PreNormBlock
+    from dispec_b200.parts.norms import RMSNorm
+    from dispec_b200.parts.rotary import RotaryEncoding
+    from dispec_b200.parts.swiglu import SwiGLUFeedForward
+    H, KVH, D, hidden, inter, eps, theta = 4, 2, 32, 96, 208, 1e-5, 30000.0
+    pe = RotaryEncoding(D, theta)
+    pe.prepare(DEV)
+    parts = dict(n1=RMSNorm(hidden, eps), n2=RMSNorm(hidden, eps),
+                 mixer=GQAAttention(hidden, H, KVH, D, True, pe), ffn=SwiGLUFeedForward(hidden, inter))
+    names = {"n1": {"weight": "input_layernorm.weight"}, "n2": {"weight": "post_attention_layernorm.weight"},
+             "mixer": {f"{n}_proj.{k}": f"self_attn.{n}_proj.{k}" for n in "qkv" for k in ("weight", "bias")}
+             | {"o_proj.weight": "self_attn.o_proj.weight"},
+             "ffn": {f"{n}_proj.weight": f"mlp.{n}_proj.weight" for n in ("gate", "up", "down")}}
+    weights = {}
+    seed = 200
+    for key, part in parts.items():
+        local = {}
+        for n, spec in part.tensor_specs().items():
+            t = rnd(spec.shape, seed, 0.12)
+            seed += 1
+            if spec.init == "one_plus_normal":
+                t = t + 1.0
+            t = t.to(dtype)
+            weights["L." + names[key][n]] = t.float()
+            local[n] = t.to(DEV)
+        part.load(local)
+    block = PreNormBlock(parts["n1"], parts["mixer"], parts["n2"], parts["ffn"])
+    T = 23
+    x = rnd((T, hidden), 300).to(dtype)
+    groups = [CacheGroupSpec(KVH, D, 0, 1)]
+    out, harness, pos = [], None, 0
+    for n in (9, 14):
+        e = [SeqEntry("s", list(range(n)), pos, [])]
+        ctx, harness = make_ctx(e, groups, 8, 6, dtype, [parts["mixer"].tokens_per_attention_tile()], harness=harness)
+        xs, pending = block.forward(ctx, x[pos:pos + n].to(DEV).clone(), None, ctx.cache_view(CachePlacement(0, 0), True), None)
+        out.append(xs if pending is None else xs + pending)
+        commit(harness, e)
+        pos += n
+    got = torch.cat(out).float().cpu()
+    c = dict(eps=eps, heads=H, kv_heads=KVH, head_dim=D)
+    cos, sin = plain.rope_tables(torch.arange(T), D, theta)
+    ref = plain.decoder_layer(x.float(), weights, "L.", c, cos, sin, 0)
+    tol = 3e-5 if dtype == torch.float32 else 6e-2
+    torch.testing.assert_close(got, ref, atol=tol, rtol=tol)
+
+
 # ------------------------------------------------------------------- toy parts and models
 
 def register_toys():
