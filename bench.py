@@ -42,6 +42,13 @@ BENCH_CONFIG = dict(
     num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, hidden_act="silu",
     tie_word_embeddings=True, max_position_embeddings=4096, use_sliding_window=False)
+# the two larger shapes of the same family (bench.py --shape 7b|14b); seeds as listed beside them
+OTHER_SHAPES = {
+    "7b": (dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                intermediate_size=18944, vocab_size=152064, rms_norm_eps=1e-6, tie_word_embeddings=False), 3),
+    "14b": (dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                 intermediate_size=13824, vocab_size=152064, rms_norm_eps=1e-5, tie_word_embeddings=False), 4),
+}
 SEED, STD = 2, 0.02
 BATCH, PROMPT_LEN, NEW_TOKENS, CONTEXT_LEN, PAGE_SIZE = 8, 1024, 256, 4096, 16
 PREFILL_TOKENS = 2048
@@ -218,13 +225,17 @@ def run_ours(args) -> dict:
     from dispec_b200.weights import load_random_model
 
     cfg_dict = dict(BENCH_CONFIG)
+    seed = SEED
+    if args.shape != "1.5b":
+        cfg_dict.update(OTHER_SHAPES[args.shape][0])
+        seed = OTHER_SHAPES[args.shape][1]
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
     layers = cfg_dict["num_hidden_layers"]
     cfg = load_model_config(cfg_dict)
     t0 = time.time()
-    model = load_random_model(cfg, SEED, STD, "bfloat16", "cuda:0")
+    model = load_random_model(cfg, seed, STD, "bfloat16", "cuda:0")
     print(f"bench: model ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
     pk = peaks()
     weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg_dict, layers)
@@ -238,12 +249,16 @@ def run_ours(args) -> dict:
     if args.only == "decode":
         r = runner_for(args.batch)
         ms, launches, ctx = decode_direct(r, random_prompts(args.batch, PROMPT_LEN, vocab, 11), args.steps, args.warmup)
-        return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
-                "tok_s": round(args.batch * 1000.0 / ms, 1), "gpu_launches": launches, "mean_ctx": ctx}
+        step_bytes = weight_bytes + args.batch * ctx * kv_per_token
+        return {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
+                "ms_per_step": round(ms, 4), "tok_s": round(args.batch * 1000.0 / ms, 1),
+                "gpu_launches": launches, "mean_ctx": ctx,
+                "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
     if args.only == "prefill":
         r = runner_for(1)
         pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=max(1, args.steps))
-        return {"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+        return {"only": "prefill", "shape": args.shape, "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                "tok_s": round(PREFILL_TOKENS / pms * 1000.0, 1),
                 "frac": round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     # headline: batch 8
     runner = runner_for(BATCH)
@@ -274,13 +289,13 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": full_layers,
+            "model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "layers_full": full_layers,
             "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
             "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
-            "intermediate": cfg_dict["intermediate_size"], "vocab": vocab, "tied": True,
+            "intermediate": cfg_dict["intermediate_size"], "vocab": vocab, "tied": cfg_dict["tie_word_embeddings"],
             "global_batch": BATCH, "seq_len": PROMPT_LEN, "context_len": CONTEXT_LEN,
             "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-            "weights": f"random N(0,{STD}) seed {SEED}",
+            "weights": f"random N(0,{STD}) seed {seed}",
             "l2": "no flush: each step reads %.2f GB of weights, above the 126 MB L2" % (weight_bytes / 1e9),
             "peaks": "of " + pk["source"],
         },
@@ -357,6 +372,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
+    ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
+                    help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="profiling aid: run one phase only and print a short line")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")

@@ -282,7 +282,7 @@ __device__ __forceinline__ void mbar_arrive_on_leader(uint64_t* bar) {
       : "memory");
 }
 
-template <typename TOut>
+template <typename TOut, int BNP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const Epilogue e, int* err) {
@@ -299,7 +299,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const int num_kb = (e.K + BK - 1) / BK;
-  const int n_tiles = (e.N + BN - 1) / BN, m_tiles = (e.M + 2 * BM - 1) / (2 * BM);
+  constexpr int STAGE_P = A_BYTES + (BNP / 2) * BK * 2;  // A tile and this CTA's half of the W tile
+  const int n_tiles = (e.N + BNP - 1) / BNP, m_tiles = (e.M + 2 * BM - 1) / (2 * BM);
   const int num_tiles = n_tiles * m_tiles;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -332,7 +333,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       int it = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
         const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
-        const int w0 = (tile % n_tiles) * BN + (int)rank * (BN / 2);
+        const int w0 = (tile % n_tiles) * BNP + (int)rank * (BNP / 2);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
@@ -340,8 +341,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             failed = 1;
             break;
           }
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE2_BYTES);
-          unsigned char* a_dst = smem + s * STAGE2_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P);
+          unsigned char* a_dst = smem + s * STAGE_P;
           tma_load_2d_pair(a_dst, &map_a, &full_bar[s], kb * BK, m0);
           tma_load_2d_pair(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, w0);
         }
@@ -349,7 +350,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc(2 * BM, BN);  // M 256 across the pair
+      const uint32_t idesc = umma_idesc(2 * BM, BNP);  // M 256 across the pair
       int it = 0, local = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
         const int buf = local & 1;
@@ -358,7 +359,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
@@ -367,7 +368,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE2_BYTES);
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_P);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
@@ -383,16 +384,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     int local = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
       const int buf = local & 1;
-      const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM, n0 = (tile % n_tiles) * BN;
+      const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM, n0 = (tile % n_tiles) * BNP;
       if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[buf], (local >> 1) & 1))) {
         failed = 1;
         break;
       }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BNP; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 256 + c0), v);
         store_row_chunk<TOut>(e, v, row, n0 + c0);
       }
       tc_fence_before();
@@ -451,26 +452,37 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
     DSP_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
   }
   if (pair_mode) {
-    const int smem2 = STAGES2 * STAGE2_BYTES + 1024;
-    const long tiles2 = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
-    const long pairs = tiles2 < num_sms / 2 ? tiles2 : num_sms / 2;
+    // tile width: 256, or 192 when that puts more of the CTA pairs to work in the last round
+    // (cost ~ rounds x width; N 1536 on 74 pairs: 48 tiles of 256 against 64 tiles of 192)
+    const long pairs_avail = num_sms / 2;
+    const long m_tiles2 = (M + 2 * BM - 1) / (2 * BM);
+    auto cost = [&](int bn) {
+      const long tiles2 = (long)((N + bn - 1) / bn) * m_tiles2;
+      return ((tiles2 + pairs_avail - 1) / pairs_avail) * bn;
+    };
+    const int bnp = cost(192) < cost(256) ? 192 : 256;
+    DSP_REQUIRE(make_map(&map_w, W, N, K, K, bnp / 2), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+    const int smem2 = STAGES2 * (A_BYTES + (bnp / 2) * BK * 2) + 1024;
+    const long tiles2 = (long)((N + bnp - 1) / bnp) * m_tiles2;
+    const long pairs = tiles2 < pairs_avail ? tiles2 : pairs_avail;
     dim3 grid2((unsigned)(2 * pairs));
+#define DSP_LAUNCH_PAIR(TYPE, WIDTH)                                                                          \
+  do {                                                                                                       \
+    static bool configured = false;                                                                          \
+    if (!configured) {                                                                                       \
+      DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<TYPE, WIDTH>,                                   \
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));                    \
+      prefer_max_shared(reinterpret_cast<const void*>(gemm_tcgen05_pair_kernel<TYPE, WIDTH>));               \
+      configured = true;                                                                                     \
+    }                                                                                                        \
+    gemm_tcgen05_pair_kernel<TYPE, WIDTH><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);          \
+  } while (0)
     if (out_dtype == DSP_BF16) {
-      static bool configured = false;
-      if (!configured) {
-        DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-        configured = true;
-      }
-      prefer_max_shared(reinterpret_cast<const void*>(gemm_tcgen05_pair_kernel<bf16>));
-      gemm_tcgen05_pair_kernel<bf16><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);
+      if (bnp == 192) DSP_LAUNCH_PAIR(bf16, 192); else DSP_LAUNCH_PAIR(bf16, 256);
     } else {
-      static bool configured = false;
-      if (!configured) {
-        DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-        configured = true;
-      }
-      gemm_tcgen05_pair_kernel<float><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);
+      if (bnp == 192) DSP_LAUNCH_PAIR(float, 192); else DSP_LAUNCH_PAIR(float, 256);
     }
+#undef DSP_LAUNCH_PAIR
     DSP_CHECK_LAUNCH("dsp_gemm_tcgen05 (CTA pairs)");
     return 0;
   }
