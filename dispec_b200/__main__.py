@@ -190,7 +190,18 @@ def main(argv=None) -> int:
     e.set_defaults(fn=lambda a: __import__("dispec_b200.env_check", fromlist=["main"]).main())
 
     args = ap.parse_args(argv)
-    return args.fn(args)
+    from dispec_b200.config.model_config import ConfigError
+    from dispec_b200.registry import RegistryError
+    try:
+        return args.fn(args)
+    except (ConfigError, RegistryError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    except ValueError as e:  # WeightError, SafetensorsError and refused requests
+        if type(e).__name__ in ("WeightError", "SafetensorsError"):
+            print(f"error: {e}", file=sys.stderr)
+            return 2
+        raise
 
 
 if __name__ == "__main__":

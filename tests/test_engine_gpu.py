@@ -210,3 +210,31 @@ def test_captured_decode_steps_match_eager_steps(folders):
     assert (results[0] - results[1]).abs().max().item() < 0.03 * scale
     # and both are right: the first decoded row of x
     assert (results[1][0] - refs["x"][len(prompts["x"]) - 8]).abs().max().item() < 0.03 * scale + 0.02
+
+
+def test_command_line_generate_and_random(tmp_path):
+    """`python -m dispec_b200 random` writes a folder that `generate` serves; greedy output equals
+    the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from safetensors.torch import load_file
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(ru.CONFIG_B))
+    out_dir = tmp_path / "model"
+    env = dict(os.environ, PYTHONPATH=ru.ROOT)
+    subprocess.run([sys.executable, "-m", "dispec_b200", "random", "--config", str(cfg_path), "--out", str(out_dir),
+                    "--seed", "5", "--std", "0.08"], check=True, env=env, cwd=ru.ROOT)
+    proc = subprocess.run([sys.executable, "-m", "dispec_b200", "generate", "--model", str(out_dir), "--dtype", "float32",
+                           "--prompt-ids", "5,17,3,99", "--prompt-ids", "7 8 9", "--max-new", "6", "--block-size", "8",
+                           "--num-blocks", "32", "--max-batch-tokens", "16", "--chunk-size", "4"],
+                          check=True, env=env, cwd=ru.ROOT, capture_output=True, text=True)
+    lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert [ln["prompt_tokens"] for ln in lines] == [4, 3]
+    weights = {k: v.float() for k, v in load_file(str(out_dir / "model.safetensors")).items()}
+    config = json.load(open(out_dir / "config.json"))
+    for ln, prompt in zip(lines, ([5, 17, 3, 99], [7, 8, 9])):
+        want, gaps = plain.greedy_generate(weights, config, prompt, 6)
+        n = next((i for i, g in enumerate(gaps) if g < 1e-4), 6)
+        assert ln["output_ids"][:n] == want[:n]
