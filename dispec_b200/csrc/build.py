@@ -153,11 +153,17 @@ def build_all(head_dims=(16, 32, 64, 128)) -> list[str]:
     libs = [core_library()]
     for d in head_dims:
         libs.append(attention_library(d))
+        if d in (64, 128):
+            libs.append(prefill_attention_library(d))
     return libs
 
 
 def attention_library(head_dim: int) -> str:
     return specialised_library(f"attn_mma_d{head_dim}", "attn_mma.cu", {"DSP_HEAD_DIM": head_dim})
+
+
+def prefill_attention_library(head_dim: int) -> str:
+    return specialised_library(f"attn_tcgen05_d{head_dim}", "attn_tcgen05.cu", {"DSP_HEAD_DIM": head_dim})
 
 
 if __name__ == "__main__":

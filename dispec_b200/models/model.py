@@ -103,7 +103,11 @@ class DecoderModel:
             members[g].append(label)
         self.cache_groups = [CacheGroupSpec(k.num_kv_heads, k.head_dim, k.window, len(m))
                              for k, m in zip(group_keys, members)]
-        tiles = {self.layers[c.layer].mixer.tokens_per_attention_tile() for c in self.schedule}
+        tiles: set = set()
+        for c in self.schedule:
+            want = self.layers[c.layer].mixer.tokens_per_attention_tile()
+            if want:
+                tiles.update(want if isinstance(want, (tuple, list)) else (want,))
         self.attention_tile_tokens = sorted(t for t in tiles if t)
 
     # ----------------------------------------------------------------------- weights

@@ -8,6 +8,8 @@ import torch
 from dispec_b200.ops import library as L
 
 ROWS_PER_TILE = 64  # query rows (token, head-in-group pairs) one tensor-core tile holds
+PREFILL_ROWS_PER_TILE = 128  # rows of a tile of the tcgen05 kernel for portions of prompts
+PREFILL_BACKEND = "tcgen05"  # "mma": portions of prompts on the mma.sync kernel as well
 
 
 def tokens_per_tile(group_size: int) -> int | None:
@@ -15,6 +17,17 @@ def tokens_per_tile(group_size: int) -> int | None:
     if group_size > ROWS_PER_TILE:
         return None
     return ROWS_PER_TILE // group_size
+
+
+def prefill_tokens_per_tile(group_size: int) -> int:
+    """Query tokens per tile of the tcgen05 kernel for portions of prompts."""
+    return PREFILL_ROWS_PER_TILE // group_size
+
+
+def tcgen05_supported(head_dim: int, group_size: int, page_size: int, dtype: torch.dtype) -> bool:
+    """The tcgen05 kernel is built for head sizes 64 and 128 and pages of 8 to 64 tokens."""
+    return (PREFILL_BACKEND == "tcgen05" and dtype == torch.bfloat16 and head_dim in (64, 128)
+            and group_size <= ROWS_PER_TILE and page_size in (8, 16, 32, 64))
 
 
 def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -115,11 +128,32 @@ def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_
         raise L.KernelError(f"dsp_attn_mma_d{D}: {_MMA_ERRORS.get(rc, rc)}")
 
 
+def _launch_tcgen05(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
+                    tile_offset, num_tiles, out, H, KVH, D, tpt, window, scale):
+    num_pages, _, page_size, _ = k_pool.shape
+    lib = L.prefill_attention_library(D)
+    fn = getattr(lib, f"dsp_attn_tcgen05_d{D}")
+    rc = fn(L.ptr(q), L.i64(q_stride), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table),
+            page_table.stride(0), L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0),
+            tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), H, KVH, tpt, page_size, num_pages,
+            window, L.f32(scale), ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
+    L.LaunchCounter.n += 1
+    if rc != 0:
+        raise L.KernelError(f"dsp_attn_tcgen05_d{D}: {_TCGEN05_ERRORS.get(rc, rc)}")
+
+
+_TCGEN05_ERRORS = {1: "launch failed", 2: "unsupported head/group counts or page size",
+                   3: "operands must be 16-byte aligned with strides in whole 16-byte pieces",
+                   4: "shared memory opt-in or tensor map creation failed"}
+
+
 def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                           tile_tok0, num_tiles, num_decode_tiles, out, H, KVH, D, window, scale,
-                          splits: int) -> torch.Tensor:
+                          splits: int, prefill_tiles=None) -> torch.Tensor:
     """Tensor-core attention over a tile list whose first ``num_decode_tiles`` tiles are single
-    tokens (run with ``splits`` key splits and merged), the rest portions of prompts."""
+    tokens (run with ``splits`` key splits and merged), the rest portions of prompts.  With
+    ``prefill_tiles`` = (tile_seq, tile_tok0, num_tiles) of the 128-row tiling (single tokens
+    first as well) the portions of prompts run on the tcgen05 kernel."""
     assert q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
     tpt = tokens_per_tile(H // KVH)
@@ -143,7 +177,13 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
         else:
             _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                         tile_tok0, 0, num_decode_tiles, out, None, None, H, KVH, D, tpt, window, 1, scale)
-    if num_tiles > num_decode_tiles:
+    if prefill_tiles is not None:
+        big_seq, big_tok0, big_n = prefill_tiles
+        if big_n > num_decode_tiles:
+            _launch_tcgen05(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, big_seq, big_tok0,
+                            num_decode_tiles, big_n - num_decode_tiles, out, H, KVH, D,
+                            prefill_tokens_per_tile(H // KVH), window, scale)
+    elif num_tiles > num_decode_tiles:
         _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
                     num_decode_tiles, num_tiles - num_decode_tiles, out, None, None, H, KVH, D, tpt,
                     window, 1, scale)
@@ -156,24 +196,33 @@ def paged_attention_tensor_core(q, q_stride, k_pool, v_pool, page_table, positio
     """Stand-alone form (tests, tools): builds the tile list for sequences given by their
     ``q_lens`` and ``ctx_lens`` (single-token sequences must come first)."""
     dev_ = q.device
-    tpt = tokens_per_tile(num_heads // num_kv_heads)
-    ts, t0 = [], []
-    n_dec = 0
-    for s, n in enumerate(q_lens):
-        if n == 1 and n_dec == s:
-            n_dec += 1
-        for a in range(0, n, tpt):
-            ts.append(s)
-            t0.append(a)
+    group = num_heads // num_kv_heads
+    tpt = tokens_per_tile(group)
+
+    def tile_list(per_tile):
+        ts, t0, n_dec = [], [], 0
+        for s, n in enumerate(q_lens):
+            if n == 1 and n_dec == s:
+                n_dec += 1
+            for a in range(0, n, per_tile):
+                ts.append(s)
+                t0.append(a)
+        return ts, t0, n_dec
+
+    ts, t0, n_dec = tile_list(tpt)
     starts = [0]
     for n in q_lens:
         starts.append(starts[-1] + n)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev_)
     if splits is None:
         splits = choose_splits(n_dec, num_kv_heads, max(ctx_lens))
+    prefill_tiles = None
+    if tcgen05_supported(head_dim, group, k_pool.shape[2], q.dtype):
+        bs, b0, _ = tile_list(prefill_tokens_per_tile(group))
+        prefill_tiles = (i32(bs), i32(b0), len(bs))
     return paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, i32(starts), i32(ctx_lens),
                                  i32(ts), i32(t0), len(ts), n_dec, out, num_heads, num_kv_heads,
-                                 head_dim, window, scale, splits)
+                                 head_dim, window, scale, splits, prefill_tiles)
 
 
 def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tensor, num_heads: int,
@@ -187,10 +236,14 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
         tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
         splits = ctx.decode_splits if ctx.decode_splits else choose_splits(
             ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len)
+        prefill_tiles = None
+        big = prefill_tokens_per_tile(group)
+        if big in ctx.attention_tiles and tcgen05_supported(head_dim, group, cache.key_pool.shape[2], q.dtype):
+            prefill_tiles = ctx.attention_tiles[big]
         return paged_attention_tiles(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                      ctx.q_start, ctx.ctx_len, tile_seq, tile_tok0, num_tiles,
                                      ctx.num_decode_seqs, out, num_heads, num_kv_heads, head_dim,
-                                     window, scale, splits)
+                                     window, scale, splits, prefill_tiles)
     return paged_attention_generic(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads,
                                    head_dim, window, scale)

@@ -51,6 +51,15 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     return _special[key]
 
 
+def prefill_attention_library(head_dim: int) -> ctypes.CDLL:
+    key = f"attn_tcgen05_d{head_dim}"
+    if key not in _special:
+        with _lock:
+            if key not in _special:
+                _special[key] = ctypes.CDLL(build.prefill_attention_library(head_dim))
+    return _special[key]
+
+
 def loaded_libraries() -> list[str]:
     out = [] if _core is None else [_core._name]
     return out + [lib._name for lib in _special.values()]

@@ -65,7 +65,11 @@ class GQAAttention(Mixer):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
 
     def tokens_per_attention_tile(self):
-        return attn_ops.tokens_per_tile(self.num_heads // self.num_kv_heads)
+        group = self.num_heads // self.num_kv_heads
+        small = attn_ops.tokens_per_tile(group)
+        if small and self.head_dim in (64, 128):
+            return (small, attn_ops.prefill_tokens_per_tile(group))  # portions of prompts: 128-row tiles
+        return small
 
     fuses_norm_and_residual = True
 

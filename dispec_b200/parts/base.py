@@ -103,8 +103,9 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
-    def tokens_per_attention_tile(self) -> int | None:
-        """Query tokens per attention tile this mixer wants listed in the batch (or None)."""
+    def tokens_per_attention_tile(self):
+        """Query tokens per attention tile this mixer wants listed in the batch: an int, a tuple
+        of them (one tile list each), or None."""
         return None
 
     def forward(self, ctx, x, cache, state):

@@ -339,88 +339,6 @@ def test_gemm_weight_streaming_is_deterministic_and_strided():
     torch.testing.assert_close(a.double(), x.double() @ w.double().T, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("case", ATTN_CASES + [(28, 4, 128, 16, 1200, 1, 0), (5, 5, 80, 16, 130, 64, 0),
-                                               (8, 1, 256, 16, 100, 9, 0), (12, 2, 128, 16, 700, 300, 0)])
-def test_attention_tensor_core(case):
-    out, ref = run_attention("tensor_core", torch.bfloat16, *case)
-    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
-
-
-@pytest.mark.parametrize("plant", [0, 15, 16, 63, 64, 65, 255, 256, 511, 600])
-@pytest.mark.parametrize("q_len", [1, 37])
-def test_attention_tensor_core_far_key_stands_out(plant, q_len):
-    out, ref = run_attention("tensor_core", torch.bfloat16, 12, 2, 64, 16, 700, q_len, 0, plant=plant,
-                             seed=plant)
-    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
-
-
-@pytest.mark.parametrize("offset", [-1, 0, 1])
-@pytest.mark.parametrize("q_len", [1, 20])
-def test_attention_tensor_core_window_edge(offset, q_len):
-    ctx, window = 333, 100
-    plant = ctx - 1 - window + 1 + offset
-    out, ref = run_attention("tensor_core", torch.bfloat16, 6, 2, 32, 8, ctx, q_len, window, plant=plant,
-                             seed=9)
-    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
-
-
-def test_attention_tensor_core_mixed_batch_matches_alone():
-    """Single tokens (with key splits) beside a portion of a prompt, ragged lengths."""
-    from dispec_b200.ops import attention as A
-    H, KVH, D, page = 6, 2, 64, 16
-    q_lens = [1, 1, 1, 23, 70]
-    ctx_lens = [17, 300, 64, 23, 200]
-    g = torch.Generator().manual_seed(11)
-    num_pages = sum((c + page - 1) // page for c in ctx_lens) + 2
-    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=torch.bfloat16)
-    vp = kp.clone()
-    perm = torch.randperm(num_pages, generator=g).tolist()
-    maxp = max((c + page - 1) // page for c in ctx_lens)
-    table = torch.full((len(q_lens), maxp), -1, dtype=torch.int32)
-    qs, refs, positions, seqs = [], [], [], []
-    for s, (ql, cl) in enumerate(zip(q_lens, ctx_lens)):
-        k = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
-        v = torch.randn(cl, KVH, D, generator=g).bfloat16().float()
-        q = torch.randn(ql, H, D, generator=g).bfloat16().float()
-        for j in range((cl + page - 1) // page):
-            table[s, j] = perm.pop()
-        for b in range(cl):
-            kp[table[s, b // page], :, b % page] = k[b].bfloat16()
-            vp[table[s, b // page], :, b % page] = v[b].bfloat16()
-        pos = torch.arange(cl - ql, cl, dtype=torch.int32)
-        refs.append(_attention_reference(q.double(), k.double(), v.double(), pos, 0, D ** -0.5))
-        qs.append(q)
-        positions.append(pos)
-        seqs += [s] * ql
-    qd = torch.cat(qs).bfloat16().reshape(-1, H * D).to(dev())
-    out = torch.empty_like(qd)
-    A.paged_attention_tensor_core(qd, H * D, kp.to(dev()), vp.to(dev()), table.to(dev()),
-                                  torch.cat(positions).to(dev()),
-                                  torch.tensor(seqs, dtype=torch.int32, device=dev()), out, H, KVH, D, 0,
-                                  D ** -0.5, q_lens=q_lens, ctx_lens=ctx_lens, splits=4)
-    got = out.float().cpu().view(-1, H, D).double()
-    torch.testing.assert_close(got, torch.cat(refs), atol=2e-2, rtol=2e-2)
-
-
-@pytest.mark.parametrize("M,N,K", [(1, 130, 96), (8, 2048, 1536), (13, 300, 776), (16, 1536, 8960)])
-def test_gemm_weight_streaming_with_fused_norm(M, N, K):
-    from dispec_b200 import ops
-    from dispec_b200.ops import gemm
-    x = rnd((M, K), torch.bfloat16, 31, 2.0)
-    gain = (1 + rnd((K,), torch.float32, 32, 0.1)).to(torch.bfloat16).to(dev())
-    w = rnd((N, K), torch.bfloat16, 33, 0.1)
-    b = rnd((N,), torch.bfloat16, 34)
-    r = rnd((M, N), torch.bfloat16, 35)
-    eps = 1e-5
-    # the fused form against the two kernels it replaces (same rounding points), and against float64
-    normed = ops.rms_norm(x, gain, eps)
-    fused = gemm.linear_rms_norm(x, gain, eps, w, b, residual=r.clone())
-    ref = normed.double() @ w.double().T + b.double() + r.double()
-    torch.testing.assert_close(fused.double(), ref, atol=3e-2, rtol=2e-2)
-    logits = gemm.linear_rms_norm(x, gain, eps, w, out_dtype=torch.float32)
-    torch.testing.assert_close(logits.double(), normed.double() @ w.double().T, atol=3e-3, rtol=3e-3)
-
-
 @pytest.mark.parametrize("M,I,K", [(1, 64, 96), (8, 8960, 1536), (13, 176, 80), (40, 224, 96), (64, 512, 776),
                                    (300, 512, 776), (2048, 1024, 1536)])
 def test_gate_up_product_with_swiglu_epilogue(M, I, K):
@@ -638,3 +556,41 @@ def test_attention_tensor_core_single_token_splits(splits, decode_kernel, monkey
     A.paged_attention_tensor_core(q.bfloat16().reshape(1, H * D).to(dev()), H * D, kp, vp, perm.view(1, -1).to(dev()),
                                   None, None, out, H, KVH, D, 0, D ** -0.5, q_lens=[1], ctx_lens=[ctx], splits=splits)
     torch.testing.assert_close(out.float().cpu().view(1, H, D).double(), ref, atol=2e-2, rtol=2e-2)
+
+
+TCGEN05_CASES = [
+    # H, KVH, D, page, ctx, q_len, window: portions of prompts on the tcgen05 kernel
+    (12, 2, 128, 16, 700, 300, 0),   # several query tiles, group of 6 (126 of 128 rows used)
+    (14, 2, 64, 8, 333, 333, 0),     # whole prompt, group of 7, small pages
+    (4, 4, 128, 32, 520, 130, 0),    # no sharing of keys between heads
+    (8, 1, 64, 64, 1000, 77, 0),     # one page per key tile
+    (6, 2, 128, 16, 900, 200, 150),  # window: first key tile of most query tiles starts before it
+    (6, 3, 64, 8, 400, 2, 70),       # two tokens
+    (64, 1, 64, 16, 150, 5, 0),      # a group that fills half a tile per token
+]
+
+
+@pytest.mark.parametrize("backend", ["tcgen05", "mma"])
+@pytest.mark.parametrize("case", TCGEN05_CASES)
+def test_attention_prefill_backends(case, backend, monkeypatch):
+    from dispec_b200.ops import attention as A
+    monkeypatch.setattr(A, "PREFILL_BACKEND", backend)
+    assert A.tcgen05_supported(case[2], case[0] // case[1], case[3], torch.bfloat16) == (backend == "tcgen05")
+    out, ref = run_attention("tensor_core", torch.bfloat16, *case)
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("plant", [0, 15, 16, 63, 64, 65, 127, 128, 255, 256, 511, 600, 699])
+def test_attention_tcgen05_far_key_stands_out(plant):
+    out, ref = run_attention("tensor_core", torch.bfloat16, 12, 2, 128, 16, 700, 150, 0, plant=plant, seed=plant)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("offset", [-1, 0, 1])
+@pytest.mark.parametrize("q_len", [2, 40])
+def test_attention_tcgen05_window_edge(offset, q_len):
+    ctx, window = 333, 100
+    plant = ctx - 1 - window + 1 + offset
+    out, ref = run_attention("tensor_core", torch.bfloat16, 6, 2, 64, 8, ctx, q_len, window, plant=plant, seed=9)
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
+

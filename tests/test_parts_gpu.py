@@ -33,6 +33,13 @@ def make_ctx(entries, groups, page_size, num_pages, dtype, tile_tokens=(), state
     return ctx, harness
 
 
+def _tile_sizes(mixer):
+    want = mixer.tokens_per_attention_tile()
+    if not want:
+        return []
+    return list(want) if isinstance(want, (tuple, list)) else [want]
+
+
 def commit(harness, entries):
     for e in entries:
         harness["cache"].commit(e.req_id, e.start + len(e.tokens))
@@ -119,7 +126,7 @@ def test_attention_part_in_two_portions(dtype, window):
     T = 29
     x = rnd((T, hidden), 40).to(dtype)
     groups = [CacheGroupSpec(KVH, D, window, 1)]
-    tiles = [mixer.tokens_per_attention_tile()]
+    tiles = _tile_sizes(mixer)
     from dispec_b200.models.model import CachePlacement
     out, harness, pos = [], None, 0
     for n in (18, 11):
@@ -180,7 +187,7 @@ def test_pre_norm_block_alone(dtype):
     out, harness, pos = [], None, 0
     for n in (9, 14):
         e = [SeqEntry("s", list(range(n)), pos, [])]
-        ctx, harness = make_ctx(e, groups, 8, 6, dtype, [parts["mixer"].tokens_per_attention_tile()], harness=harness)
+        ctx, harness = make_ctx(e, groups, 8, 6, dtype, _tile_sizes(parts["mixer"]), harness=harness)
         xs, pending = block.forward(ctx, x[pos:pos + n].to(DEV).clone(), None, ctx.cache_view(CachePlacement(0, 0), True), None)
         out.append(xs if pending is None else xs + pending)
         commit(harness, e)
