@@ -377,7 +377,9 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="profiling aid: run one phase only and print a short line")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     args = ap.parse_args()
+    globals()["PAGE_SIZE"] = args.page_size
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

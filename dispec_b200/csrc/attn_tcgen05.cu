@@ -7,7 +7,8 @@
 // pair, so the G query heads that share a KV head share every key/value load.  Keys are walked in
 // tiles of 64 through the page table.  Roles, one CTA per tile:
 //   warp 0      issues the TMA loads of K and V tiles, one lane per page (a ring of four tiles);
-//   warp 1      one thread issues the products S[i] = Q K[i]^T and O[i % 2] += P[i] V[i];
+//   warp 1      one thread issues the products S[i] = Q K[i]^T and O[i % 2] += P[i] V[i], each as soon
+//               as its operands are ready (it polls the barriers of both);
 //   warps 2..9  two softmax groups of four warps.  Group g owns the key tiles i = g, g + 2, ...: its own
 //               score buffer S[g] and output accumulator O[g] in tensor memory, its own P[g] in
 //               shared memory and its own running maximum and sum, so the two groups never exchange
@@ -96,6 +97,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// one non-blocking look at a barrier phase
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -115,6 +128,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
   __shared__ __align__(8) uint64_t kv_full[STAGES];   // K and V of a tile have landed
   __shared__ __align__(8) uint64_t kv_empty[STAGES];  // both products of the tile have read them
   __shared__ __align__(8) uint64_t s_full[2];         // a score buffer is complete
+  __shared__ __align__(8) uint64_t s_free[2];         // the group has read its score buffer
   __shared__ __align__(8) uint64_t p_full[2];         // P written, O rescaled, V rows zeroed
   __shared__ __align__(8) uint64_t o_done[2];         // O[g] += P V of a tile is complete
   __shared__ float merge_m[BM], merge_l[BM];          // group 1's running maximum and sum per row
@@ -154,6 +168,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
+      mbar_init(&s_free[b], 4);
       mbar_init(&p_full[b], 4);  // one arrival per warp of the group
       mbar_init(&o_done[b], 1);
     }
@@ -191,8 +206,18 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     // ---- TMA producer: lane j looks up page j of the key tile and issues its loads
     const int pages_per_tile = BN / p.page_size;
     const uint32_t page_bytes = 2u * KD * (uint32_t)p.page_size * 128u;  // K and V, every slice
+    // pages that hold keys some row may see; the others are not read.  The table entry of the next
+    // tile is fetched before the wait on the ring, so its latency is off the loads' path.
+    auto lookup = [&](int i) -> int {
+      const int first = (kt_begin + i) * BN + lane * p.page_size;
+      if (lane < pages_per_tile && first <= pos_last && first + p.page_size > lo) return table[first / p.page_size];
+      return -2;  // not wanted
+    };
+    int pg_next = lookup(0);
     for (int i = 0; i < n_kt; ++i) {
       const int s = i % STAGES;
+      int pg = pg_next;
+      if (i + 1 < n_kt) pg_next = lookup(i + 1);
       int ok = 1;
       if (lane == 0) ok = !failed && mbar_wait(&kv_empty[s], ((i / STAGES) & 1) ^ 1);
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -200,15 +225,9 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         if (lane == 0) failed = 1;
         break;
       }
-      const int first = (kt_begin + i) * BN + lane * p.page_size;
-      // pages that hold keys some row may see; the others are not read
-      int pg = -1;
-      if (lane < pages_per_tile && first <= pos_last && first + p.page_size > lo) {
-        pg = table[first / p.page_size];
-        if (pg < 0 || pg >= p.num_pages) {
-          atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          pg = -1;
-        }
+      if (pg != -2 && (pg < 0 || pg >= p.num_pages)) {
+        atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        pg = -1;
       }
       const uint32_t live = __ballot_sync(0xffffffffu, pg >= 0);
       if (lane == 0) {
@@ -231,42 +250,59 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(BM, BN);
       const uint32_t idesc_o = umma_idesc(BM, D) | (1u << 16);  // B (values) is N-major
-      const uint32_t q_addr = smem_u32(q_s);
-      auto issue_scores = [&](int i) -> bool {
+      // descriptors are linear in the address: the tile's base once, a constant per k step
+      const uint64_t q_desc = umma_desc(smem_u32(q_s));
+      const uint64_t k_desc0 = umma_desc(smem_u32(k_s));
+      const uint64_t v_desc0 = umma_desc_mn(smem_u32(v_s), KV_SLICE);
+      const uint64_t p_desc0 = umma_desc(smem_u32(p_s));
+      auto issue_scores = [&](int i) {
         const int s = i % STAGES;
-        if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_s + s * KV_BYTES);
+        const uint64_t k_desc = k_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
         const uint32_t tmem_s = tmem_base + (uint32_t)((i & 1) * S_COLS);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (uint32_t)(k >> 2), in = (uint32_t)(k & 3) * 32u;
-          umma(tmem_s, umma_desc(q_addr + off * Q_SLICE + in), umma_desc(k_addr + off * KV_SLICE + in), idesc_s,
-               k != 0);
+          umma(tmem_s, q_desc + ((off * Q_SLICE + in) >> 4), k_desc + ((off * KV_SLICE + in) >> 4), idesc_s, k != 0);
         }
         umma_commit(&s_full[i & 1]);
-        return true;
       };
-      bool ok = issue_scores(0);
-      if (ok && n_kt > 1) ok = issue_scores(1);
-      for (int i = 0; i < n_kt && ok; ++i) {
-        const int g = i & 1;
-        if (!mbar_wait(&p_full[g], (i >> 1) & 1)) {
+      auto issue_output = [&](int i) {
+        const int g = i & 1, s = i % STAGES;
+        tc_fence_after();
+        const uint64_t v_desc = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
+        const uint64_t p_desc = p_desc0 + (uint64_t)(g * (P_BYTES >> 4));
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          umma(tmem_base + (uint32_t)(O_COL + g * D), p_desc + (uint64_t)(k * 2), v_desc + (uint64_t)(k * 128), idesc_o,
+               (i >= 2) || k != 0);
+        umma_commit(&kv_empty[s]);
+        umma_commit(&o_done[g]);
+      };
+      // Work in whatever order it becomes ready: the scores of tile a need K[a] and, from the third
+      // tile on, that the group has read S[a % 2] (tile a - 2); the output product of tile b needs P[b].
+      int a = 0, b = 0;
+      uint32_t polls = 0;
+      bool ok = true;
+      while (b < n_kt) {
+        bool progress = false;
+        if (a < n_kt && mbar_test(&kv_full[a % STAGES], (a / STAGES) & 1) &&
+            (a < 2 || mbar_test(&s_free[a & 1], ((a - 2) >> 1) & 1))) {
+          issue_scores(a);
+          ++a;
+          progress = true;
+        }
+        if (mbar_test(&p_full[b & 1], (b >> 1) & 1)) {
+          issue_output(b);
+          ++b;
+          progress = true;
+        }
+        if (progress) {
+          polls = 0;
+        } else if (++polls > (1u << 24)) {
           ok = false;
           break;
         }
-        tc_fence_after();
-        const int s = i % STAGES;
-        const uint32_t v_addr = smem_u32(v_s + s * KV_BYTES);
-        const uint32_t p_addr = smem_u32(p_s + g * P_BYTES);
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          umma(tmem_base + (uint32_t)(O_COL + g * D), umma_desc(p_addr + k * 32),
-               umma_desc_mn(v_addr + k * 2048, KV_SLICE), idesc_o, (i >= 2) || k != 0);
-        umma_commit(&kv_empty[s]);
-        umma_commit(&o_done[g]);
-        // the group has read S[g] (it arrived on p_full): the scores of its next tile may overwrite it
-        if (i + 2 < n_kt) ok = issue_scores(i + 2);
       }
       if (!ok) failed = 1;
     }
@@ -304,6 +340,10 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
           sv[32 + c] = b[c];
         }
       }
+      // the scores are in registers: the next scores of this group may overwrite S[g]
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[g]);
       // tiles every row of the CTA sees whole (most of them) skip the mask
       if (!(key0 + BN - 1 <= pos0 && key0 >= lo_top)) {
 #pragma unroll

@@ -37,11 +37,19 @@ CONFIG_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 intermediate_size=150, vocab_size=211, rope_theta=777.0, rms_norm_eps=2e-6,
                 hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=512,
                 use_sliding_window=False)
+# head size 64: portions of prompts run on the tcgen05 attention kernel, one layer with a window
+CONFIG_E = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+                hidden_size=72, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+                intermediate_size=160, vocab_size=300, rope_theta=20000.0, rms_norm_eps=1e-5,
+                hidden_act="silu", tie_word_embeddings=True, max_position_embeddings=2048,
+                use_sliding_window=True, sliding_window=50,
+                layer_types=["sliding_attention", "full_attention"])
 TINY = {
     "a": dict(config=CONFIG_A, seed=0, std=0.02, page_size=16),
     "b": dict(config=CONFIG_B, seed=1, std=0.05, page_size=8),
     "c": dict(config=CONFIG_C, seed=7, std=0.04, page_size=16),
     "d": dict(config=CONFIG_D, seed=9, std=0.06, page_size=32),
+    "e": dict(config=CONFIG_E, seed=4, std=0.05, page_size=8),
 }
 
 

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
-    for name in ("a", "b", "c"):
+    for name in ("a", "b", "c", "e"):
         d = str(tmp_path_factory.mktemp(f"model_{name}"))
         out[name] = (d,) + ru.make_model_folder(d, name, dtype="bfloat16")
     return out
@@ -110,6 +110,30 @@ def test_continuous_batching_chunked_mixed_greedy_and_temperature(folders, dtype
             agree = sum(g == w for g, w in zip(got, want))
             assert agree >= 10, (rid, got, want)
     assert engine.runner.cache.num_free_pages() == 48
+
+
+def test_head_size_64_chunked_prompts_beside_decoding(folders):
+    """The configuration whose portions of prompts run on the tcgen05 attention kernel (one
+    layer with a window of 50): prompts longer than a key tile, cut into portions of 48 beside
+    decoded tokens, greedy, against the plain implementation."""
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    from dispec_b200.ops import attention as A
+    folder, config, weights = folders["e"]
+    assert A.tcgen05_supported(config["head_dim"], 3, 8, torch.bfloat16)
+    engine = ContinuousBatchingEngine(load(folder, "bfloat16"), KVConfig(block_size=8), num_blocks=160,
+                                      max_batch_tokens=64, chunk_size=48)
+    reqs = []
+    for i, n in enumerate([150, 7, 260, 97]):
+        prompt = ru.random_ids(n, config["vocab_size"], 600 + i)
+        reqs.append((engine.add_request(prompt, 10, SamplingParams()), prompt))
+    engine.run_until_done()
+    out = engine.collect_outputs()
+    for rid, prompt in reqs:
+        got = out[rid]
+        want, margin = replay_sampling(weights, config, prompt, got, SamplingParams())
+        scale = 0.03 * plain.forward_logits(weights, config, prompt).abs().max().item() + 0.02
+        assert got == want or margin < 2 * scale, (rid, got, want, margin)
+    assert engine.runner.cache.num_free_pages() == 160
 
 
 def test_no_leak_between_identical_requests(folders):

@@ -1,7 +1,7 @@
 """bin/trace_run against the plain implementation: the same requests whole, with the last 32
 tokens one by one, in portions of changing size down to two tokens, and mixed (up to four
 live, portions beside decoded tokens, few pages so that they are used again, freed pages
-filled with NaN), in float32 and in bfloat16, for four tiny configurations."""
+filled with NaN), in float32 and in bfloat16, for five tiny configurations."""
 import pytest
 import torch
 
@@ -10,7 +10,8 @@ import replay_util as ru
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 40, 64, 131], "c": [3, 50, 97, 150], "d": [2, 45, 100]}
+LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 40, 64, 131], "c": [3, 50, 97, 150], "d": [2, 45, 100],
+           "e": [4, 66, 130, 300]}
 
 
 def check(name, dtype, tmp_path):
@@ -42,11 +43,11 @@ def check(name, dtype, tmp_path):
     return worst
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_replay_float32(name, tmp_path):
     check(name, "float32", tmp_path)
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_replay_bfloat16(name, tmp_path):
     check(name, "bfloat16", tmp_path)
