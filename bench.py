@@ -151,12 +151,26 @@ def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
         for e, t in zip(batch, toks):
             last[e.req_id] = t
     pos = {rid: len(p) for rid, p in zip(ids, prompts)}
+    # Each step takes its tokens from the previous step's result on the device and copies its own
+    # result to pinned host memory; the host reads that copy one step later, while the next step
+    # runs (the engine's overlapped steps, without the scheduler).
+    state = {"tokens": torch.tensor([last[rid] for rid in ids], dtype=torch.int32, device=runner.device),
+             "pending": None}
+    host = [torch.empty(len(ids), dtype=torch.int32, pin_memory=True) for _ in range(2)]
 
     def one_step():
-        entries = [SeqEntry(rid, [last[rid]], pos[rid], [0]) for rid in ids]
-        toks = ops.argmax(runner.step(entries)).tolist()  # device -> host read of the result
-        for rid, t in zip(ids, toks):
-            last[rid] = t
+        entries = [SeqEntry(rid, [0], pos[rid], [0], feed_row=i) for i, rid in enumerate(ids)]
+        toks = ops.argmax(runner.step(entries, feed_tokens=state["tokens"]))
+        turn = runner.num_steps & 1
+        host[turn].copy_(toks, non_blocking=True)  # device -> host copy of the result
+        ev = torch.cuda.Event()
+        ev.record()
+        previous, state["pending"], state["tokens"] = state["pending"], (host[turn], ev), toks
+        if previous is not None:
+            previous[1].synchronize()
+            for rid, t in zip(ids, previous[0].tolist()):
+                last[rid] = t
+        for rid in ids:
             pos[rid] += 1
 
     for _ in range(warmup):

@@ -85,6 +85,10 @@ class CacheManager:
     def num_available_pages(self, group: int = 0) -> int:
         return self.pools[group].available
 
+    def min_free_pages(self) -> int:
+        """Pages no request holds or has reserved, in the group that has the fewest."""
+        return min(pool.available for pool in self.pools)
+
     def free_slots(self) -> int:
         return len(self._free_slots)
 

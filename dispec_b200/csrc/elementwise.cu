@@ -44,6 +44,34 @@ extern "C" int dsp_embed(const void* table, const int* ids, void* out, int T, in
   return 0;
 }
 
+// ------------------------------------------------------------------ tokens fed on the device
+// ids[t] = prev[src[t]] where src[t] >= 0: the token a request sampled in the previous step becomes
+// its input in this one without a round trip through the host.  A source row outside prev is
+// recorded in the device error word; the value itself is range-checked by the embedding kernel.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src,
+                                   const int* __restrict__ prev, int n, int n_prev, int* err) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const int s = src[t];
+  if (s < 0) return;
+  if (s >= n_prev) {
+    atomicOr(err, DSP_ERR_BAD_TOKEN);
+    return;
+  }
+  ids[t] = prev[s];
+}
+
+extern "C" int dsp_feed_tokens(int* ids, const int* src, const int* prev, int n, int n_prev,
+                               cudaStream_t stream) {
+  if (n == 0) return 0;
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_feed_tokens: no device error word");
+  DSP_REQUIRE(ids && src && prev && n_prev > 0, "dsp_feed_tokens: missing operand");
+  feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, src, prev, n, n_prev, err);
+  DSP_CHECK_LAUNCH("dsp_feed_tokens");
+  return 0;
+}
+
 // ------------------------------------------------------------------------------ RMSNorm
 // y = w * round_T( x * rsqrt(mean(x^2) + eps) ), x read as 32-bit, the product with w
 // rounded once more to T (for float both roundings are the identity).

@@ -24,6 +24,7 @@ class SeqEntry:
     tokens: list
     start: int  # position of tokens[0]; equals the request's stored length
     want: list = field(default_factory=list)  # indices into tokens
+    feed_row: int = -1  # >= 0: the single token is row feed_row of the previous step's sampled tokens
 
 
 @dataclass
@@ -62,6 +63,7 @@ class StepContext:
         self.ctx_len = None  # [S] int32: stored length after this step
         self.state_slot = None  # [S] int32
         self.logit_rows = None  # [n] int32
+        self.feed_src = None  # [S] int32: row of the previous step's tokens that feeds a single token, or -1
         self.logit_rows_are_all = False  # the wanted rows are 0..T-1 in order
         self.page_tables: list = []  # per cache group [S, max_pages] int32
         self.host_q_len: list = []
@@ -75,6 +77,7 @@ class StepContext:
         self.cache_groups = None
         self.page_size = 0
         self.decode_splits = 0  # fixed number of key splits for single-token rows (0: chosen per step)
+        self.num_fed = 0  # single tokens whose value comes from the previous step on the device
         self.graph_capture = False  # host-side choices must not depend on the step's values
         self.scratch: dict = {}
 
@@ -153,6 +156,7 @@ def plan_layout(T: int, S: int, n_rows: int, pages_per_group: list, tiles: dict)
     put("ctx_len", S)
     put("state_slot", S)
     put("logit_rows", n_rows)
+    put("feed_src", S)
     for g, mp in enumerate(pages_per_group):
         put(f"page_table{g}", S * mp)
     for tpt, nt in tiles.items():
@@ -173,6 +177,12 @@ class StepPlanLayout:
         ctx_lens = [e.start + len(e.tokens) for e in self.sorted_entries]
         self.num_real_seqs = real
         self.num_decode = sum(1 for q in q_lens if q == 1)
+        self.num_fed = 0
+        for e in self.sorted_entries:
+            if e.feed_row >= 0:
+                if len(e.tokens) != 1:
+                    raise ValueError(f"request {e.req_id!r}: only a single token can be fed on the device")
+                self.num_fed += 1
         if pad_seqs is not None:
             # fixed-shape batch of single tokens: padding rows have position -1 and length 0
             if self.num_decode != real or real > pad_seqs:
@@ -238,6 +248,11 @@ class StepPlanLayout:
         slots[:] = 0
         slots[:self.num_real_seqs] = [cache.state_slot(e.req_id) for e in self.sorted_entries]
         view("logit_rows")[:] = self.rows
+        feed = view("feed_src")
+        feed[:] = -1
+        if self.num_fed:
+            # single-token entries come first: the flat row of sequence s is s
+            feed[:self.num_real_seqs] = [e.feed_row if len(e.tokens) == 1 else -1 for e in self.sorted_entries]
         for g, mp in enumerate(self.pages_per_group):
             pt = view(f"page_table{g}").reshape(self.S, mp)
             pt[:] = -1
@@ -266,6 +281,7 @@ class StepPlanLayout:
         ctx.seq_of_token = dview("seq_of_token")
         ctx.q_start, ctx.ctx_len, ctx.state_slot = dview("q_start"), dview("ctx_len"), dview("state_slot")
         ctx.logit_rows = dview("logit_rows")
+        ctx.feed_src = dview("feed_src")
         ctx.logit_rows_are_all = self.rows == list(range(self.T))
         ctx.page_tables = [dview(f"page_table{g}").view(self.S, mp)
                            for g, mp in enumerate(self.pages_per_group)]
@@ -286,4 +302,6 @@ def build_context(entries: list, cache, storage, states, staging: HostStaging, d
     the logits the step returns (logit rows follow the original order of entries and wants)."""
     plan = StepPlanLayout(entries, cache, tile_tokens, vocab_size)
     dev = staging.upload(plan.total, plan.fill)
-    return plan.context(dev, storage, states, dtype, device), plan.row_offsets
+    ctx = plan.context(dev, storage, states, dtype, device)
+    ctx.num_fed = plan.num_fed
+    return ctx, plan.row_offsets

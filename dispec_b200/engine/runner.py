@@ -64,9 +64,11 @@ class ModelRunner:
 
     # ----------------------------------------------------------------------- the step
     @torch.inference_mode()
-    def step(self, entries: list[SeqEntry]) -> torch.Tensor:
+    def step(self, entries: list[SeqEntry], feed_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [number of wanted places, vocab] in float32, in the order of ``entries`` and
-        of each entry's ``want``."""
+        of each entry's ``want``.  ``feed_tokens`` (int32, on the device): the tokens sampled in
+        the previous step; an entry with ``feed_row`` r takes its single token from row r of it
+        on the device, so the host need not have seen that token yet."""
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         seen = set()
@@ -82,14 +84,18 @@ class ModelRunner:
             if e.start != stored:
                 raise ValueError(f"request {e.req_id!r}: tokens start at position {e.start} but "
                                  f"{stored} tokens are stored")
+        if any(e.feed_row >= 0 for e in entries) and feed_tokens is None:
+            raise ValueError("an entry is fed from the previous step but feed_tokens is missing")
         for e in entries:  # may raise OutOfPagesError before anything ran
             self.cache.extend(e.req_id, e.start + len(e.tokens))
         if (self.cuda_graph and self.graph_buckets and len(entries) <= self.graph_buckets[-1]
                 and all(len(e.tokens) == 1 for e in entries)):
-            return self._graph_step(entries)
+            return self._graph_step(entries, feed_tokens)
         ctx, _ = build_context(entries, self.cache, self.storage, self.states, self.staging,
                                self.dtype, self.device, self.model.attention_tile_tokens,
                                self.vocab_size)
+        if ctx.num_fed:
+            ops.feed_tokens(ctx.token_ids, ctx.feed_src, feed_tokens)
         x, pending = self.model.forward(ctx)
         n_rows = ctx.logit_rows.shape[0]
         if n_rows:
@@ -135,13 +141,16 @@ class ModelRunner:
         self._graphs[bucket] = entry
         return entry
 
-    def _graph_step(self, entries: list) -> torch.Tensor:
+    def _graph_step(self, entries: list, feed_tokens=None) -> torch.Tensor:
         bucket = next(b for b in self.graph_buckets if b >= len(entries))
         g = self._graphs.get(bucket) or self._capture(bucket)
         plan = StepPlanLayout(entries, self.cache, self.model.attention_tile_tokens, self.vocab_size,
                               pad_seqs=bucket, fixed_pages=self._graph_pages)
         assert plan.total == g["total"]
         self.staging.upload(plan.total, plan.fill, into=g["buffer"])
+        if plan.num_fed:
+            (o_ids, n_ids), (o_src, n_src) = plan.layout["token_ids"], plan.layout["feed_src"]
+            ops.feed_tokens(g["buffer"][o_ids:o_ids + n_ids], g["buffer"][o_src:o_src + n_src], feed_tokens)
         g["graph"].replay()
         _library.LaunchCounter.n += g["launches"]
         for e in entries:

@@ -14,6 +14,16 @@ waiting queue with prompt + emitted tokens as its new prompt, and it keeps what 
 A request that could never fit the pool alone is refused in ``add_request``.  Sampling uses
 each request's own parameters and generator.
 
+Overlapped steps (not in the reference): the engine launches step n + 1 before it has read the
+tokens of step n.  ``Scheduler.launched`` puts a placeholder into the output of every request
+the step samples for (so lengths, and finishing by length, are known at once);
+``Scheduler.resolve`` fills the placeholders in when the tokens arrive and retires requests
+that drew their end-of-sequence token, one step late: such a request has one more step in
+flight, whose token is dropped.  A request whose newest token is a placeholder is scheduled
+with ``SeqEntry.feed_row``: the step takes the token from the previous step's result on the
+device.  Preemption needs the real tokens (the request is recomputed from them), so the
+engine resolves the step in flight first whenever pages are short.
+
 ``Scheduler`` is pure bookkeeping over a ``CacheManager`` (testable without a GPU);
 ``ContinuousBatchingEngine`` joins it with the step function and the sampler.
 """
@@ -23,11 +33,16 @@ import itertools
 from dataclasses import dataclass, field
 from enum import Enum, auto
 
+import torch
+
 from dispec_b200.cache.manager import CacheManager
 from dispec_b200.cache.pages import OutOfPagesError
 from dispec_b200.config.engine_config import KVConfig
 from dispec_b200.engine.batch import SeqEntry
 from dispec_b200.sampling.sampler import SamplingParams, make_rng
+
+
+PENDING = -1  # placeholder in output_ids for a token that a step in flight will sample
 
 
 class State(Enum):
@@ -53,6 +68,7 @@ class Request:
     finish_reason: str | None = None
     rng: object = None
     _recompute: list | None = None  # prompt + emitted tokens after a preemption
+    _pending_row: int = -1  # row of the newest launched step's tokens that holds output_ids[-1]
 
     @property
     def feed(self) -> list:
@@ -72,6 +88,7 @@ class StepPlan:
     sampled: list  # requests that get a token this step, in the order of the logits rows
     num_decode_tokens: int = 0
     num_prefill_tokens: int = 0
+    pending_index: dict = field(default_factory=dict)  # request id -> index of its placeholder in output_ids
 
 
 class Scheduler:
@@ -123,6 +140,9 @@ class Scheduler:
 
     # ------------------------------------------------------------------------ preemption
     def _preempt(self, req: Request) -> None:
+        if PENDING in req.output_ids:
+            raise RuntimeError("a request with a token still in flight cannot be preempted "
+                               "(resolve the launched step first)")
         self._on_free(req.id)
         if req in self.running:
             self.running.remove(req)
@@ -174,7 +194,10 @@ class Scheduler:
             if not placed:
                 continue
             self.cache.extend(req.id, stored + 1)
-            entries[req.id] = SeqEntry(req.id, [req.output_ids[-1]], stored, [0])
+            if req.output_ids[-1] == PENDING:  # sampled by the step in flight: fed on the device
+                entries[req.id] = SeqEntry(req.id, [0], stored, [0], feed_row=req._pending_row)
+            else:
+                entries[req.id] = SeqEntry(req.id, [req.output_ids[-1]], stored, [0])
             sampled.append(req)
             budget -= 1
             n_dec += 1
@@ -222,22 +245,60 @@ class Scheduler:
         self.num_prefill_tokens += n_pre
         return StepPlan(ordered, want_rows, n_dec, n_pre)
 
-    def process(self, plan: StepPlan, token_ids: list) -> list[Request]:
-        """Appends the sampled tokens, retires finished requests; returns those retired."""
+    def needs_resolved_tokens(self) -> bool:
+        """True when the next ``schedule`` may have to preempt, which needs every emitted token
+        on the host: some cache group has fewer free pages than there are running requests."""
+        if not self.running:
+            return False
+        return self.cache.min_free_pages() < len(self.running)
+
+    def launched(self, plan: StepPlan) -> None:
+        """The step is on its way.  Every request it samples for gets a placeholder for the
+        token; a request that reaches its length with it retires now (its pages may be given
+        to steps launched later, which run after this one)."""
         self.num_steps += 1
+        for row, req in enumerate(plan.sampled):
+            plan.pending_index[req.id] = len(req.output_ids)
+            req.output_ids.append(PENDING)
+            req._pending_row = row
+            if len(req.output_ids) >= req.max_new_tokens:
+                req.finish_reason = "length"
+                self._retire(req)
+
+    def resolve(self, plan: StepPlan, token_ids: list) -> list[Request]:
+        """The tokens of a launched step have arrived: fills the placeholders in and retires
+        requests that drew their end-of-sequence token; returns the requests that are complete."""
         done = []
         for req, tid in zip(plan.sampled, token_ids):
-            req.output_ids.append(int(tid))
-            if req.done:
-                req.finish_reason = ("stop" if req.eos_id is not None and req.output_ids[-1] == req.eos_id
-                                     else "length")
-                req.state = State.FINISHED
+            idx = plan.pending_index.get(req.id)
+            if idx is None or idx >= len(req.output_ids) or req.output_ids[idx] != PENDING:
+                continue  # cut off: the request ended at an earlier token
+            req.output_ids[idx] = int(tid)
+            if idx == len(req.output_ids) - 1:
+                req._pending_row = -1
+            if req.eos_id is not None and int(tid) == req.eos_id:
+                del req.output_ids[idx + 1:]  # a later step in flight sampled past the end
+                req._pending_row = -1
+                req.finish_reason = "stop"
+                if req.state != State.FINISHED:
+                    self._retire(req)
                 done.append(req)
-        for req in done:
-            self.running.remove(req)
-            self.finished.append(req)
-            self._on_free(req.id)
+            elif req.state == State.FINISHED and idx == len(req.output_ids) - 1:
+                done.append(req)
         return done
+
+    def _retire(self, req: Request) -> None:
+        req.state = State.FINISHED
+        if req in self.running:
+            self.running.remove(req)
+        self.finished.append(req)
+        self._on_free(req.id)
+
+    def process(self, plan: StepPlan, token_ids: list) -> list[Request]:
+        """Appends the sampled tokens, retires finished requests; returns those retired
+        (``launched`` and ``resolve`` in one, for a caller that waits for every step)."""
+        self.launched(plan)
+        return self.resolve(plan, token_ids)
 
 
 class ContinuousBatchingEngine:
@@ -249,7 +310,7 @@ class ContinuousBatchingEngine:
 
     def __init__(self, model, kv: KVConfig | None = None, num_blocks: int = 2048,
                  max_batch_tokens: int = 2048, chunk_size: int | None = None, max_num_seqs: int = 256,
-                 cuda_graph: bool = True, poison: bool = False):
+                 cuda_graph: bool = True, poison: bool = False, overlap: bool = True):
         from dispec_b200.engine.runner import ModelRunner
         from dispec_b200.sampling.sampler import Sampler
 
@@ -261,6 +322,14 @@ class ContinuousBatchingEngine:
         self.scheduler = Scheduler(self.runner.cache, max_batch_tokens, chunk_size,
                                    max_model_len=model.spec.max_position or None,
                                    on_admit=self.runner.admit, on_free=self.runner.release)
+        # overlap: step n + 1 is scheduled and launched while step n runs; its tokens are read
+        # one step late (outputs and the queues lag by one step until has_work / collect_outputs /
+        # run_until_done catch up)
+        self.overlap = overlap
+        self._inflight = None  # (plan, tokens on the device, pinned host copy, event)
+        self._host_tokens = [torch.empty(max(max_num_seqs, 1), dtype=torch.int32, pin_memory=True)
+                             for _ in range(3)]
+        self._turn = 0
 
     # queues and counters under the reference's names
     waiting = property(lambda self: self.scheduler.waiting)
@@ -277,22 +346,53 @@ class ContinuousBatchingEngine:
         return self.scheduler.add_request(prompt_ids, max_new_tokens, params, eos_id, priority)
 
     def step(self) -> None:
-        plan = self.scheduler.schedule()
+        sched = self.scheduler
+        if self._inflight is not None and (not self.overlap or sched.needs_resolved_tokens()):
+            self.flush()
+        plan = sched.schedule()
         if not plan.entries:
+            self.flush()
             return
-        logits = self.runner.step(plan.entries)
-        tokens = self.sampler.sample(logits, [r.params for r in plan.sampled],
-                                     [r.rng for r in plan.sampled])
-        self.scheduler.process(plan, tokens)
+        feed = self._inflight[1] if self._inflight is not None else None
+        logits = self.runner.step(plan.entries, feed_tokens=feed)
+        tokens = self.sampler.sample_device(logits, [r.params for r in plan.sampled],
+                                            [r.rng for r in plan.sampled])
+        self._turn = (self._turn + 1) % len(self._host_tokens)
+        if tokens.shape[0] > self._host_tokens[self._turn].shape[0]:
+            self._host_tokens[self._turn] = torch.empty(tokens.shape[0], dtype=torch.int32, pin_memory=True)
+        host = self._host_tokens[self._turn][:tokens.shape[0]]
+        host.copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        sched.launched(plan)
+        previous, self._inflight = self._inflight, (plan, tokens, host, event)
+        if previous is not None:
+            self._resolve(previous)
+        if not self.overlap:
+            self.flush()
+
+    def _resolve(self, launched) -> None:
+        plan, _, host, event = launched
+        event.synchronize()
+        self.scheduler.resolve(plan, host.tolist())
+
+    def flush(self) -> None:
+        """Reads the tokens of the step in flight, if any: afterwards outputs and queues are current."""
+        if self._inflight is not None:
+            launched, self._inflight = self._inflight, None
+            self._resolve(launched)
 
     def collect_outputs(self) -> dict:
+        self.flush()
         return self.scheduler.collect_outputs()
 
     def has_work(self) -> bool:
+        self.flush()
         return self.scheduler.has_work()
 
     def run_until_done(self, max_steps: int = 100_000) -> None:
         steps = 0
-        while self.has_work() and steps < max_steps:
+        while (self.scheduler.has_work() or self._inflight is not None) and steps < max_steps:
             self.step()
             steps += 1
+        self.flush()

@@ -27,6 +27,17 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def feed_tokens(ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
+    """ids[t] = prev[src[t]] where src[t] >= 0 (all int32, on the device): tokens sampled in the
+    previous step become inputs of this one without passing through the host."""
+    _cuda(ids, src, prev)
+    assert ids.dtype == src.dtype == prev.dtype == torch.int32
+    assert ids.is_contiguous() and src.is_contiguous() and prev.is_contiguous()
+    assert src.shape[0] <= ids.shape[0]
+    L.check(L.core().dsp_feed_tokens(L.ptr(ids), L.ptr(src), L.ptr(prev), src.shape[0], prev.shape[0],
+                                     L.stream_handle()))
+
+
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.Tensor | None = None,
              rows: torch.Tensor | None = None, write_back: bool = False,
              out: torch.Tensor | None = None) -> torch.Tensor:

@@ -48,14 +48,20 @@ class Sampler:
     def __init__(self, device):
         self.device = device
 
-    @torch.inference_mode()
     def sample(self, logits: torch.Tensor, params: list, rngs: list) -> list[int]:
-        n = logits.shape[0]
-        if n == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.sample_device(logits, params, rngs).tolist()
+
+    @torch.inference_mode()
+    def sample_device(self, logits: torch.Tensor, params: list, rngs: list) -> torch.Tensor:
+        """The same draw, left on the device (int32 [n]): the caller reads it when it needs it."""
+        n = logits.shape[0]
         assert len(params) == n and len(rngs) == n
+        if n == 0:
+            return torch.empty((0,), dtype=torch.int32, device=logits.device)
         if all(p.greedy for p in params):
-            return ops.argmax(logits).tolist()
+            return ops.argmax(logits)
         host = torch.empty((4, n), dtype=torch.float32, pin_memory=True)
         for i, (p, rng) in enumerate(zip(params, rngs)):
             host[0, i] = p.temperature
@@ -64,8 +70,7 @@ class Sampler:
             host[3, i] = 0.0 if p.greedy else min(rng.random(), _BELOW_ONE)
         dev = host.to(self.device, non_blocking=True)
         top_k = dev[1].to(torch.int32)
-        return ops.sample(logits, dev[0].contiguous(), top_k, dev[2].contiguous(),
-                          dev[3].contiguous()).tolist()
+        return ops.sample(logits, dev[0].contiguous(), top_k, dev[2].contiguous(), dev[3].contiguous())
 
 
 def sample(logits: torch.Tensor, params: SamplingParams, generator=None) -> torch.Tensor:

@@ -136,6 +136,50 @@ def test_head_size_64_chunked_prompts_beside_decoding(folders):
     assert engine.runner.cache.num_free_pages() == 160
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_steps_give_the_same_tokens_as_waiting_for_every_step(folders, dtype):
+    """Step n + 1 launched before the tokens of step n are read (tokens fed on the device, end of
+    sequence seen one step late) against the engine that waits for every step: the same outputs,
+    with ends of sequence in mid-stream, temperature sampling, portions of prompts and arrivals
+    while others decode."""
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    folder, config, weights = folders["b"]
+    model = load(folder, dtype)
+    prompts = [ru.random_ids(n, config["vocab_size"], 700 + i) for i, n in enumerate([1, 9, 40, 64, 9, 23])]
+
+    def run(overlap, eos):
+        engine = ContinuousBatchingEngine(model, KVConfig(block_size=8), num_blocks=64, max_batch_tokens=32,
+                                          chunk_size=16, overlap=overlap)
+        ids = []
+        for i, p in enumerate(prompts[:4]):
+            params = SamplingParams(temperature=0.7 if i % 2 else 0.0, top_k=20 if i == 1 else 0, seed=90 + i)
+            ids.append(engine.add_request(p, 14, params, eos_id=eos.get(i)))
+        for _ in range(5):
+            engine.step()
+        for i, p in enumerate(prompts[4:], start=4):  # arrive while the others decode
+            ids.append(engine.add_request(p, 14, SamplingParams(seed=90 + i), eos_id=eos.get(i)))
+        engine.run_until_done()
+        out = engine.collect_outputs()
+        assert engine.runner.cache.num_free_pages() == 64
+        assert not engine.has_work()
+        return [out[i] for i in ids], engine.num_steps
+
+    free_run, _ = run(False, {})
+    eos, cut = {}, {}
+    for i, toks in enumerate(free_run):  # a token in mid-stream that did not occur before it
+        for k in range(2, 11):
+            if toks[k] not in toks[:k]:
+                eos[i], cut[i] = toks[k], k + 1
+                break
+    assert len(eos) >= 2, "too few requests can stop in mid-stream with these weights"
+    waited, steps_waited = run(False, eos)
+    overlapped, steps_overlapped = run(True, eos)
+    assert waited == overlapped
+    for i, tok in eos.items():
+        assert waited[i] == free_run[i][:cut[i]] and waited[i][-1] == tok
+    assert steps_overlapped >= steps_waited
+
+
 def test_no_leak_between_identical_requests(folders):
     from dispec_b200 import ContinuousBatchingEngine, SamplingParams
     folder, config, _ = folders["a"]

@@ -203,3 +203,142 @@ def test_a_request_that_can_never_fit_is_refused():
     sched.add_request(list(range(8)), 1)  # 8 stored positions fit exactly
     with pytest.raises(ValueError):
         sched.add_request([], 2)
+
+
+# ------------------------------------------------------------------- overlapped steps
+def run_overlapped(sched, cache, model, max_steps=10000):
+    """The engine's loop with one step in flight: step n + 1 is scheduled and run before the
+    tokens of step n are resolved; an entry with feed_row takes its token from the result of
+    the step before, as the device does."""
+    inflight = None
+    steps = 0
+    wasted = 0
+
+    def resolve(launched):
+        for r in sched.resolve(*launched):
+            model.forget(r.id)
+
+    while (sched.has_work() or inflight) and steps < max_steps:
+        if inflight and sched.needs_resolved_tokens():
+            resolve(inflight)
+            inflight = None
+        plan = sched.schedule()
+        cache.check()
+        if not plan.entries:
+            assert inflight, "a step with work scheduled nothing"
+            resolve(inflight)
+            inflight = None
+            continue
+        for e in plan.entries:
+            if e.feed_row >= 0:
+                assert e.tokens == [0] and inflight is not None
+                e.tokens = [inflight[1][e.feed_row]]
+        tokens = model.step(plan, cache)
+        wasted += sum(1 for r in plan.sampled if r.state == State.FINISHED and r.finish_reason == "stop")
+        sched.launched(plan)
+        previous, inflight = inflight, (plan, tokens)
+        if previous:
+            resolve(previous)
+        steps += 1
+    assert not sched.has_work() and inflight is None
+    return steps
+
+
+def test_overlap_feeds_the_token_in_flight_by_its_row():
+    from dispec_b200.engine.scheduler import PENDING
+    sched, cache = make()
+    a = sched.add_request([1, 2, 3], 4)
+    b = sched.add_request([4, 5], 4)
+    plan0 = sched.schedule()
+    for e in plan0.entries:
+        cache.commit(e.req_id, e.start + len(e.tokens))
+    sched.launched(plan0)
+    assert [r.output_ids for r in plan0.sampled] == [[PENDING], [PENDING]]
+    plan1 = sched.schedule()
+    assert [(e.req_id, e.tokens, e.feed_row) for e in plan1.entries] == [(a, [0], 0), (b, [0], 1)]
+    for e in plan1.entries:
+        cache.commit(e.req_id, e.start + 1)
+    sched.launched(plan1)
+    sched.resolve(plan0, [11, 12])
+    assert [r.output_ids for r in plan0.sampled] == [[11, PENDING], [12, PENDING]]
+    # the newest token is still in flight: fed again, from the rows of plan1
+    plan2 = sched.schedule()
+    assert [(e.tokens, e.feed_row) for e in plan2.entries] == [([0], 0), ([0], 1)]
+    for e in plan2.entries:
+        cache.commit(e.req_id, e.start + 1)
+    sched.launched(plan2)
+    sched.resolve(plan1, [21, 22])
+    sched.resolve(plan2, [31, 32])
+    plan3 = sched.schedule()  # everything resolved: tokens come from the host again
+    assert [(e.tokens, e.feed_row) for e in plan3.entries] == [([31], -1), ([32], -1)]
+
+
+def test_overlap_end_of_sequence_is_seen_one_step_late_and_length_at_once():
+    sched, cache = make()
+    model = FakeModel()
+    wire(sched, cache, model)
+    prompt = [5, 6, 7]
+    full = expected(prompt, 12)
+    eos = full[4]
+    assert eos not in full[:4]
+    stops = sched.add_request(prompt, 12, eos_id=eos)
+    short = sched.add_request([9, 8], 3)
+    free0 = cache.num_free_pages()
+    steps = run_overlapped(sched, cache, model)
+    out = sched.collect_outputs()
+    assert out[stops] == full[:5] and out[short] == expected([9, 8], 3)
+    by_id = {r.id: r for r in sched.finished}
+    assert by_id[stops].finish_reason == "stop" and by_id[short].finish_reason == "length"
+    # the request that stopped ran one step past its last token; nothing else did
+    assert steps == 6
+    assert cache.num_free_pages() == free0
+    cache.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_overlap_gives_the_same_tokens_as_waiting_for_every_step(seed):
+    import random
+    rnd = random.Random(seed)
+    reqs = []
+    for _ in range(12):
+        prompt = [rnd.randrange(VOCAB) for _ in range(rnd.randrange(1, 30))]
+        n = rnd.randrange(1, 20)
+        eos = rnd.choice([None, None, rnd.randrange(VOCAB)])
+        reqs.append((prompt, n, eos))
+    outs = []
+    for overlapped in (False, True):
+        sched, cache = make(pages=40, page_size=4, budget=24, chunk=8)
+        model = FakeModel()
+        wire(sched, cache, model)
+        ids = [sched.add_request(p, n, eos_id=e) for p, n, e in reqs]
+        (run_overlapped if overlapped else run)(sched, cache, model)
+        out = sched.collect_outputs()
+        outs.append([out[i] for i in ids])
+        assert cache.num_free_pages() == 40
+        cache.check()
+    assert outs[0] == outs[1]
+    for (p, n, e), got in zip(reqs, outs[1]):
+        assert got == expected(p, n, e)
+
+
+def test_overlap_resolves_first_when_pages_are_short_and_never_preempts_a_pending_token():
+    sched, cache = make(pages=6, page_size=4, budget=64)
+    a = sched.add_request([1] * 8, 12)
+    b = sched.add_request([2] * 8, 12)
+    model = FakeModel()
+    wire(sched, cache, model)
+    plan = sched.schedule()
+    model.step(plan, cache)
+    sched.launched(plan)
+    # 2 full pages each, 2 free, 2 running: enough for one more token each
+    assert not sched.needs_resolved_tokens()
+    plan2 = sched.schedule()
+    tokens2 = None
+    for e in plan2.entries:
+        e.tokens = [3]
+    tokens2 = model.step(plan2, cache)
+    sched.launched(plan2)
+    assert cache.min_free_pages() < 2 and sched.needs_resolved_tokens()
+    with pytest.raises(RuntimeError):
+        sched._preempt(sched.running[0])
+    assert a != b and tokens2 is not None
