@@ -348,28 +348,39 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
 }
 
 // ------------------------------------------------------------------------------------------
-// Single decoded tokens (the G rows of one KV head fit one 16-row mma tile): the key tiles of a
-// sequence are spread over the CTAs of a cluster (grid.z) and, inside a CTA, over its four warps,
-// each warp loading and processing whole 64-key tiles on its own (private shared memory, no CTA
-// barrier in the loop).  With 8 CTAs a context of 2048 keys is one tile per warp: one load
-// latency, one tile of arithmetic, then the 4 x grid.z partials are merged through distributed
-// shared memory, a row per warp.
-constexpr int DBN = 32;  // keys per warp tile: small enough that two or three CTAs share an SM and
-                        // every cluster of the launch is resident at once
+// Single decoded tokens (the G rows of one KV head fit one 16-row mma tile), built for latency:
+// a step's attention reads a few hundred KB per CTA, so what counts is how soon the bytes are
+// asked for, not how fast they stream.
+//  * The key tiles (16 keys) of a sequence are spread over the CTAs of a cluster (grid.z) and,
+//    inside a CTA, over its four warps; a warp loads and processes its tiles on its own
+//    (private ring of three tiles in shared memory, no CTA barrier in the loop).
+//  * Keys and values of earlier positions were written by earlier steps, and the page table and
+//    lengths by the host: they do not depend on the kernel before this one.  So the page ids of
+//    the CTA's range are fetched, and the first tiles of every warp are requested, BEFORE the
+//    kernel waits for its predecessor (programmatic dependent launch); only the query and the
+//    tile that holds the newest position wait.  With 8 CTAs a context of 1,500 keys is in flight
+//    before the previous kernel has ended.
+//  * Partials merge in two levels: the four warps of a CTA through its own shared memory, then
+//    the CTAs of the cluster through distributed shared memory with all remote reads of a row
+//    issued at once.
+constexpr int DK = 16;       // keys per warp tile
+constexpr int DSTAGES = 3;   // tiles in flight per warp
+constexpr int DEC_MAXP = 256;  // page ids of the CTA's range kept in shared memory
 constexpr int DEC_Q_BYTES = 16 * ROW_BYTES;
-constexpr int DEC_TILE_BYTES = DBN * ROW_BYTES;
-constexpr int DEC_PART_BYTES = (16 * D + 32) * 4;  // a warp's partial: [16][D] outputs and [16][2] (m, l)
-constexpr int DEC_WARP_BYTES = 2 * DEC_TILE_BYTES > DEC_PART_BYTES ? 2 * DEC_TILE_BYTES : DEC_PART_BYTES;
-constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES;
+constexpr int DEC_TILE_BYTES = DK * ROW_BYTES;
+constexpr int DEC_PART_BYTES = (16 * D + 32) * 4;  // a partial: [16][D] outputs and [16][2] (m, l)
+constexpr int DEC_RING_BYTES = DSTAGES * 2 * DEC_TILE_BYTES;
+constexpr int DEC_WARP_BYTES = DEC_RING_BYTES > DEC_PART_BYTES ? DEC_RING_BYTES : DEC_PART_BYTES;
+constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES + DEC_MAXP * 4;
 
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  // the tile list, lengths and page tables come from the host, not from the kernel before
   const int seq = p.tile_seq[tile];
   const int qs = p.q_start[seq];
   const int ctx = p.ctx_len[seq];
@@ -377,36 +388,74 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const int G = p.G;
   const int pos = ctx - 1;
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const int kt_begin = lo / DBN, kt_end = pos / DBN + 1;
+  const int kt_begin = lo / DK, kt_end = pos / DK + 1;
   const int per = (kt_end - kt_begin + nsplit - 1) / nsplit;
   const int my_begin = kt_begin + split * per;
   const int my_end = min(kt_end, my_begin + per);
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
   const uint32_t q_s = s_base;
-  const uint32_t k_s = s_base + DEC_Q_BYTES + warp * DEC_WARP_BYTES, v_s = k_s + DEC_TILE_BYTES;
+  unsigned char* warp_mem = smem + DEC_Q_BYTES + warp * DEC_WARP_BYTES;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(warp_mem);
+  float* cta_part = reinterpret_cast<float*>(smem + DEC_Q_BYTES + 4 * DEC_WARP_BYTES);
+  int* pages_s = reinterpret_cast<int*>(smem + DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES);
 
-  // Q: the G heads of this KV head, one row each
-  for (int i = tid; i < 16 * CHUNKS; i += THREADS) {
-    const int r = i / CHUNKS, chunk = i % CHUNKS;
-    const bool valid = r < G;
-    const bf16* src = valid ? p.q + (size_t)qs * p.q_stride + (size_t)(kvh * G + r) * D + chunk * 8 : p.q;
-    cp_async16(q_s + sw(r, chunk), src, valid);
-  }
-  cp_async_commit();
+  // ---- before the wait: page ids of this CTA's keys, then the first tiles of every warp
+  const int first_page = my_begin < my_end ? (my_begin * DK) / p.page_size : 0;
+  const int last_page = my_begin < my_end ? min(pos, my_end * DK - 1) / p.page_size : -1;
+  const int n_pages = last_page - first_page + 1;
+  const bool cached = n_pages <= DEC_MAXP;
+  if (cached)
+    for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = table[first_page + i];
+  __syncthreads();
 
-  auto load_tile = [&](int kt) {  // by one warp: consecutive lanes take consecutive 16-byte pieces of a row
+  // a tile lies within one page when the page size is a multiple of the tile (the usual case): one
+  // page lookup per tile, and a lane's pieces differ by a constant row stride
+  const bool tile_in_page = p.page_size % DK == 0;
+  auto load_tile = [&](int kt, int stage) {  // by one warp: consecutive lanes take consecutive 16-byte pieces of a row
+    const uint32_t k_s = ring + stage * 2 * DEC_TILE_BYTES, v_s = k_s + DEC_TILE_BYTES;
+    if (tile_in_page) {
+      const int b0 = kt * DK;
+      const int lp = b0 / p.page_size;
+      const int page = cached ? pages_s[lp - first_page] : table[lp];
+      const bool page_ok = page >= 0 && page < p.num_pages;
+      if (!page_ok && lane == 0 && b0 <= pos && b0 + DK > lo) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+      const size_t base = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + (b0 % p.page_size)) * D;
+      constexpr int ROWS_PER_PASS = 32 / CHUNKS > 0 ? 32 / CHUNKS : 1;
+      if constexpr (32 % CHUNKS == 0) {  // whole rows per pass of the warp
+        const int r0 = lane / CHUNKS, chunk = lane % CHUNKS;
+#pragma unroll
+        for (int r = r0; r < DK; r += ROWS_PER_PASS) {
+          const int b = b0 + r;
+          const bool valid = page_ok && b <= pos && b >= lo;
+          const size_t off = base + (size_t)r * D + chunk * 8;
+          cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
+          cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
+        }
+      } else {
 #pragma unroll 4
-    for (int i = lane; i < DBN * CHUNKS; i += 32) {
+        for (int i = lane; i < DK * CHUNKS; i += 32) {
+          const int r = i / CHUNKS, chunk = i % CHUNKS;
+          const int b = b0 + r;
+          const bool valid = page_ok && b <= pos && b >= lo;
+          const size_t off = base + (size_t)r * D + chunk * 8;
+          cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
+          cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
+        }
+      }
+      return;
+    }
+#pragma unroll 4
+    for (int i = lane; i < DK * CHUNKS; i += 32) {
       const int r = i / CHUNKS, chunk = i % CHUNKS;
-      const int b = kt * DBN + r;
-      bool valid = b <= pos;
+      const int b = kt * DK + r;
+      bool valid = b <= pos && b >= lo;
       size_t off = 0;
       if (valid) {
         const int lp = p.page_shift >= 0 ? (b >> p.page_shift) : (b / p.page_size);
         const int within = p.page_shift >= 0 ? (b & (p.page_size - 1)) : (b % p.page_size);
-        const int page = table[lp];
+        const int page = cached ? pages_s[lp - first_page] : table[lp];
         if (page < 0 || page >= p.num_pages) {
-          if (b >= lo && chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          if (chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
           valid = false;
         } else {
           off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D + chunk * 8;
@@ -415,8 +464,40 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       cp_async16(k_s + sw(r, chunk), p.k_pool + off, valid);
       cp_async16(v_s + sw(r, chunk), p.v_pool + off, valid);
     }
-    cp_async_commit();
   };
+
+  // this warp's tiles: my_begin + warp, + 4, ...; the tile that holds the newest position (always the
+  // last tile of the sequence) is requested after the wait, every other one may go at once
+  const int first = my_begin + warp;
+  const int newest = pos / DK;
+  int issued = 0;  // tiles of this warp requested so far (one commit group each, in order)
+  for (int j = 0; j < DSTAGES; ++j) {
+    const int kt = first + 4 * j;
+    if (kt >= my_end || kt == newest) break;
+    load_tile(kt, j);
+    cp_async_commit();
+    ++issued;
+  }
+
+  pdl_wait();
+  // Q: the G heads of this KV head, one row each
+  for (int i = tid; i < 16 * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, chunk = i % CHUNKS;
+    const bool valid = r < G;
+    const bf16* src = valid ? p.q + (size_t)qs * p.q_stride + (size_t)(kvh * G + r) * D + chunk * 8 : p.q;
+    cp_async16(q_s + sw(r, chunk), src, valid);
+  }
+  cp_async_commit();  // every thread: one more group (Q), after its tiles
+  // the ring's remaining slots, now including the newest tile
+  for (int j = issued; j < DSTAGES; ++j) {
+    const int kt = first + 4 * j;
+    if (kt >= my_end) break;
+    load_tile(kt, j);
+    cp_async_commit();
+    ++issued;
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // Q is complete for every warp (and this warp's first tiles with it)
 
   float o[D / 8][4];
 #pragma unroll
@@ -425,43 +506,43 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const bool row_ok[2] = {g4 < G, g4 + 8 < G};
-
-  const int first = my_begin + warp;
-  if (first < my_end) load_tile(first);
-  cp_async_wait<0>();
-  __syncthreads();  // Q is complete for every warp
   const int m8 = lane >> 3, l8 = lane & 7;
-  for (int kt = first; kt < my_end; kt += 4) {
-    if (kt != first) {
-      __syncwarp();
-      load_tile(kt);
-      cp_async_wait<0>();
+  // the A fragments of Q do not change over the tiles
+  uint32_t qa[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(qa[kk], q_s + sw((m8 & 1) * 8 + l8, kk * 2 + (m8 >> 1)));
+
+  int n = 0;  // tiles of this warp done so far
+  for (int kt = first; kt < my_end; kt += 4, ++n) {
+    const int stage = n % DSTAGES;
+    if (n >= DSTAGES) {
+      // tiles beyond the first ring: the groups complete in order, at most DSTAGES - 1 may stay open
+      const int ahead = issued - n - 1;  // groups requested after this tile's
+      if (ahead >= 2) cp_async_wait<2>();
+      else if (ahead == 1) cp_async_wait<1>();
+      else cp_async_wait<0>();
       __syncwarp();
     }
-    float s[DBN / 8][4];
+    const uint32_t k_s = ring + stage * 2 * DEC_TILE_BYTES, v_s = k_s + DEC_TILE_BYTES;
+    float s[DK / 8][4];
 #pragma unroll
-    for (int i = 0; i < DBN / 8; ++i)
+    for (int i = 0; i < DK / 8; ++i)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(a, q_s + sw((m8 & 1) * 8 + l8, kk * 2 + (m8 >> 1)));
-#pragma unroll
-      for (int nn = 0; nn < DBN / 16; ++nn) {
-        uint32_t b[4];
-        ldmatrix_x4(b, k_s + sw(nn * 16 + (m8 >> 1) * 8 + l8, kk * 2 + (m8 & 1)));
-        mma_bf16(s[2 * nn], a, b[0], b[1]);
-        mma_bf16(s[2 * nn + 1], a, b[2], b[3]);
-      }
+      uint32_t b[4];
+      ldmatrix_x4(b, k_s + sw((m8 >> 1) * 8 + l8, kk * 2 + (m8 & 1)));
+      mma_bf16(s[0], qa[kk], b[0], b[1]);
+      mma_bf16(s[1], qa[kk], b[2], b[3]);
     }
     float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < DBN / 8; ++nt)
+    for (int nt = 0; nt < DK / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const int key = kt * DBN + nt * 8 + 2 * c4 + (e & 1);
+        const int key = kt * DK + nt * 8 + 2 * c4 + (e & 1);
         const bool vis = row_ok[r] && key <= pos && key >= lo;
         const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
         s[nt][e] = v;
@@ -479,7 +560,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       l_run[r] *= alpha[r];
     }
 #pragma unroll
-    for (int nt = 0; nt < DBN / 8; ++nt)
+    for (int nt = 0; nt < DK / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float pv = exp2f(s[nt][e] - m_safe[e >> 1]);
@@ -493,20 +574,27 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       o[i][2] *= alpha[1];
       o[i][3] *= alpha[1];
     }
-#pragma unroll
-    for (int j = 0; j < DBN / 16; ++j) {
+    {
       uint32_t a[4];
-      a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
-      a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
-      a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
-      a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+      a[0] = pack_bf16(s[0][0], s[0][1]);
+      a[1] = pack_bf16(s[0][2], s[0][3]);
+      a[2] = pack_bf16(s[1][0], s[1][1]);
+      a[3] = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
       for (int dd = 0; dd < D / 16; ++dd) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, v_s + sw(j * 16 + (m8 & 1) * 8 + l8, dd * 2 + (m8 >> 1)));
+        ldmatrix_x4_trans(b, v_s + sw((m8 & 1) * 8 + l8, dd * 2 + (m8 >> 1)));
         mma_bf16(o[2 * dd], a, b[0], b[1]);
         mma_bf16(o[2 * dd + 1], a, b[2], b[3]);
       }
+    }
+    // the slot is free: the tile DSTAGES further on goes into it
+    const int next = kt + 4 * DSTAGES;
+    if (next < my_end) {
+      __syncwarp();
+      load_tile(next, stage);
+      cp_async_commit();
+      ++issued;
     }
   }
 #pragma unroll
@@ -514,51 +602,105 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
-  // the warp's partial over its own tiles, in its own (now free) tile memory: [16][D] and [16][2]
+  // ---- level 1: the warp's partial into its own (now free) ring memory, merged over the CTA's warps
   __syncwarp();
-  float* part_o = reinterpret_cast<float*>(smem + DEC_Q_BYTES + warp * DEC_WARP_BYTES);
-  float* part_ml = part_o + 16 * D;
+  {
+    float* part_o = reinterpret_cast<float*>(warp_mem);
+    float* part_ml = part_o + 16 * D;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = g4 + 8 * r;
+    for (int r = 0; r < 2; ++r) {
+      const int row = g4 + 8 * r;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<float2*>(part_o + row * D + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
-    if (c4 == 0) {
-      part_ml[row * 2] = m_run[r];
-      part_ml[row * 2 + 1] = l_run[r];
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(part_o + row * D + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+      if (c4 == 0) {
+        part_ml[row * 2] = m_run[r];
+        part_ml[row * 2 + 1] = l_run[r];
+      }
     }
   }
-  cg::cluster_group cluster = cg::this_cluster();
-  cluster.sync();
-  float* base0 = reinterpret_cast<float*>(smem + DEC_Q_BYTES);
-  const int np = nsplit * 4;  // partials of a row: one per warp of the cluster (at most 32)
-  // lane i looks at partial i (CTA i / 4, warp i % 4): one round of remote reads for all (m, l)
-  const float* mine = nullptr;
-  if (lane < np) mine = cluster.map_shared_rank(base0, lane >> 2) + (lane & 3) * (DEC_WARP_BYTES / 4);
-  for (int row = split * 4 + warp; row < G; row += nsplit * 4) {
-    float m_i = -INFINITY, l_i = 0.f;
-    if (mine) {
-      m_i = mine[16 * D + row * 2];
-      l_i = mine[16 * D + row * 2 + 1];
+  __syncthreads();
+  const bool last_level = nsplit == 1;
+  for (int row = warp; row < G; row += 4) {
+    float m_w[4], l_w[4];
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* ml = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + 16 * D;
+      m_w[w] = ml[row * 2];
+      l_w[w] = ml[row * 2 + 1];
+      M = fmaxf(M, m_w[w]);
     }
-    const float M = warp_max(m_i);
-    const float w_i = (m_i == -INFINITY) ? 0.f : exp2f(m_i - M);
-    const float L = warp_sum(w_i * l_i);
+    float L = 0.f;
     float acc[(D + 31) / 32];
 #pragma unroll
     for (int j = 0; j < (D + 31) / 32; ++j) acc[j] = 0.f;
-    // the weights are known: the reads of the partial outputs do not depend on one another
-#pragma unroll 4
-    for (int i = 0; i < np; ++i) {
-      const float wgt = __shfl_sync(0xffffffffu, w_i, i);
-      if (wgt == 0.f) continue;  // a warp that had no tile
-      const float* po = cluster.map_shared_rank(base0, i >> 2) + (i & 3) * (DEC_WARP_BYTES / 4) + row * D;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = m_w[w] == -INFINITY ? 0.f : exp2f(m_w[w] - M);
+      L += wgt * l_w[w];
+      const float* po = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + row * D;
 #pragma unroll
       for (int j = 0; j < (D + 31) / 32; ++j) {
         const int d = lane + 32 * j;
         if (d < D) acc[j] += wgt * po[d];
       }
+    }
+    if (last_level) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) dst[d] = __float2bfloat16(acc[j] * inv);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) cta_part[row * D + d] = acc[j];
+      }
+      if (lane == 0) {
+        cta_part[16 * D + row * 2] = M;
+        cta_part[16 * D + row * 2 + 1] = L;
+      }
+    }
+  }
+  if (last_level) return;
+  // ---- level 2: the CTAs of the cluster; the rows are dealt to its warps
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  for (int row = split * 4 + warp; row < G; row += nsplit * 4) {
+    float m_c[8], l_c[8];
+    const float* remote[8];
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      remote[c] = cluster.map_shared_rank(cta_part, c < nsplit ? c : 0);
+      m_c[c] = c < nsplit ? remote[c][16 * D + row * 2] : -INFINITY;
+      l_c[c] = c < nsplit ? remote[c][16 * D + row * 2 + 1] : 0.f;
+    }
+    // all partial outputs of the row are requested before any is used
+    float po[8][(D + 31) / 32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        po[c][j] = (c < nsplit && d < D) ? remote[c][row * D + d] : 0.f;
+      }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) M = fmaxf(M, m_c[c]);
+    float L = 0.f;
+    float acc[(D + 31) / 32];
+#pragma unroll
+    for (int j = 0; j < (D + 31) / 32; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float wgt = m_c[c] == -INFINITY ? 0.f : exp2f(m_c[c] - M);
+      L += wgt * l_c[c];
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) acc[j] += wgt * po[c][j];
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
     bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;

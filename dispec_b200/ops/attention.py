@@ -62,7 +62,7 @@ _MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
 MAX_SPLITS = 32
 USE_CLUSTER_COMBINE = True
 USE_DECODE_KERNEL = True  # warp-parallel kernel for single tokens whose group fits 16 rows
-DECODE_KERNEL_MAX_SPLITS = 4  # measured: it wins for larger batches (few splits), the tile kernel for small ones
+DECODE_KERNEL_MAX_SPLITS = 8  # every split count the cluster merge allows
 TARGET_CTAS = 148 * 2
 _partials: dict = {}
 _err_addr: dict = {}
