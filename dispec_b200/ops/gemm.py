@@ -40,7 +40,7 @@ def _skinny(x, w, bias, residual, out, target_ctas=None, prologue=PRO_NONE, gain
             epilogue=EPI_PLAIN):
     M = x.shape[0]
     N, K = w.shape
-    L.check(L.core().dsp_gemm_skinny(
+    L.check(L.skinny().dsp_gemm_skinny(
         L.ptr(x), L.i64(x.stride(0)), L.ptr(w), L.ptr(bias), L.ptr(residual),
         L.i64(residual.stride(0) if residual is not None else 0), L.ptr(out), L.i64(out.stride(0)),
         M, N, K, L.dtype_code(out.dtype), SKINNY_TARGET_CTAS if target_ctas is None else target_ctas,

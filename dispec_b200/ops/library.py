@@ -36,10 +36,21 @@ def core() -> ctypes.CDLL:
         with _lock:
             if _core is None:
                 path = build.core_library()
-                lib = ctypes.CDLL(path)
+                # global: libraries loaded later resolve the runtime's symbols against this one
+                lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
                 lib.dsp_last_error.restype = ctypes.c_char_p
                 _core = lib
     return _core
+
+
+def skinny() -> ctypes.CDLL:
+    """The mma.sync product for few rows, in a library of its own (built at first use)."""
+    if "gemm_skinny" not in _special:
+        core()
+        with _lock:
+            if "gemm_skinny" not in _special:
+                _special["gemm_skinny"] = ctypes.CDLL(build.skinny_library())
+    return _special["gemm_skinny"]
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
