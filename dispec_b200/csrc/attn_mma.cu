@@ -58,6 +58,10 @@ struct Params {
   int cluster_combine;  // the splits of a tile are one cluster and merge on chip
   float scale_log2;
   int* err;
+  // single-token kernel only: q points into the fused q/k/v rows before rotation; the kernel rotates q
+  // itself and, if write_kv, rotates the token's key, stores key and value into the cache and uses them
+  const float* inv_freq;
+  int rotary_dim, fused_rope, write_kv;
 };
 
 __device__ __forceinline__ uint32_t sw(int row, int chunk) {
@@ -371,7 +375,24 @@ constexpr int DEC_TILE_BYTES = DK * ROW_BYTES;
 constexpr int DEC_PART_BYTES = (16 * D + 32) * 4;  // a partial: [16][D] outputs and [16][2] (m, l)
 constexpr int DEC_RING_BYTES = DSTAGES * 2 * DEC_TILE_BYTES;
 constexpr int DEC_WARP_BYTES = DEC_RING_BYTES > DEC_PART_BYTES ? DEC_RING_BYTES : DEC_PART_BYTES;
-constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES + DEC_MAXP * 4;
+constexpr int DEC_CS_BYTES = D * 4;  // cos and sin of the token's angles (fused rotation)
+constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES + DEC_MAXP * 4 + DEC_CS_BYTES;
+
+__device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// eight elements of the low half with the eight of the high half: lo' = lo cos - hi sin, hi' = hi cos + lo sin,
+// in 32-bit, rounded once (as the separate rotation kernel does)
+__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* c, const float* sn) {
+  bf16* a = reinterpret_cast<bf16*>(&lo);
+  bf16* b = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float av = __bfloat162float(a[k]), bv = __bfloat162float(b[k]);
+    a[k] = __float2bfloat16(av * c[k] - bv * sn[k]);
+    b[k] = __float2bfloat16(bv * c[k] + av * sn[k]);
+  }
+}
 
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -398,6 +419,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(warp_mem);
   float* cta_part = reinterpret_cast<float*>(smem + DEC_Q_BYTES + 4 * DEC_WARP_BYTES);
   int* pages_s = reinterpret_cast<int*>(smem + DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES);
+  float* cs = reinterpret_cast<float*>(smem + DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES + DEC_MAXP * 4);
+  // with the fused rotation the newest key and value are not in the cache yet: this kernel puts them there
+  const bool own_new = p.fused_rope && p.write_kv;
+  const int last_cached = own_new ? pos - 1 : pos;
 
   // ---- before the wait: page ids of this CTA's keys, then the first tiles of every warp
   const int first_page = my_begin < my_end ? (my_begin * DK) / p.page_size : 0;
@@ -426,7 +451,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
 #pragma unroll
         for (int r = r0; r < DK; r += ROWS_PER_PASS) {
           const int b = b0 + r;
-          const bool valid = page_ok && b <= pos && b >= lo;
+          const bool valid = page_ok && b <= last_cached && b >= lo;
           const size_t off = base + (size_t)r * D + chunk * 8;
           cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
           cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
@@ -436,7 +461,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
         for (int i = lane; i < DK * CHUNKS; i += 32) {
           const int r = i / CHUNKS, chunk = i % CHUNKS;
           const int b = b0 + r;
-          const bool valid = page_ok && b <= pos && b >= lo;
+          const bool valid = page_ok && b <= last_cached && b >= lo;
           const size_t off = base + (size_t)r * D + chunk * 8;
           cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
           cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
@@ -448,7 +473,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     for (int i = lane; i < DK * CHUNKS; i += 32) {
       const int r = i / CHUNKS, chunk = i % CHUNKS;
       const int b = kt * DK + r;
-      bool valid = b <= pos && b >= lo;
+      bool valid = b <= last_cached && b >= lo;
       size_t off = 0;
       if (valid) {
         const int lp = p.page_shift >= 0 ? (b >> p.page_shift) : (b / p.page_size);
@@ -480,12 +505,47 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
 
   pdl_wait();
-  // Q: the G heads of this KV head, one row each
-  for (int i = tid; i < 16 * CHUNKS; i += THREADS) {
-    const int r = i / CHUNKS, chunk = i % CHUNKS;
-    const bool valid = r < G;
-    const bf16* src = valid ? p.q + (size_t)qs * p.q_stride + (size_t)(kvh * G + r) * D + chunk * 8 : p.q;
-    cp_async16(q_s + sw(r, chunk), src, valid);
+  const int half = p.rotary_dim / 2;
+  if (p.fused_rope) {
+    // cos and sin of this position's angles, once for q and for the new key
+    for (int i = tid; i < half; i += THREADS) {
+      float sn, c;
+      sincosf((float)pos * p.inv_freq[i], &sn, &c);
+      cs[i] = c;
+      cs[half + i] = sn;
+    }
+    __syncthreads();
+    // Q: the G heads of this KV head, rotated on the way into shared memory (16-byte pieces; piece j
+    // of the low half rotates with piece j of the high half)
+    const int hv = half / 8, tail = (D - p.rotary_dim) / 8;
+    const bf16* q0 = p.q + (size_t)qs * p.q_stride + (size_t)kvh * G * D;
+    for (int i = tid; i < 16 * (hv + tail); i += THREADS) {
+      const int r = i / (hv + tail), j = i % (hv + tail);
+      const bool valid = r < G;
+      if (j < hv) {
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (valid) {
+          lo = *reinterpret_cast<const uint4*>(q0 + (size_t)r * D + j * 8);
+          hi = *reinterpret_cast<const uint4*>(q0 + (size_t)r * D + half + j * 8);
+          rotate8(lo, hi, cs + j * 8, cs + half + j * 8);
+        }
+        st_shared16(q_s + sw(r, j), lo);
+        st_shared16(q_s + sw(r, hv + j), hi);
+      } else {
+        const int chunk = 2 * hv + (j - hv);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (valid) v = *reinterpret_cast<const uint4*>(q0 + (size_t)r * D + chunk * 8);
+        st_shared16(q_s + sw(r, chunk), v);
+      }
+    }
+  } else {
+    // Q: the G heads of this KV head, one row each
+    for (int i = tid; i < 16 * CHUNKS; i += THREADS) {
+      const int r = i / CHUNKS, chunk = i % CHUNKS;
+      const bool valid = r < G;
+      const bf16* src = valid ? p.q + (size_t)qs * p.q_stride + (size_t)(kvh * G + r) * D + chunk * 8 : p.q;
+      cp_async16(q_s + sw(r, chunk), src, valid);
+    }
   }
   cp_async_commit();  // every thread: one more group (Q), after its tiles
   // the ring's remaining slots, now including the newest tile
@@ -524,6 +584,44 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       __syncwarp();
     }
     const uint32_t k_s = ring + stage * 2 * DEC_TILE_BYTES, v_s = k_s + DEC_TILE_BYTES;
+    if (own_new && kt == newest) {
+      // the token's own key (rotated) and value: from the fused q/k/v row into this tile and into the cache
+      const int r = pos - kt * DK;
+      const int hv = half / 8, tail = (D - p.rotary_dim) / 8;
+      const bf16* k0 = p.q + (size_t)qs * p.q_stride + (size_t)(p.H + kvh) * D;
+      const bf16* v0 = p.q + (size_t)qs * p.q_stride + (size_t)(p.H + p.KVH + kvh) * D;
+      const int lp = pos / p.page_size;
+      const int page = cached ? pages_s[lp - first_page] : table[lp];
+      const bool page_ok = page >= 0 && page < p.num_pages;
+      if (!page_ok && lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+      const size_t dst = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + pos % p.page_size) * D;
+      bf16* k_out = const_cast<bf16*>(p.k_pool) + dst;
+      bf16* v_out = const_cast<bf16*>(p.v_pool) + dst;
+      for (int i = lane; i < hv + tail + CHUNKS; i += 32) {
+        if (i < hv) {
+          uint4 klo = *reinterpret_cast<const uint4*>(k0 + i * 8);
+          uint4 khi = *reinterpret_cast<const uint4*>(k0 + half + i * 8);
+          rotate8(klo, khi, cs + i * 8, cs + half + i * 8);
+          st_shared16(k_s + sw(r, i), klo);
+          st_shared16(k_s + sw(r, hv + i), khi);
+          if (page_ok) {
+            *reinterpret_cast<uint4*>(k_out + i * 8) = klo;
+            *reinterpret_cast<uint4*>(k_out + half + i * 8) = khi;
+          }
+        } else if (i < hv + tail) {
+          const int chunk = 2 * hv + (i - hv);
+          const uint4 kv = *reinterpret_cast<const uint4*>(k0 + chunk * 8);
+          st_shared16(k_s + sw(r, chunk), kv);
+          if (page_ok) *reinterpret_cast<uint4*>(k_out + chunk * 8) = kv;
+        } else {
+          const int chunk = i - hv - tail;
+          const uint4 vv = *reinterpret_cast<const uint4*>(v0 + chunk * 8);
+          st_shared16(v_s + sw(r, chunk), vv);
+          if (page_ok) *reinterpret_cast<uint4*>(v_out + chunk * 8) = vv;
+        }
+      }
+      __syncwarp();
+    }
     float s[DK / 8][4];
 #pragma unroll
     for (int i = 0; i < DK / 8; ++i)
@@ -721,7 +819,8 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     int pt_stride, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0,
     int tile_offset, int num_tiles, void* out, long out_stride, float* part_o, float* part_ml, int H,
     int KVH, int tokens_per_tile, int page_size, int num_pages, int window, int num_splits,
-    int cluster_combine, int decode_only, float scale, int* err, cudaStream_t stream) {
+    int cluster_combine, int decode_only, float scale, const float* inv_freq, int rotary_dim, int fused_rope,
+    int write_kv, int* err, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (KVH <= 0 || H % KVH != 0 || (H / KVH) * tokens_per_tile > BM || tokens_per_tile < 1) return 2;
   if (num_splits < 1 || num_splits > 65535 || KVH > 65535) return 2;
@@ -757,6 +856,15 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   p.cluster_combine = cluster_combine;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = err;
+  p.inv_freq = inv_freq;
+  p.rotary_dim = rotary_dim;
+  p.fused_rope = fused_rope;
+  p.write_kv = write_kv;
+  if (fused_rope) {
+    // only the single-token kernel rotates, and in 16-byte pieces
+    if (!(decode_only && p.G <= 16 && num_splits <= 8 && DEC_SMEM <= 227 * 1024)) return 2;
+    if (inv_freq == nullptr || rotary_dim <= 0 || rotary_dim > D || rotary_dim % 16 != 0) return 2;
+  }
   const int smem = 5 * TILE_BYTES;
   static bool configured = false;  // once; not repeated under graph capture
   if (!configured) {

@@ -62,6 +62,7 @@ _MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
 MAX_SPLITS = 32
 USE_CLUSTER_COMBINE = True
 USE_DECODE_KERNEL = True  # warp-parallel kernel for single tokens whose group fits 16 rows
+FUSE_DECODE_ROPE = True  # that kernel rotates q and the token's key itself and writes key and value to the cache
 DECODE_KERNEL_MAX_SPLITS = 8  # every split count the cluster merge allows
 TARGET_CTAS = 148 * 2
 _partials: dict = {}
@@ -113,9 +114,21 @@ def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int) -> int
 CLUSTER_MAX_SPLITS = 8  # splits that merge on chip (one thread-block cluster per tile)
 
 
+def decode_rope_fusable(ctx, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+                        dtype: torch.dtype) -> bool:
+    """Whether the single tokens of this step go through the kernel that rotates q and k itself
+    (then the separate rotation kernel must skip them)."""
+    group = num_heads // num_kv_heads
+    return (FUSE_DECODE_ROPE and USE_DECODE_KERNEL and USE_CLUSTER_COMBINE and ctx.num_decode_seqs > 0
+            and tensor_core_supported(head_dim, group, dtype) and group <= 16
+            and tokens_per_tile(group) in ctx.attention_tiles
+            and 0 < rotary_dim <= head_dim and rotary_dim % 16 == 0
+            and DECODE_KERNEL_MAX_SPLITS >= CLUSTER_MAX_SPLITS)
+
+
 def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
                 tile_offset, num_tiles, out, part_o, part_ml, H, KVH, D, tpt, window, splits, scale,
-                cluster_combine=False, decode_only=False):
+                cluster_combine=False, decode_only=False, fused_rope=None):
     num_pages, _, page_size, _ = k_pool.shape
     lib = L.attention_library(D)
     fn = getattr(lib, f"dsp_attn_mma_d{D}")
@@ -123,7 +136,8 @@ def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_
             page_table.stride(0), L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0),
             tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml),
             H, KVH, tpt, page_size, num_pages, window, splits, int(cluster_combine), int(decode_only),
-            L.f32(scale),
+            L.f32(scale), L.ptr(fused_rope[0]) if fused_rope else None, fused_rope[1] if fused_rope else 0,
+            1 if fused_rope else 0, int(fused_rope[2]) if fused_rope else 0,
             ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
     L.LaunchCounter.n += 1
     if rc != 0:
@@ -151,11 +165,13 @@ _TCGEN05_ERRORS = {1: "launch failed", 2: "unsupported head/group counts or page
 
 def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                           tile_tok0, num_tiles, num_decode_tiles, out, H, KVH, D, window, scale,
-                          splits: int, prefill_tiles=None) -> torch.Tensor:
+                          splits: int, prefill_tiles=None, fused_rope=None) -> torch.Tensor:
     """Tensor-core attention over a tile list whose first ``num_decode_tiles`` tiles are single
     tokens (run with ``splits`` key splits and merged), the rest portions of prompts.  With
     ``prefill_tiles`` = (tile_seq, tile_tok0, num_tiles) of the 128-row tiling (single tokens
-    first as well) the portions of prompts run on the tcgen05 kernel."""
+    first as well) the portions of prompts run on the tcgen05 kernel.  ``fused_rope`` = (inv_freq,
+    rotary_dim, write_kv): ``q`` are the fused q/k/v rows and the single tokens' rows are not
+    rotated yet; their kernel rotates them and stores key and value (see ``decode_rope_fusable``)."""
     assert q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
     tpt = tokens_per_tile(H // KVH)
@@ -166,7 +182,10 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
             _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                         tile_tok0, 0, num_decode_tiles, out, None, None, H, KVH, D, tpt, window,
                         splits, scale, cluster_combine=splits > 1,
-                        decode_only=USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS)
+                        decode_only=USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS,
+                        fused_rope=fused_rope)
+        elif fused_rope:
+            raise L.KernelError("single tokens were left unrotated for a kernel that is not in use")
         elif splits > 1:
             rows = num_decode_tiles * H  # decode tokens are the first rows of the flat batch
             part_o, part_ml = _partial_buffers(q.device, rows, splits, D)
@@ -228,7 +247,7 @@ def paged_attention_tensor_core(q, q_stride, k_pool, v_pool, page_table, positio
 
 
 def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tensor, num_heads: int,
-                    num_kv_heads: int, head_dim: int, window: int, scale: float) -> torch.Tensor:
+                    num_kv_heads: int, head_dim: int, window: int, scale: float, fused_rope=None) -> torch.Tensor:
     """Attention of the step described by ``ctx`` over the layer cache ``cache``: the
     tensor-core kernel for bfloat16 where it is built for the sizes, the 32-bit kernel
     otherwise (and always on the float32 path)."""
@@ -245,7 +264,9 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
         return paged_attention_tiles(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                      ctx.q_start, ctx.ctx_len, tile_seq, tile_tok0, num_tiles,
                                      ctx.num_decode_seqs, out, num_heads, num_kv_heads, head_dim,
-                                     window, scale, splits, prefill_tiles)
+                                     window, scale, splits, prefill_tiles, fused_rope)
+    if fused_rope:
+        raise L.KernelError("single tokens were left unrotated for a kernel that is not in use")
     return paged_attention_generic(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads,
                                    head_dim, window, scale)

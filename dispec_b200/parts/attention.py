@@ -83,11 +83,19 @@ class GQAAttention(Mixer):
         else:
             qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         pe = self.position_encoding
-        ops.rope_kv_store(qkv, ctx.positions, ctx.seq_of_token, cache.page_table,
-                          cache.key_pool if cache.write else None,
-                          cache.value_pool if cache.write else None,
-                          pe.inv_freq, H, KVH, D, pe.rotary_dim, write_kv=cache.write)
+        # single tokens come first in the batch: when their attention kernel rotates q and k itself and
+        # stores the new key and value, the rotation kernel runs on the portions of prompts only
+        n_dec = ctx.num_decode_seqs
+        fused = None
+        if attn_ops.decode_rope_fusable(ctx, H, KVH, D, pe.rotary_dim, qkv.dtype):
+            fused = (pe.inv_freq, pe.rotary_dim, cache.write)
+        first = n_dec if fused else 0
+        if qkv.shape[0] > first:
+            ops.rope_kv_store(qkv[first:], ctx.positions[first:], ctx.seq_of_token[first:], cache.page_table,
+                              cache.key_pool if cache.write else None,
+                              cache.value_pool if cache.write else None,
+                              pe.inv_freq, H, KVH, D, pe.rotary_dim, write_kv=cache.write)
         out = torch.empty((x.shape[0], H * D), dtype=x.dtype, device=x.device)
         attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
-                                 self.scale)
+                                 self.scale, fused_rope=fused)
         return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual)

@@ -594,3 +594,58 @@ def test_attention_tcgen05_window_edge(offset, q_len):
     out, ref = run_attention("tensor_core", torch.bfloat16, 6, 2, 64, 8, ctx, q_len, window, plant=plant, seed=9)
     torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
 
+
+
+@pytest.mark.parametrize("H,KVH,D,rot,page,window", [(12, 2, 128, 128, 16, 0), (6, 3, 64, 32, 8, 40), (4, 4, 16, 16, 32, 0),
+                                                     (14, 2, 48, 48, 16, 0)])
+def test_decode_attention_that_rotates_and_stores_itself(H, KVH, D, rot, page, window):
+    """Single tokens: the kernel that rotates q and the token's key and writes key and value to the
+    cache against the rotation kernel followed by the plain attention kernel: the same outputs and
+    the same cache, for tokens at a page's first and last offset and in the middle."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import attention as A
+    ctx_lens = [page * 3, page * 2 + 1, 77, 1, 300]
+    B = len(ctx_lens)
+    g = torch.Generator().manual_seed(5)
+    pages_per = [(c + page - 1) // page for c in ctx_lens]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    for s in range(B):
+        for j in range(pages_per[s]):
+            table[s, j] = perm.pop()
+    pool = torch.randn(2, num_pages, KVH, page, D, generator=g).bfloat16()
+    for s, c in enumerate(ctx_lens):  # the slot of the newest position is not in the cache yet
+        pool[:, table[s, (c - 1) // page], :, (c - 1) % page] = float("nan")
+    qkv = torch.randn(B, (H + 2 * KVH) * D, generator=g).bfloat16().to(dev())
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev())
+    positions = torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32, device=dev())
+    seq = torch.arange(B, dtype=torch.int32, device=dev())
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev())
+    q_start, ctx_len = i32(list(range(B + 1))), i32(ctx_lens)
+    ts, t0 = i32(list(range(B))), i32([0] * B)
+    table_d = table.to(dev())
+    results = []
+    for fused in (False, True):
+        kp, vp = pool[0].clone().to(dev()), pool[1].clone().to(dev())
+        rows = qkv.clone()
+        out = torch.empty((B, H * D), dtype=torch.bfloat16, device=dev())
+        if not fused:
+            ops.rope_kv_store(rows, positions, seq, table_d, kp, vp, inv_freq, H, KVH, D, rot)
+        for splits in (3,):
+            A.paged_attention_tiles(rows, rows.stride(0), kp, vp, table_d, q_start, ctx_len, ts, t0, B, B, out, H,
+                                    KVH, D, window, D ** -0.5, splits,
+                                    fused_rope=(inv_freq, rot, True) if fused else None)
+        torch.cuda.synchronize()
+        results.append((out.float().cpu(), kp.float().cpu(), vp.float().cpu()))
+    (o0, k0, v0), (o1, k1, v1) = results
+    assert torch.isfinite(o0).all() and torch.isfinite(o1).all()
+    torch.testing.assert_close(o1, o0, atol=2e-2, rtol=2e-2)
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for s, c in enumerate(ctx_lens):
+        written[table[s, (c - 1) // page], (c - 1) % page] = True
+    for a, b in ((k0, k1), (v0, v1)):
+        a, b = a.permute(0, 2, 1, 3), b.permute(0, 2, 1, 3)  # [page, offset, kvh, d]
+        torch.testing.assert_close(b[written], a[written], atol=1e-2, rtol=1e-2)
+        assert torch.equal(b[~written], a[~written])  # nothing else was touched
+    ops.raise_on_device_error("decode attention with rotation")
