@@ -420,3 +420,194 @@ def test_schedule_runs_a_layer_twice_and_shares_a_cache(tmp_path):
         out.append(runner.step([SeqEntry("s", ids[pos:pos + n], pos, list(range(n)))]))
         pos += n
     assert (torch.cat(out).cpu() - ref).abs().max().item() < 1e-4
+
+
+# ------------------------------------------------ a feed-forward with routing, another position encoding
+
+def register_routed_toy():
+    """Two more toy parts, registered from here through the public calls: a feed-forward that
+    routes every token to one of its experts (32-bit router), and a rotary encoding with
+    slowed-down frequencies over half of the head.  A toy architecture uses them in its odd
+    layers and the package's own dense feed-forward and rotary encoding in its even ones."""
+    from dispec_b200 import register_architecture, register_part
+    from dispec_b200.config.model_config import ModelConfig
+    from dispec_b200.models.spec import LayerCall, ModelSpec
+    from dispec_b200.parts.base import FeedForward, PartSpec, PositionEncoding, TensorSpec
+    from dispec_b200.registry import architectures
+
+    if "ToyRoutedForCausalLM" in architectures():
+        return
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """p = softmax(h Wr^T) in 32-bit; e = argmax p; y = p_e * down_e(silu(gate_e h) * up_e h)."""
+
+        def __init__(self, hidden_size, intermediate_size, num_experts):
+            self.h, self.i, self.e = hidden_size, intermediate_size, num_experts
+
+        def tensor_specs(self):
+            return {"router.weight": TensorSpec((self.e, self.h), dtype="float32"),
+                    "gate.weight": TensorSpec((self.e, self.i, self.h)),
+                    "up.weight": TensorSpec((self.e, self.i, self.h)),
+                    "down.weight": TensorSpec((self.e, self.h, self.i))}
+
+        def load(self, tensors):
+            self.router, self.gate = tensors["router.weight"], tensors["gate.weight"]
+            self.up, self.down = tensors["up.weight"], tensors["down.weight"]
+            assert self.router.dtype == torch.float32
+
+        def forward(self, ctx, x):
+            from dispec_b200 import ops
+            probs = torch.softmax(x.float() @ self.router.T, dim=-1)
+            top_p, top_e = probs.max(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.e):  # the package's own products, expert by expert
+                rows = (top_e == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                h = x.index_select(0, rows)
+                act = ops.swiglu(ops.linear(h, torch.cat([self.gate[e], self.up[e]]).contiguous()))
+                y = ops.linear(act, self.down[e].contiguous()).float() * top_p[rows, None]
+                out.index_copy_(0, rows, y.to(x.dtype))
+            return out
+
+    @register_part("position_encoding", "toy_slow_half_rotary")
+    class SlowHalfRotary(PositionEncoding):
+        """Rotates the first half of each head with frequencies divided by ``factor``."""
+
+        def __init__(self, head_dim, theta, factor):
+            self.rotary_dim = head_dim // 2
+            self.theta, self.factor = float(theta), float(factor)
+            self.inv_freq = None
+
+        def prepare(self, device):
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+            self.inv_freq = (1.0 / (self.theta ** exponent) / self.factor).to(torch.float32).to(device)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyRoutedForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+        heads: int = 0
+        kv_heads: int = 0
+        head_dim: int = 0
+        intermediate_size: int = 0
+        num_experts: int = 0
+        num_layers: int = 0
+        eps: float = 0.0
+        theta: float = 0.0
+        factor: float = 1.0
+
+        KEYS: ClassVar[tuple] = ("vocab_size", "hidden_size", "heads", "kv_heads", "head_dim", "intermediate_size",
+                                 "num_experts", "num_layers", "eps", "theta", "factor")
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: d[k] for k in cls.KEYS})
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in self.KEYS})
+
+    def build(cfg):
+        h = cfg.hidden_size
+        layers = []
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            odd = i % 2 == 1
+            norm = lambda n: PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": p + n})
+            pe = (PartSpec("position_encoding", "toy_slow_half_rotary",
+                           {"head_dim": cfg.head_dim, "theta": cfg.theta, "factor": cfg.factor}) if odd else
+                  PartSpec("position_encoding", "rotary", {"head_dim": cfg.head_dim, "theta": cfg.theta}))
+            mixer = PartSpec("mixer", "gqa_attention",
+                             {"hidden_size": h, "num_heads": cfg.heads, "num_kv_heads": cfg.kv_heads,
+                              "head_dim": cfg.head_dim, "qkv_bias": False, "position_encoding": pe, "window": 0},
+                             {f"{n}_proj.weight": f"{p}attn.{n}" for n in "qkvo"})
+            if odd:
+                ffn = PartSpec("feed_forward", "toy_top1_experts",
+                               {"hidden_size": h, "intermediate_size": cfg.intermediate_size, "num_experts": cfg.num_experts},
+                               {f"{n}.weight": f"{p}moe.{n}" for n in ("router", "gate", "up", "down")})
+            else:
+                ffn = PartSpec("feed_forward", "swiglu", {"hidden_size": h, "intermediate_size": cfg.intermediate_size},
+                               {f"{n}_proj.weight": f"{p}ffn.{n}" for n in ("gate", "up", "down")})
+            layers.append(PartSpec("block", "pre_norm", {"mixer_norm": norm("n1"), "mixer": mixer,
+                                                         "ffn_norm": norm("n2"), "feed_forward": ffn}))
+        return ModelSpec("ToyRoutedForCausalLM",
+                         PartSpec("embedding", "token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                         layers,
+                         PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": "final"}),
+                         PartSpec("head", "linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "head"}),
+                         schedule=[LayerCall(i, i, True) for i in range(cfg.num_layers)],
+                         vocab_size=cfg.vocab_size, max_position=4096)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build)
+
+
+def plain_routed(weights, cfg, ids):
+    T = len(ids)
+    H, KVH, D = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    x = weights["emb"][torch.as_tensor(ids)]
+    pos = torch.arange(T, dtype=torch.float32)
+    for i in range(cfg["num_layers"]):
+        p = f"layers.{i}."
+        odd = i % 2 == 1
+        h = plain.rms_norm(x, weights[p + "n1"], cfg["eps"])
+        q = (h @ weights[p + "attn.q"].T).view(T, H, D)
+        k = (h @ weights[p + "attn.k"].T).view(T, KVH, D)
+        v = (h @ weights[p + "attn.v"].T).view(T, KVH, D)
+        rot = D // 2 if odd else D
+        inv = 1.0 / (cfg["theta"] ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        if odd:
+            inv = inv / cfg["factor"]
+        ang = pos[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+        def rotate(t):
+            lo, hi, rest = t[..., :rot // 2], t[..., rot // 2:rot], t[..., rot:]
+            return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin, rest], dim=-1)
+
+        o = plain.causal_attention(rotate(q), rotate(k), v)
+        x = x + o.reshape(T, -1) @ weights[p + "attn.o"].T
+        h = plain.rms_norm(x, weights[p + "n2"], cfg["eps"])
+        if odd:
+            probs = torch.softmax(h @ weights[p + "moe.router"].T, dim=-1)
+            top_p, top_e = probs.max(dim=-1)
+            y = torch.stack([top_p[t] * plain.swiglu_mlp(h[t:t + 1], weights[p + "moe.gate"][top_e[t]],
+                                                         weights[p + "moe.up"][top_e[t]],
+                                                         weights[p + "moe.down"][top_e[t]])[0] for t in range(T)])
+            x = x + y
+        else:
+            x = x + plain.swiglu_mlp(h, weights[p + "ffn.gate"], weights[p + "ffn.up"], weights[p + "ffn.down"])
+    return plain.rms_norm(x, weights["final"], cfg["eps"]) @ weights["head"].T
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding_in_alternate_layers(tmp_path):
+    """Registered from the test, built from a config, loaded from the random-weights folder and
+    stepped through the package's own step function and cache, without a change to the package."""
+    from safetensors.torch import load_file
+    from dispec_b200 import load_model, load_model_config, write_random_model
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    register_routed_toy()
+    cfg_dict = dict(architectures=["ToyRoutedForCausalLM"], vocab_size=77, hidden_size=40, heads=4, kv_heads=2,
+                    head_dim=16, intermediate_size=48, num_experts=3, num_layers=4, eps=1e-5, theta=5000.0, factor=4.0)
+    cfg = load_model_config(cfg_dict)
+    write_random_model(cfg, str(tmp_path), seed=6, std=0.15, dtype="bfloat16")
+    weights = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+    model = load_model(str(tmp_path), "float32", DEV)
+    assert [type(l.feed_forward).__name__ for l in model.layers] == ["SwiGLUFeedForward", "Top1Experts"] * 2
+    assert model.layers[1].mixer.position_encoding.rotary_dim == 8 and model.layers[0].mixer.position_encoding.rotary_dim == 16
+    runner = ModelRunner(model, page_size=8, num_pages=16, max_num_seqs=2, poison=True)
+    a, b = ru.random_ids(29, 77, 8), ru.random_ids(13, 77, 9)
+    ref_a, ref_b = plain_routed(weights, cfg_dict, a), plain_routed(weights, cfg_dict, b)
+    runner.admit("a")
+    runner.admit("b")
+    got_a, got_b = [], []
+    got_a.append(runner.step([SeqEntry("a", a[:11], 0, list(range(11)))]))
+    l = runner.step([SeqEntry("a", a[11:12], 11, [0]), SeqEntry("b", b[:7], 0, list(range(7)))])
+    got_a.append(l[:1]); got_b.append(l[1:])
+    l = runner.step([SeqEntry("b", b[7:8], 7, [0]), SeqEntry("a", a[12:], 12, list(range(17)))])
+    got_b.append(l[:1]); got_a.append(l[1:])
+    got_b.append(runner.step([SeqEntry("b", b[8:], 8, list(range(5)))]))
+    scale = max(1.0, ref_a.abs().max().item())
+    assert (torch.cat(got_a).cpu() - ref_a).abs().max().item() < 2e-4 * scale
+    assert (torch.cat(got_b).cpu() - ref_b).abs().max().item() < 2e-4 * scale
