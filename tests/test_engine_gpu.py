@@ -180,6 +180,51 @@ def test_overlapped_steps_give_the_same_tokens_as_waiting_for_every_step(folders
     assert steps_overlapped >= steps_waited
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_overlapped_steps_under_page_pressure_random_workload(folders, seed):
+    """Thirty requests of random lengths, ends of sequence and priorities through a pool so small
+    that requests are preempted and recomputed, arriving in three waves: overlapped steps against
+    waiting for every step, in 32-bit so that equal means equal."""
+    import random as pyrandom
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    folder, config, weights = folders["a"]
+    model = load(folder, "float32")
+    rnd_ = pyrandom.Random(seed)
+    reqs = []
+    for i in range(30):
+        n = rnd_.randrange(1, 40)
+        reqs.append(dict(prompt=ru.random_ids(n, config["vocab_size"], 900 + 31 * seed + i),
+                         max_new=rnd_.randrange(1, 24), eos=rnd_.choice([None, None, rnd_.randrange(config["vocab_size"])]),
+                         temperature=rnd_.choice([0.0, 0.0, 0.9]), priority=rnd_.choice([0, 0, 1]), wave=i % 3))
+
+    def run(overlap):
+        engine = ContinuousBatchingEngine(model, KVConfig(block_size=16), num_blocks=14, max_batch_tokens=48,
+                                          chunk_size=16, max_num_seqs=8, overlap=overlap)
+        ids = {}
+        for wave in range(3):
+            for i, r in enumerate(reqs):
+                if r["wave"] == wave:
+                    ids[i] = engine.add_request(r["prompt"], r["max_new"],
+                                                SamplingParams(temperature=r["temperature"], seed=70 + i),
+                                                eos_id=r["eos"], priority=r["priority"])
+            for _ in range(7):
+                engine.step()
+        engine.run_until_done()
+        out = engine.collect_outputs()
+        assert engine.runner.cache.num_free_pages() == 14 and not engine.has_work()
+        engine.runner.cache.check()
+        return [out[ids[i]] for i in range(len(reqs))], engine.num_preemptions
+
+    waited, pre_waited = run(False)
+    overlapped, pre_overlapped = run(True)
+    assert waited == overlapped
+    assert pre_waited > 0 and pre_overlapped > 0, "the pool was meant to be too small"
+    for r, toks in zip(reqs, waited):
+        assert 1 <= len(toks) <= r["max_new"]
+        if r["eos"] is not None and r["eos"] in toks:
+            assert toks.index(r["eos"]) == len(toks) - 1
+
+
 def test_no_leak_between_identical_requests(folders):
     from dispec_b200 import ContinuousBatchingEngine, SamplingParams
     folder, config, _ = folders["a"]
