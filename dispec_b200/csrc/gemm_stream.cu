@@ -236,7 +236,23 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int rows_per = (a.M + splits - 1) / splits;
     float* inbox = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // second half of the start barrier
+    // bias and residual of the rows this CTA finishes are fetched while the products still run
+    constexpr int MAX_OWN = 8;  // rows per CTA: at most 16 rows over at least 2 ranks
+    float own_res[MAX_OWN];
+    float own_bias = 0.f;
+    auto fetch_own = [&]() {
+      pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+      const int n = blockIdx.x * ROWS_W + row;
+#pragma unroll
+      for (int slot = 0; slot < MAX_OWN; ++slot) {
+        const int m = rank + slot * splits;
+        own_res[slot] = (!swiglu && a.residual && m < a.M && n < a.N)
+                            ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f;
+      }
+      if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
+    };
     if (warp >= 2) {
+      fetch_own();
       const bool ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
       tc_fence_after();
@@ -261,23 +277,25 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     cluster.sync();
     if (warp >= 2 && !failed) {
-      pdl_wait();
       const int n = blockIdx.x * ROWS_W + row;
-      for (int slot = 0; slot < rows_per; ++slot) {
+#pragma unroll
+      for (int slot = 0; slot < MAX_OWN; ++slot) {
         const int m = rank + slot * splits;
-        if (m >= a.M) break;
-        float total = 0.f, total_up = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
-          const float* src = inbox + (sp * rows_per + slot) * ROWS_W + row;
-          total += src[0];
-          if (swiglu && lane < 16) total_up += src[16];
-        }
-        if (swiglu) {
-          if (lane < 16 && n + 16 < a.N)
-            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
-        } else if (n < a.N) {
-          finish<TOut>(a, total, m, n);
+        if (slot < rows_per && m < a.M) {
+          float total = 0.f, total_up = 0.f;
+          for (int sp = 0; sp < splits; ++sp) {
+            const float* src = inbox + (sp * rows_per + slot) * ROWS_W + row;
+            total += src[0];
+            if (swiglu && lane < 16) total_up += src[16];
+          }
+          if (swiglu) {
+            if (lane < 16 && n + 16 < a.N)
+              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
+                  from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+          } else if (n < a.N) {
+            // the same order of sums as finish(): bias, then residual
+            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>((total + own_bias) + own_res[slot]);
+          }
         }
       }
     }
