@@ -397,7 +397,6 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* c, co
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
@@ -505,6 +504,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
 
   pdl_wait();
+  // the next kernel (the output projection) may start now and not earlier: its weight ring would
+  // compete with the key tiles requested above (measured: 1.314 ms -> 1.294 ms per decode step)
+  pdl_launch_dependents();
   const int half = p.rotary_dim / 2;
   if (p.fused_rope) {
     // cos and sin of this position's angles, once for q and for the new key

@@ -61,6 +61,9 @@ struct Args {
   int M, N, K;
   int kb_per_split;
   int epilogue;
+  // when the next kernel may start (programmatic dependent launch): 0 at once, 1 when this CTA has
+  // requested its last tile of W
+  int late_trigger;
 };
 
 template <typename TOut>
@@ -85,7 +88,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
-  pdl_launch_dependents();
+  if (!a.late_trigger) pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int splits = gridDim.y, split = blockIdx.y;
   const int n_blocks = (a.N + ROWS_W - 1) / ROWS_W;
@@ -149,6 +152,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tma_load_2d(dst, &map_w, &full_bar[s], k_of(it), w_row(it));
         tma_load_2d(dst + W_BYTES, &map_x, &full_bar[s], k_of(it), 0);
       }
+      if (a.late_trigger) pdl_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -433,6 +437,11 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   a.K = K;
   a.kb_per_split = kb_per_split;
   a.epilogue = epilogue;
+  // A long stream (gate/up, down, the output head) lets the next kernel start only when its own
+  // last tile is on its way: what the next kernels request before their wait (weight rings, key
+  // tiles) would otherwise compete with this stream.  Short products let it start at once.
+  // Measured on the captured decode step of the 1.5B shape: 1.334 ms -> 1.312 ms.
+  a.late_trigger = (long)kb_total * n_blocks >= 1000 ? 1 : 0;
   if (out_dtype == DSP_BF16) {
     if (nb_rows == 16) return launch<16, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
     if (nb_rows == 32) return launch<32, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
