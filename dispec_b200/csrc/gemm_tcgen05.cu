@@ -105,6 +105,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (e.K + BK - 1) / BK;
   const int n_tiles = (e.N + BN - 1) / BN, m_tiles = (e.M + BM - 1) / BM;
@@ -136,6 +137,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     // ---- TMA producer: the ring runs on across tiles
     if (lane == 0) {
+      pdl_wait();  // A comes from the kernel before
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
@@ -190,6 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {
     // ---- epilogue warps 2..5: warp w owns accumulator lanes 32 (w % 4) .. +31
+    pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
     const int quarter = warp & 3;
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
@@ -296,6 +299,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const int num_kb = (e.K + BK - 1) / BK;
@@ -330,6 +334,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (warp == 0) {
     if (lane == 0) {
+      pdl_wait();  // A comes from the kernel before
       int it = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
         const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
@@ -380,6 +385,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
+    pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
     const int quarter = warp & 3;
     int local = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
@@ -475,7 +481,8 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
       prefer_max_shared(reinterpret_cast<const void*>(gemm_tcgen05_pair_kernel<TYPE, WIDTH>));               \
       configured = true;                                                                                     \
     }                                                                                                        \
-    gemm_tcgen05_pair_kernel<TYPE, WIDTH><<<grid2, THREADS, smem2, stream>>>(map_a, map_w, e, err);          \
+    launch_pdl(gemm_tcgen05_pair_kernel<TYPE, WIDTH>, grid2, dim3(THREADS), smem2, stream, map_a, map_w,     \
+               e, err);                                                                                      \
   } while (0)
     if (out_dtype == DSP_BF16) {
       if (bnp == 192) DSP_LAUNCH_PAIR(bf16, 192); else DSP_LAUNCH_PAIR(bf16, 256);
@@ -494,14 +501,14 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
       DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       configured = true;
     }
-    gemm_tcgen05_kernel<bf16><<<grid, THREADS, smem, stream>>>(map_a, map_w, e, err);
+    launch_pdl(gemm_tcgen05_kernel<bf16>, dim3(grid), dim3(THREADS), smem, stream, map_a, map_w, e, err);
   } else {
     static bool configured = false;
     if (!configured) {
       DSP_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       configured = true;
     }
-    gemm_tcgen05_kernel<float><<<grid, THREADS, smem, stream>>>(map_a, map_w, e, err);
+    launch_pdl(gemm_tcgen05_kernel<float>, dim3(grid), dim3(THREADS), smem, stream, map_a, map_w, e, err);
   }
   DSP_CHECK_LAUNCH("dsp_gemm_tcgen05");
   return 0;
