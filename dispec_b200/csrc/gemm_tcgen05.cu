@@ -137,21 +137,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     // ---- TMA producer: the ring runs on across tiles
     if (lane == 0) {
-      pdl_wait();  // A comes from the kernel before
+      // The weights do not depend on the kernel before: the first ring of W tiles is asked for
+      // while that kernel still runs.  A comes from it, so A waits.
+      const int ahead = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < ahead; ++kb) {
+        mbar_expect_tx(&full_bar[kb], STAGE_BYTES);
+        tma_load_2d(smem + kb * STAGE_BYTES + A_BYTES, &map_w, &full_bar[kb], kb * BK,
+                    ((int)blockIdx.x % n_tiles) * BN);
+      }
+      pdl_wait();
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
-            failed = 1;
-            break;
-          }
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           unsigned char* a_dst = smem + s * STAGE_BYTES;
+          if (it >= ahead) {
+            if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+              failed = 1;
+              break;
+            }
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+          }
           tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
-          tma_load_2d(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
         }
       }
     }
@@ -334,7 +344,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (warp == 0) {
     if (lane == 0) {
-      pdl_wait();  // A comes from the kernel before
+      // as in the one-CTA kernel: the first ring of W tiles is asked for before the wait
+      const int ahead = num_kb < STAGES2 ? num_kb : STAGES2;
+      for (int kb = 0; kb < ahead; ++kb) {
+        if (rank == 0) mbar_expect_tx(&full_bar[kb], 2 * STAGE_P);
+        tma_load_2d_pair(smem + kb * STAGE_P + A_BYTES, &map_w, &full_bar[kb], kb * BK,
+                         (pair % n_tiles) * BNP + (int)rank * (BNP / 2));
+      }
+      pdl_wait();
       int it = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
         const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
@@ -342,14 +359,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
-            failed = 1;
-            break;
-          }
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P);
           unsigned char* a_dst = smem + s * STAGE_P;
+          if (it >= ahead) {
+            if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+              failed = 1;
+              break;
+            }
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P);
+            tma_load_2d_pair(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, w0);
+          }
           tma_load_2d_pair(a_dst, &map_a, &full_bar[s], kb * BK, m0);
-          tma_load_2d_pair(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, w0);
         }
       }
     }
