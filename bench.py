@@ -140,15 +140,20 @@ def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
     for rid in ids:
         runner.admit(rid)
     last = {}
-    pending = list(zip(ids, prompts))
-    while pending:  # prefill, untimed
+    pending = [(rid, p, 0) for rid, p in zip(ids, prompts)]
+    while pending:  # prefill, untimed: whole prompts side by side, longer ones in portions
         batch, used = [], 0
-        while pending and used + len(pending[0][1]) <= max_batch_tokens:
-            rid, p = pending.pop(0)
-            batch.append(SeqEntry(rid, p, 0, [len(p) - 1]))
-            used += len(p)
+        while pending and used < max_batch_tokens:
+            rid, p, done = pending.pop(0)
+            n = min(len(p) - done, max_batch_tokens - used)
+            if done + n < len(p):
+                batch.append(SeqEntry(rid, p[done:done + n], done, []))
+                pending.insert(0, (rid, p, done + n))
+            else:
+                batch.append(SeqEntry(rid, p[done:], done, [n - 1]))
+            used += n
         toks = ops.argmax(runner.step(batch)).tolist()
-        for e, t in zip(batch, toks):
+        for e, t in zip([e for e in batch if e.want], toks):
             last[e.req_id] = t
     pos = {rid: len(p) for rid, p in zip(ids, prompts)}
     # Each step takes its tokens from the previous step's result on the device and copies its own
@@ -246,6 +251,8 @@ def run_ours(args) -> dict:
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
+    if args.only == "decode" and args.context:
+        cfg_dict["max_position_embeddings"] = max(cfg_dict["max_position_embeddings"], 2 * args.context)
     layers = cfg_dict["num_hidden_layers"]
     cfg = load_model_config(cfg_dict)
     t0 = time.time()
@@ -253,16 +260,20 @@ def run_ours(args) -> dict:
     print(f"bench: model ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
     pk = peaks()
     weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg_dict, layers)
-    pages_per_req = (PROMPT_LEN + NEW_TOKENS + args.steps + args.warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    prompt_len = args.context if args.only == "decode" and args.context else PROMPT_LEN
+    pages_per_req = (prompt_len + NEW_TOKENS + args.steps + args.warmup + PAGE_SIZE) // PAGE_SIZE + 1
     vocab = cfg_dict["vocab_size"]
 
     def runner_for(batch):
         return ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(batch * pages_per_req, 160),
                            max_num_seqs=max(batch, 8), cuda_graph=True)
 
+    if args.max_key_ranges:
+        from dispec_b200.ops import attention
+        attention.MAX_OUTER = args.max_key_ranges
     if args.only == "decode":
         r = runner_for(args.batch)
-        ms, launches, ctx = decode_direct(r, random_prompts(args.batch, PROMPT_LEN, vocab, 11), args.steps, args.warmup)
+        ms, launches, ctx = decode_direct(r, random_prompts(args.batch, prompt_len, vocab, 11), args.steps, args.warmup)
         step_bytes = weight_bytes + args.batch * ctx * kv_per_token
         return {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
                 "ms_per_step": round(ms, 4), "tok_s": round(args.batch * 1000.0 / ms, 1),
@@ -391,6 +402,10 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="profiling aid: run one phase only and print a short line")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
+    ap.add_argument("--max-key-ranges", type=int, default=0,
+                    help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")
+    ap.add_argument("--context", type=int, default=0,
+                    help="prompt length of the --only decode phase (default: the recorded configuration's)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     args = ap.parse_args()
     globals()["PAGE_SIZE"] = args.page_size

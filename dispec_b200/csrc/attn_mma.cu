@@ -62,6 +62,8 @@ struct Params {
   // itself and, if write_kv, rotates the token's key, stores key and value into the cache and uses them
   const float* inv_freq;
   int rotary_dim, fused_rope, write_kv;
+  // single-token kernel only: key ranges per row beyond the cluster (their partials go to part_o / part_ml)
+  int num_outer, num_dec_tiles;
 };
 
 __device__ __forceinline__ uint32_t sw(int row, int chunk) {
@@ -399,18 +401,31 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
-  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  // A row's keys are cut into num_outer ranges, each range into the nsplit CTAs of one cluster.
+  // The cluster merges on chip; with more than one range its result is a partial in global
+  // memory and dsp_attn_combine merges the ranges.
+  const int tile = blockIdx.x % p.num_dec_tiles, outer = blockIdx.x / p.num_dec_tiles;
+  const int kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  const bool to_partials = p.num_outer > 1;
   // the tile list, lengths and page tables come from the host, not from the kernel before
   const int seq = p.tile_seq[tile];
   const int qs = p.q_start[seq];
   const int ctx = p.ctx_len[seq];
-  if (ctx <= 0) return;  // a padding row: the whole cluster leaves
   const int G = p.G;
+  if (ctx <= 0) {  // a padding row: the whole cluster leaves (its partials say "no key seen")
+    if (to_partials && split == 0 && tid < G) {
+      pdl_wait();
+      const size_t idx = ((size_t)qs * p.H + kvh * G + tid) * p.num_outer + outer;
+      p.part_ml[idx * 2] = -INFINITY;
+      p.part_ml[idx * 2 + 1] = 0.f;
+    }
+    return;
+  }
   const int pos = ctx - 1;
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
   const int kt_begin = lo / DK, kt_end = pos / DK + 1;
-  const int per = (kt_end - kt_begin + nsplit - 1) / nsplit;
-  const int my_begin = kt_begin + split * per;
+  const int per = (kt_end - kt_begin + nsplit * p.num_outer - 1) / (nsplit * p.num_outer);
+  const int my_begin = kt_begin + (outer * nsplit + split) * per;
   const int my_end = min(kt_end, my_begin + per);
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
   const uint32_t q_s = s_base;
@@ -746,7 +761,18 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
         if (d < D) acc[j] += wgt * po[d];
       }
     }
-    if (last_level) {
+    if (last_level && to_partials) {
+      const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) p.part_o[idx * D + d] = acc[j];
+      }
+      if (lane == 0) {
+        p.part_ml[idx * 2] = M;
+        p.part_ml[idx * 2 + 1] = L;
+      }
+    } else if (last_level) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
       bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
 #pragma unroll
@@ -802,6 +828,19 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
 #pragma unroll
       for (int j = 0; j < (D + 31) / 32; ++j) acc[j] += wgt * po[c][j];
     }
+    if (to_partials) {
+      const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
+#pragma unroll
+      for (int j = 0; j < (D + 31) / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) p.part_o[idx * D + d] = acc[j];
+      }
+      if (lane == 0) {
+        p.part_ml[idx * 2] = M;
+        p.part_ml[idx * 2 + 1] = L;
+      }
+      continue;
+    }
     const float inv = L > 0.f ? 1.f / L : 0.f;
     bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
 #pragma unroll
@@ -814,20 +853,24 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
 }
 }  // namespace
 
-// Runs tiles [tile_offset, tile_offset + num_tiles) of the tile list.  With num_splits > 1 the
-// partials go to part_o / part_ml and dsp_attn_combine must follow.
+// Runs tiles [tile_offset, tile_offset + num_tiles) of the tile list.  With num_splits > 1 and no
+// cluster the partials go to part_o / part_ml, [row][num_splits], and dsp_attn_combine must follow.
+// The single-token kernel (decode_only) takes num_outer key ranges per row on top of the cluster's
+// num_splits; with num_outer > 1 its partials are [row][num_outer] and dsp_attn_combine follows.
 extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     const void* q, long q_stride, const void* k_pool, const void* v_pool, const int* page_table,
     int pt_stride, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0,
     int tile_offset, int num_tiles, void* out, long out_stride, float* part_o, float* part_ml, int H,
     int KVH, int tokens_per_tile, int page_size, int num_pages, int window, int num_splits,
-    int cluster_combine, int decode_only, float scale, const float* inv_freq, int rotary_dim, int fused_rope,
+    int cluster_combine, int decode_only, int num_outer, float scale, const float* inv_freq, int rotary_dim, int fused_rope,
     int write_kv, int* err, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (KVH <= 0 || H % KVH != 0 || (H / KVH) * tokens_per_tile > BM || tokens_per_tile < 1) return 2;
   if (num_splits < 1 || num_splits > 65535 || KVH > 65535) return 2;
   if (num_splits > 1 && !cluster_combine && (part_o == nullptr || part_ml == nullptr)) return 2;
   if (cluster_combine && !decode_only && (num_splits < 2 || num_splits > 8)) return 2;
+  if (num_outer < 1 || (num_outer > 1 && (!decode_only || part_o == nullptr || part_ml == nullptr))) return 2;
+  if ((long)num_tiles * num_outer > 0x7fffffffL) return 2;
   if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) ||
       ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4))
     return 3;
@@ -862,6 +905,8 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   p.rotary_dim = rotary_dim;
   p.fused_rope = fused_rope;
   p.write_kv = write_kv;
+  p.num_outer = num_outer;
+  p.num_dec_tiles = num_tiles;
   if (fused_rope) {
     // only the single-token kernel rotates, and in 16-byte pieces
     if (!(decode_only && p.G <= 16 && num_splits <= 8 && DEC_SMEM <= 227 * 1024)) return 2;
@@ -885,7 +930,7 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     }
     if (tile_offset != 0) return 2;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
+    cfg.gridDim = dim3(num_tiles * num_outer, KVH, num_splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = (size_t)DEC_SMEM;
     cfg.stream = stream;
@@ -901,6 +946,7 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
     prefer_max_shared(reinterpret_cast<const void*>(attn_decode_kernel));
     return cudaLaunchKernelEx(&cfg, attn_decode_kernel, p) == cudaSuccess ? 0 : 1;
   }
+  if (num_outer > 1) return 2;  // only the single-token kernel cuts a row's keys beyond the cluster
   if (cluster_combine) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -77,6 +77,7 @@ class StepContext:
         self.cache_groups = None
         self.page_size = 0
         self.decode_splits = 0  # fixed number of key splits for single-token rows (0: chosen per step)
+        self.decode_outer = 0  # fixed number of key ranges per single-token row beyond the cluster (0: chosen)
         self.num_fed = 0  # single tokens whose value comes from the previous step on the device
         self.graph_capture = False  # host-side choices must not depend on the step's values
         self.scratch: dict = {}

@@ -19,6 +19,11 @@ from dispec_b200.engine.batch import HostStaging, SeqEntry, StepPlanLayout, buil
 from dispec_b200.ops import library as _library
 from dispec_b200.models.model import DecoderModel
 
+# Context lengths for which a captured decode step is laid out (the last class is the engine's
+# own maximum): few enough that little is captured, far enough apart that a short context does
+# not pay for the key sharing that a long one needs.
+GRAPH_CONTEXT_CLASSES = (2048, 8192, 32768, 131072, 524288)
+
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages=4096,
@@ -108,8 +113,19 @@ class ModelRunner:
         return logits
 
     # -------------------------------------------------------- captured all-decode steps
-    def _capture(self, bucket: int) -> dict:
-        """Captures one decode step of ``bucket`` single-token rows as a CUDA graph.  Every
+    def _context_class(self, entries: list) -> int:
+        """The context length a captured step is laid out for: the smallest class that holds the
+        step's longest request.  How the keys of a row are shared among CTAs is decided on the
+        host from this bound, so a graph serves one class."""
+        longest = max(e.start + len(e.tokens) for e in entries)
+        for bound in GRAPH_CONTEXT_CLASSES:
+            if longest <= bound < self.max_model_len:
+                return bound
+        return self.max_model_len
+
+    def _capture(self, bucket: int, ctx_bound: int) -> dict:
+        """Captures one decode step of ``bucket`` single-token rows, none longer than
+        ``ctx_bound``, as a CUDA graph.  Every
         integer input lives in one device buffer of fixed address and layout; a replay copies
         the step's values there first.  Rows beyond the live requests carry position -1 and
         length 0, which the kernels skip."""
@@ -118,7 +134,7 @@ class ModelRunner:
         buffer = torch.empty(plan.total, dtype=torch.int32, device=self.device)
         self.staging.upload(plan.total, plan.fill, into=buffer)
         ctx = plan.context(buffer, self.storage, self.states, self.dtype, self.device)
-        ctx.max_ctx_len = self.max_model_len  # choices made on the host must not vary per step
+        ctx.max_ctx_len = ctx_bound  # choices made on the host must not vary per step
         ctx.graph_capture = True
 
         def run():
@@ -138,12 +154,13 @@ class ModelRunner:
             logits = run()
         entry = dict(graph=graph, buffer=buffer, total=plan.total, logits=logits,
                      launches=_library.LaunchCounter.n - before)
-        self._graphs[bucket] = entry
+        self._graphs[(bucket, ctx_bound)] = entry
         return entry
 
     def _graph_step(self, entries: list, feed_tokens=None) -> torch.Tensor:
         bucket = next(b for b in self.graph_buckets if b >= len(entries))
-        g = self._graphs.get(bucket) or self._capture(bucket)
+        ctx_bound = self._context_class(entries)
+        g = self._graphs.get((bucket, ctx_bound)) or self._capture(bucket, ctx_bound)
         plan = StepPlanLayout(entries, self.cache, self.model.attention_tile_tokens, self.vocab_size,
                               pad_seqs=bucket, fixed_pages=self._graph_pages)
         assert plan.total == g["total"]

@@ -112,6 +112,19 @@ def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int) -> int
 
 
 CLUSTER_MAX_SPLITS = 8  # splits that merge on chip (one thread-block cluster per tile)
+OUTER_MIN_KEYS = 256  # a CTA of a row cut into ranges still reads at least this many keys
+MAX_OUTER = 32
+
+
+def choose_outer(num_decode_tiles: int, num_kv_heads: int, max_ctx: int, splits: int) -> int:
+    """Key ranges per single-token row on top of the cluster's ``splits``: when a full cluster
+    per row and KV head still leaves SMs idle (few rows) and the context is long enough to share.
+    Measured (12 heads over 2 KV heads, head size 128): the best count brings the launch to about
+    256 CTAs (16 ranges at batch 1 and 32,768 keys, 2 at batch 8), as long as a CTA keeps 256 keys."""
+    if num_decode_tiles <= 0 or splits < CLUSTER_MAX_SPLITS or not USE_DECODE_KERNEL:
+        return 1
+    want = TARGET_CTAS // (num_decode_tiles * num_kv_heads * splits)
+    return max(1, min(want, MAX_OUTER, max_ctx // (splits * OUTER_MIN_KEYS)))
 
 
 def decode_rope_fusable(ctx, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
@@ -128,7 +141,7 @@ def decode_rope_fusable(ctx, num_heads: int, num_kv_heads: int, head_dim: int, r
 
 def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
                 tile_offset, num_tiles, out, part_o, part_ml, H, KVH, D, tpt, window, splits, scale,
-                cluster_combine=False, decode_only=False, fused_rope=None):
+                cluster_combine=False, decode_only=False, fused_rope=None, outer=1):
     num_pages, _, page_size, _ = k_pool.shape
     lib = L.attention_library(D)
     fn = getattr(lib, f"dsp_attn_mma_d{D}")
@@ -136,7 +149,7 @@ def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_
             page_table.stride(0), L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0),
             tile_offset, num_tiles, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml),
             H, KVH, tpt, page_size, num_pages, window, splits, int(cluster_combine), int(decode_only),
-            L.f32(scale), L.ptr(fused_rope[0]) if fused_rope else None, fused_rope[1] if fused_rope else 0,
+            outer, L.f32(scale), L.ptr(fused_rope[0]) if fused_rope else None, fused_rope[1] if fused_rope else 0,
             1 if fused_rope else 0, int(fused_rope[2]) if fused_rope else 0,
             ctypes.c_void_p(_device_error_address(q.device)), L.stream_handle())
     L.LaunchCounter.n += 1
@@ -165,13 +178,15 @@ _TCGEN05_ERRORS = {1: "launch failed", 2: "unsupported head/group counts or page
 
 def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                           tile_tok0, num_tiles, num_decode_tiles, out, H, KVH, D, window, scale,
-                          splits: int, prefill_tiles=None, fused_rope=None) -> torch.Tensor:
+                          splits: int, prefill_tiles=None, fused_rope=None, outer: int = 1) -> torch.Tensor:
     """Tensor-core attention over a tile list whose first ``num_decode_tiles`` tiles are single
     tokens (run with ``splits`` key splits and merged), the rest portions of prompts.  With
     ``prefill_tiles`` = (tile_seq, tile_tok0, num_tiles) of the 128-row tiling (single tokens
     first as well) the portions of prompts run on the tcgen05 kernel.  ``fused_rope`` = (inv_freq,
     rotary_dim, write_kv): ``q`` are the fused q/k/v rows and the single tokens' rows are not
-    rotated yet; their kernel rotates them and stores key and value (see ``decode_rope_fusable``)."""
+    rotated yet; their kernel rotates them and stores key and value (see ``decode_rope_fusable``).
+    ``outer`` > 1 cuts each single token's keys into that many ranges, each run by a cluster of
+    ``splits`` CTAs; a second kernel merges the ranges (long contexts at small batches)."""
     assert q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
     tpt = tokens_per_tile(H // KVH)
@@ -179,11 +194,20 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
         if splits <= CLUSTER_MAX_SPLITS and USE_CLUSTER_COMBINE and (
                 (USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS) or splits > 1):
             # single tokens: the cluster kernels (warp-parallel keys when the group fits 16 rows)
+            decode_only = USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS
+            if outer > 1 and not decode_only:
+                outer = 1
+            part_o = part_ml = None
+            if outer > 1:
+                part_o, part_ml = _partial_buffers(q.device, num_decode_tiles * H, outer, D)
             _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
-                        tile_tok0, 0, num_decode_tiles, out, None, None, H, KVH, D, tpt, window,
-                        splits, scale, cluster_combine=splits > 1,
-                        decode_only=USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS,
-                        fused_rope=fused_rope)
+                        tile_tok0, 0, num_decode_tiles, out, part_o, part_ml, H, KVH, D, tpt, window,
+                        splits, scale, cluster_combine=splits > 1, decode_only=decode_only,
+                        fused_rope=fused_rope, outer=outer)
+            if outer > 1:
+                L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out),
+                                                  L.i64(out.stride(0)), num_decode_tiles, H, D, outer,
+                                                  L.dtype_code(out.dtype), L.stream_handle()))
         elif fused_rope:
             raise L.KernelError("single tokens were left unrotated for a kernel that is not in use")
         elif splits > 1:
@@ -257,6 +281,8 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
         tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
         splits = ctx.decode_splits if ctx.decode_splits else choose_splits(
             ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len)
+        outer = ctx.decode_outer if ctx.decode_outer else choose_outer(
+            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len, splits)
         prefill_tiles = None
         big = prefill_tokens_per_tile(group)
         if big in ctx.attention_tiles and tcgen05_supported(head_dim, group, cache.key_pool.shape[2], q.dtype):
@@ -264,7 +290,7 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
         return paged_attention_tiles(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                      ctx.q_start, ctx.ctx_len, tile_seq, tile_tok0, num_tiles,
                                      ctx.num_decode_seqs, out, num_heads, num_kv_heads, head_dim,
-                                     window, scale, splits, prefill_tiles, fused_rope)
+                                     window, scale, splits, prefill_tiles, fused_rope, outer)
     if fused_rope:
         raise L.KernelError("single tokens were left unrotated for a kernel that is not in use")
     return paged_attention_generic(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,

@@ -50,6 +50,8 @@ TINY = {
     "c": dict(config=CONFIG_C, seed=7, std=0.04, page_size=16),
     "d": dict(config=CONFIG_D, seed=9, std=0.06, page_size=32),
     "e": dict(config=CONFIG_E, seed=4, std=0.05, page_size=8),
+    # configuration A with room for long contexts
+    "a_long": dict(config=dict(CONFIG_A, max_position_embeddings=16384), seed=0, std=0.02, page_size=16),
 }
 
 

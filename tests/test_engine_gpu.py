@@ -315,7 +315,7 @@ def test_captured_decode_steps_match_eager_steps(folders):
             for r in live:
                 pos[r] += 1
         if graphs:
-            assert set(runner._graphs) == {2, 4}
+            assert {bucket for bucket, _ in runner._graphs} == {2, 4}
         runner.check_device()
         results.append(torch.cat(rows))
     refs = {r: plain.forward_logits(weights, config, p) for r, p in prompts.items()}
@@ -323,6 +323,36 @@ def test_captured_decode_steps_match_eager_steps(folders):
     assert (results[0] - results[1]).abs().max().item() < 0.03 * scale
     # and both are right: the first decoded row of x
     assert (results[1][0] - refs["x"][len(prompts["x"]) - 8]).abs().max().item() < 0.03 * scale + 0.02
+
+
+def test_captured_decode_steps_follow_the_context_into_the_next_class(tmp_path):
+    """One request decoded from 2,041 to 2,056 tokens: the captured step changes, at 2,048, to the
+    one laid out for longer contexts, which cuts the row's keys into ranges merged by a second
+    kernel.  The logits stay those of the eager path and of the plain implementation."""
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    from dispec_b200.ops import attention as A
+    folder = str(tmp_path)
+    config, weights = ru.make_model_folder(folder, "a_long", dtype="bfloat16")
+    model = load(folder, "bfloat16")
+    n, tail = 2056, 16
+    ids = ru.random_ids(n, config["vocab_size"], 77)
+    results = []
+    for graphs in (False, True):
+        runner = ModelRunner(model, page_size=16, num_pages=600, max_num_seqs=2, cuda_graph=graphs,
+                             poison=True)
+        runner.admit("r")
+        runner.step([SeqEntry("r", ids[:n - tail], 0, [])])
+        rows = [runner.step([SeqEntry("r", [ids[i]], i, [0])]).float().cpu().clone() for i in range(n - tail, n)]
+        if graphs:
+            assert set(runner._graphs) == {(1, 2048), (1, 8192)}
+        runner.check_device()
+        results.append(torch.cat(rows))
+    kvh = config["num_key_value_heads"]
+    assert A.choose_outer(1, kvh, 8192, A.choose_splits(1, kvh, 8192)) > 1  # the second class does cut
+    ref = plain.forward_logits(weights, config, ids)[n - tail:]
+    scale = ref.abs().max().item()
+    assert (results[0] - results[1]).abs().max().item() < 0.03 * scale
+    assert (results[1] - ref).abs().max().item() < 0.03 * scale + 0.02
 
 
 def test_command_line_generate_and_random(tmp_path):

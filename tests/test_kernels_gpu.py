@@ -596,9 +596,59 @@ def test_attention_tcgen05_window_edge(offset, q_len):
 
 
 
-@pytest.mark.parametrize("H,KVH,D,rot,page,window", [(12, 2, 128, 128, 16, 0), (6, 3, 64, 32, 8, 40), (4, 4, 16, 16, 32, 0),
-                                                     (14, 2, 48, 48, 16, 0)])
-def test_decode_attention_that_rotates_and_stores_itself(H, KVH, D, rot, page, window):
+@pytest.mark.parametrize("splits,outer", [(8, 2), (8, 5), (3, 4), (1, 3)])
+@pytest.mark.parametrize("H,KVH,D,page,window", [(12, 2, 128, 16, 0), (6, 3, 64, 8, 700), (14, 2, 48, 32, 0)])
+def test_decode_attention_with_key_ranges_beyond_the_cluster(splits, outer, H, KVH, D, page, window):
+    """Single tokens whose keys are cut into ``outer`` ranges of ``splits`` CTAs each, merged by a
+    second kernel: long and short rows side by side (ranges without a key, a row of one key, a
+    padding row of length 0), with one far key made to stand out in every row."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import attention as A
+    ctx_lens = [2500, 1, 0, 40, 1023, 1025]
+    plant = [1300, 0, 0, 17, 3, 1024]
+    B = len(ctx_lens)
+    g = torch.Generator().manual_seed(11 * splits + outer)
+    pages_per = [(c + page - 1) // page for c in ctx_lens]
+    num_pages = sum(pages_per) + 2
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=torch.bfloat16)
+    vp = kp.clone()
+    q = torch.randn(B, H, D, generator=g).bfloat16()
+    refs = []
+    for s, c in enumerate(ctx_lens):
+        if c == 0:
+            refs.append(None)
+            continue
+        k = torch.randn(c, KVH, D, generator=g).bfloat16()
+        v = torch.randn(c, KVH, D, generator=g).bfloat16()
+        # the planted key is the query of the group's first head, enlarged: that head sees little else
+        k[plant[s]] = (q[s, ::H // KVH] * 4.0).bfloat16()
+        for j in range(pages_per[s]):
+            table[s, j] = perm.pop()
+        for b in range(c):
+            kp[table[s, b // page], :, b % page] = k[b]
+            vp[table[s, b // page], :, b % page] = v[b]
+        refs.append(_attention_reference(q[s:s + 1].double(), k.double(), v.double(), torch.tensor([c - 1]),
+                                         window, D ** -0.5)[0])
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.full((B, H * D), float("nan"), dtype=torch.bfloat16, device=dev())
+    A.paged_attention_tiles(q.reshape(B, H * D).to(dev()), H * D, kp.to(dev()), vp.to(dev()), table.to(dev()),
+                            i32(list(range(B + 1))), i32(ctx_lens), i32(list(range(B))), i32([0] * B), B, B, out,
+                            H, KVH, D, window, D ** -0.5, splits, outer=outer)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error("decode attention with key ranges")
+    got = out.float().cpu().view(B, H, D)
+    for s, ref in enumerate(refs):
+        if ref is None:
+            continue
+        torch.testing.assert_close(got[s].double(), ref, atol=2e-2, rtol=2e-2, msg=lambda m: f"row {s}: {m}")
+
+
+@pytest.mark.parametrize("H,KVH,D,rot,page,window,outer", [(12, 2, 128, 128, 16, 0, 1), (6, 3, 64, 32, 8, 40, 1),
+                                                           (4, 4, 16, 16, 32, 0, 1), (14, 2, 48, 48, 16, 0, 1),
+                                                           (12, 2, 128, 128, 16, 0, 3), (6, 3, 64, 32, 8, 40, 2)])
+def test_decode_attention_that_rotates_and_stores_itself(H, KVH, D, rot, page, window, outer):
     """Single tokens: the kernel that rotates q and the token's key and writes key and value to the
     cache against the rotation kernel followed by the plain attention kernel: the same outputs and
     the same cache, for tokens at a page's first and last offset and in the middle."""
@@ -635,7 +685,7 @@ def test_decode_attention_that_rotates_and_stores_itself(H, KVH, D, rot, page, w
         for splits in (3,):
             A.paged_attention_tiles(rows, rows.stride(0), kp, vp, table_d, q_start, ctx_len, ts, t0, B, B, out, H,
                                     KVH, D, window, D ** -0.5, splits,
-                                    fused_rope=(inv_freq, rot, True) if fused else None)
+                                    fused_rope=(inv_freq, rot, True) if fused else None, outer=outer)
         torch.cuda.synchronize()
         results.append((out.float().cpu(), kp.float().cpu(), vp.float().cpu()))
     (o0, k0, v0), (o1, k1, v1) = results
