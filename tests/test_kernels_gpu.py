@@ -595,7 +595,6 @@ def test_attention_tcgen05_window_edge(offset, q_len):
     torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
 
 
-
 @pytest.mark.parametrize("splits,outer", [(8, 2), (8, 5), (3, 4), (1, 3)])
 @pytest.mark.parametrize("H,KVH,D,page,window", [(12, 2, 128, 16, 0), (6, 3, 64, 8, 700), (14, 2, 48, 32, 0)])
 def test_decode_attention_with_key_ranges_beyond_the_cluster(splits, outer, H, KVH, D, page, window):
