@@ -332,19 +332,44 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       pdl_wait();
       const int rank = (int)cluster.block_rank();
       const int n = blockIdx.x * ROWS_W + row;
-      for (int m = rank; m < a.M; m += splits) {
-        float total = 0.f, total_up = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
-          const float* remote = cluster.map_shared_rank(red, sp);
-          total += remote[m * ROWS_W + row];
-          if (swiglu && lane < 16) total_up += remote[m * ROWS_W + row + 16];
+      // the partial sums of four rows are requested from every CTA of the cluster at once (remote
+      // reads take a few hundred cycles each), then added in rank order
+      constexpr int ROWS_AT_ONCE = 4;
+      const float* remote[MAX_SPLITS];
+#pragma unroll
+      for (int sp = 0; sp < MAX_SPLITS; ++sp) remote[sp] = cluster.map_shared_rank(red, sp < splits ? sp : 0);
+      const bool up_lane = swiglu && lane < 16;
+      for (int m0 = rank; m0 < a.M; m0 += splits * ROWS_AT_ONCE) {
+        float part[ROWS_AT_ONCE][MAX_SPLITS], part_up[ROWS_AT_ONCE][MAX_SPLITS];
+#pragma unroll
+        for (int j = 0; j < ROWS_AT_ONCE; ++j) {
+          const int m = m0 + j * splits;
+#pragma unroll
+          for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+            const bool on = sp < splits && m < a.M;
+            part[j][sp] = on ? remote[sp][m * ROWS_W + row] : 0.f;
+            part_up[j][sp] = (on && up_lane) ? remote[sp][m * ROWS_W + row + 16] : 0.f;
+          }
         }
-        if (swiglu) {
-          if (lane < 16 && n + 16 < a.N)
-            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
-        } else if (n < a.N) {
-          finish<TOut>(a, total, m, n);
+#pragma unroll
+        for (int j = 0; j < ROWS_AT_ONCE; ++j) {
+          const int m = m0 + j * splits;
+          if (m >= a.M) break;
+          float total = 0.f, total_up = 0.f;
+#pragma unroll
+          for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+            if (sp < splits) {
+              total += part[j][sp];
+              total_up += part_up[j][sp];
+            }
+          }
+          if (swiglu) {
+            if (lane < 16 && n + 16 < a.N)
+              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
+                  from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+          } else if (n < a.N) {
+            finish<TOut>(a, total, m, n);
+          }
         }
       }
     }
