@@ -66,6 +66,7 @@ FUSE_DECODE_ROPE = True  # that kernel rotates q and the token's key itself and 
 DECODE_KERNEL_MAX_SPLITS = 8  # every split count the cluster merge allows
 TARGET_CTAS = 148 * 2
 _partials: dict = {}
+_retired: list = []
 _err_addr: dict = {}
 
 
@@ -80,7 +81,12 @@ def _partial_buffers(device, rows: int, splits: int, head_dim: int):
     need = rows * splits * (head_dim + 2)
     buf = _partials.get(key)
     if buf is None or buf.numel() < need:
-        buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device)
+        # a captured step keeps the address of the scratch it was captured with: a buffer that is
+        # outgrown stays alive (sizes at least double, so all of them together stay below twice the last)
+        if buf is not None:
+            _retired.append(buf)
+        buf = torch.empty(max(need, 1 << 20, 2 * (buf.numel() if buf is not None else 0)),
+                          dtype=torch.float32, device=device)
         _partials[key] = buf
     n_o = rows * splits * head_dim
     return buf[:n_o], buf[n_o:n_o + rows * splits * 2]
