@@ -52,6 +52,7 @@ OTHER_SHAPES = {
 SEED, STD = 2, 0.02
 BATCH, PROMPT_LEN, NEW_TOKENS, CONTEXT_LEN, PAGE_SIZE = 8, 1024, 256, 4096, 16
 PREFILL_TOKENS = 2048
+LONG_CONTEXT = 32768  # an extra point: decoding one request at this context length
 
 
 def peaks() -> dict:
@@ -251,8 +252,6 @@ def run_ours(args) -> dict:
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
-    if args.only == "decode" and args.context:
-        cfg_dict["max_position_embeddings"] = max(cfg_dict["max_position_embeddings"], 2 * args.context)
     layers = cfg_dict["num_hidden_layers"]
     cfg = load_model_config(cfg_dict)
     t0 = time.time()
@@ -264,15 +263,15 @@ def run_ours(args) -> dict:
     pages_per_req = (prompt_len + NEW_TOKENS + args.steps + args.warmup + PAGE_SIZE) // PAGE_SIZE + 1
     vocab = cfg_dict["vocab_size"]
 
-    def runner_for(batch):
-        return ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(batch * pages_per_req, 160),
-                           max_num_seqs=max(batch, 8), cuda_graph=True)
+    def runner_for(batch, per_req=pages_per_req, max_len=None):
+        return ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(batch * per_req, 160),
+                           max_num_seqs=max(batch, 8), cuda_graph=True, max_model_len=max_len)
 
     if args.max_key_ranges:
         from dispec_b200.ops import attention
         attention.MAX_OUTER = args.max_key_ranges
     if args.only == "decode":
-        r = runner_for(args.batch)
+        r = runner_for(args.batch, max_len=2 * args.context if args.context else None)
         ms, launches, ctx = decode_direct(r, random_prompts(args.batch, prompt_len, vocab, 11), args.steps, args.warmup)
         step_bytes = weight_bytes + args.batch * ctx * kv_per_token
         return {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
@@ -307,6 +306,14 @@ def run_ours(args) -> dict:
         points[f"decode_b{b}"] = round(b * 1000.0 / bms, 1)
         del r
         torch.cuda.empty_cache()
+    # beyond the recorded configuration: one request with a long context (its keys are shared
+    # among clusters, see profiles/attn_decode_long_context.md)
+    steps = max(20, min(args.steps, 100))
+    r = runner_for(1, (LONG_CONTEXT + steps + 64) // PAGE_SIZE + 2, 2 * LONG_CONTEXT)
+    bms, _, _ = decode_direct(r, random_prompts(1, LONG_CONTEXT, vocab, 31), steps, max(3, args.warmup // 2))
+    points[f"decode_b1_ctx{LONG_CONTEXT}"] = round(1000.0 / bms, 1)
+    del r
+    torch.cuda.empty_cache()
     from dispec_b200.ops import library
     return {
         "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1,

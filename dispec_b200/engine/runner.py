@@ -27,7 +27,8 @@ GRAPH_CONTEXT_CLASSES = (2048, 8192, 32768, 131072, 524288)
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages=4096,
-                 max_num_seqs: int = 256, poison: bool = False, cuda_graph: bool = False):
+                 max_num_seqs: int = 256, poison: bool = False, cuda_graph: bool = False,
+                 max_model_len: int | None = None):
         if model.device is None:
             raise ValueError("the model has no weights yet (load it first)")
         self.model = model
@@ -48,7 +49,9 @@ class ModelRunner:
         # captured decode steps, one per padded batch size; the page tables of a captured step
         # have room for the longest sequence the pools or the model allow
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_num_seqs]
-        limit = model.spec.max_position or (1 << 30)
+        # the longest request: the configuration's max_position_embeddings unless the caller says
+        # otherwise (angles are computed from the position, so no table stands in the way of more)
+        limit = max_model_len or model.spec.max_position or (1 << 30)
         self.max_model_len = min(limit, self.cache.capacity_tokens())
         self._graph_pages = [max(1, min(c, -(-self.max_model_len // page_size))) for c in counts]
         self._graphs: dict = {}
