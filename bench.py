@@ -88,7 +88,7 @@ class ClockSampler:
                     self.samples.append([x.strip() for x in out[0].split(",")])
             except Exception:  # noqa: BLE001 - sampling must never break the run
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.05)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
