@@ -4,6 +4,12 @@
 // A split that saw no key has l_s = 0 and m_s = -inf and contributes nothing.
 #include "common.cuh"
 
+// One block per row, at most 32 splits.  Every warp reads the row's (m_s, l_s), one split per
+// lane, and finds M, the weights and the sum by shuffles (no loop of dependent loads); each thread
+// then requests the splits' outputs of its element eight at a time before it adds them in split
+// order.
+constexpr int COMBINE_MAX_SPLITS = 32;
+
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, long out_stride, int H, int D, int splits) {
@@ -12,22 +18,34 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   const size_t row = blockIdx.x;  // t * H + h
   const size_t t = row / H;
   const int h = (int)(row % H);
-  const float* ml = part_ml + row * splits * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-  float L = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float m = ml[2 * s];
-    if (m != -INFINITY) L += exp2f(m - M) * ml[2 * s + 1];
+  const int lane = threadIdx.x & 31;
+  float m = -INFINITY, l = 0.f;
+  if (lane < splits) {
+    const float2 ml = reinterpret_cast<const float2*>(part_ml)[row * splits + lane];
+    m = ml.x;
+    l = ml.y;
   }
+  const float M = warp_max(m);
+  const float w = m == -INFINITY ? 0.f : exp2f(m - M);
+  const float L = warp_sum(w * l);
   const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  const float* po = part_o + row * splits * D;
+  for (int d0 = (int)threadIdx.x - lane; d0 < D; d0 += blockDim.x) {  // the same trips for a whole warp (shuffles)
+    const int d = d0 + lane;
+    const bool on = d < D;
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = ml[2 * s];
-      if (m != -INFINITY) acc += exp2f(m - M) * part_o[(row * splits + s) * D + d];
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float ws = __shfl_sync(0xffffffffu, w, (s0 + j) & 31);
+        // a split that saw no key has weight 0 and an output that was never written: not read
+        v[j] = (on && s0 + j < splits && ws != 0.f) ? ws * po[(size_t)(s0 + j) * D + d] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += v[j];
     }
-    out[t * out_stride + (size_t)h * D + d] = from_f32<T>(acc * inv);
+    if (on) out[t * out_stride + (size_t)h * D + d] = from_f32<T>(acc * inv);
   }
 }
 
@@ -35,7 +53,8 @@ extern "C" int dsp_attn_combine(const float* part_o, const float* part_ml, void*
                                 int num_tokens, int H, int D, int splits, int dtype,
                                 cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  DSP_REQUIRE(splits >= 1, "dsp_attn_combine: splits=%d", splits);
+  DSP_REQUIRE(splits >= 1 && splits <= COMBINE_MAX_SPLITS, "dsp_attn_combine: splits=%d outside 1..%d", splits,
+              COMBINE_MAX_SPLITS);
   const int rows = num_tokens * H;
   const int threads = D >= 128 ? 128 : 64;
   if (dtype == DSP_BF16)

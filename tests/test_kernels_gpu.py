@@ -558,6 +558,37 @@ def test_attention_tensor_core_single_token_splits(splits, decode_kernel, monkey
     torch.testing.assert_close(out.float().cpu().view(1, H, D).double(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tokens,H,D,splits", [(1, 12, 128, 16), (3, 5, 16, 1), (2, 14, 48, 7), (4, 2, 256, 32)])
+def test_attention_combine_alone(tokens, H, D, splits, out_dtype):
+    """The kernel that merges split attention, against the same formula in float64; some splits saw
+    no key (maximum -inf, sum 0, output never written), one row saw none at all."""
+    from dispec_b200.ops import library as L
+    g = torch.Generator().manual_seed(100 + splits)
+    rows = tokens * H
+    o = torch.randn(rows, splits, D, generator=g)
+    m = torch.randn(rows, splits, generator=g) * 6
+    l = torch.rand(rows, splits, generator=g) * 50 + 0.1
+    dead = torch.rand(rows, splits, generator=g) < 0.3
+    dead[0] = True  # a padding row
+    if rows > 1:
+        dead[1] = False
+    m[dead], l[dead] = float("-inf"), 0.0
+    o[dead] = float("nan")
+    w = torch.where(dead, torch.zeros(()), torch.exp2(m - m.max(1, keepdim=True).values).nan_to_num(0.0)).double()
+    num = (w[..., None] * o.nan_to_num(0.0).double()).sum(1)
+    den = (w * l.double()).sum(1, keepdim=True)
+    ref = torch.where(den > 0, num / den.clamp_min(1e-300), torch.zeros(())).view(tokens, H * D)
+    out = torch.full((tokens, H * D), float("nan"), dtype=out_dtype, device=dev())
+    ml = torch.stack([m, l], -1).contiguous().to(dev())
+    od = o.contiguous().to(dev())
+    L.check(L.core().dsp_attn_combine(L.ptr(od), L.ptr(ml), L.ptr(out), L.i64(out.stride(0)), tokens, H, D, splits,
+                                      L.dtype_code(out_dtype), L.stream_handle()))
+    torch.cuda.synchronize()
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(out.double().cpu(), ref, atol=tol, rtol=tol)
+
+
 TCGEN05_CASES = [
     # H, KVH, D, page, ctx, q_len, window: portions of prompts on the tcgen05 kernel
     (12, 2, 128, 16, 700, 300, 0),   # several query tiles, group of 6 (126 of 128 rows used)
