@@ -214,18 +214,26 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
         const int n = nb * ROWS_W + row;
+        if (swiglu) {
+          // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs.  Two rows
+          // of A at a time: the low lanes finish the first (they get its up values), the high
+          // lanes the second (they get its gate values), so every lane computes.
+          const bool low = lane < 16;
+          const int col = ((n - lane) >> 1) + (lane & 15);
+          const bool n_ok = n - lane < a.N;  // N is a multiple of 32: the block of 32 rows is whole
 #pragma unroll
-        for (int m = 0; m < NB; ++m) {
-          const float x = __uint_as_float(v[m]);
-          if (swiglu) {
-            const float up = __shfl_down_sync(0xffffffffu, x, 16);
-            // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs
-            if (lane < 16 && m < a.M && n + 16 < a.N)
-              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                  from_f32<TOut>(x / (1.f + expf(-x)) * up);
-          } else if (m < a.M && n < a.N) {
-            finish<TOut>(a, x, m, n);
+          for (int m0 = 0; m0 < NB; m0 += 2) {
+            const float x0 = __uint_as_float(v[m0]), x1 = __uint_as_float(v[m0 + 1]);
+            const float other = __shfl_xor_sync(0xffffffffu, low ? x1 : x0, 16);
+            const float gate = low ? x0 : other, up = low ? other : x1;
+            const int m = low ? m0 : m0 + 1;
+            if (m < a.M && n_ok)
+              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
           }
+        } else {
+#pragma unroll
+          for (int m = 0; m < NB; ++m)
+            if (m < a.M && n < a.N) finish<TOut>(a, __uint_as_float(v[m]), m, n);
         }
       }
     }
