@@ -522,7 +522,10 @@ def test_gemm_stream_tcgen05(M, N, K, bias, resid, out_dtype, target):
     assert torch.equal(out, again)  # the cluster sum runs in a fixed order
 
 
-@pytest.mark.parametrize("M,I,K,target", [(8, 8960, 1536, 0), (3, 224, 96, 148), (33, 2048, 1536, 0), (64, 176, 80, 0)])
+@pytest.mark.parametrize("M,I,K,target", [(8, 8960, 1536, 0), (3, 224, 96, 148), (33, 2048, 1536, 0), (64, 176, 80, 0),
+                                          # an odd number of rows (the epilogue pairs them), every width of the tile of A
+                                          (1, 8960, 1536, 0), (7, 512, 96, 0), (16, 512, 96, 0), (17, 512, 96, 0),
+                                          (24, 8960, 1536, 0), (31, 224, 96, 0), (32, 512, 776, 0), (63, 512, 96, 0)])
 def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
     from dispec_b200.ops import gemm, library
     x = rnd((M, K), torch.bfloat16, 65)
