@@ -306,21 +306,24 @@ class ContinuousBatchingEngine:
     ``add_request / step / has_work / run_until_done / collect_outputs`` as in the reference
     (dispec/sched/scheduler.py:60-63,85-101,234-244).  ``model`` is a model loaded by
     ``dispec_b200.load_model``; the reference's ``attn_backend`` and ``fuse`` switches have no
-    counterpart (there is one attention path, projections are always fused)."""
+    counterpart (there is one attention path, projections are always fused).  ``max_model_len``
+    replaces the configuration's ``max_position_embeddings`` as the longest request."""
 
     def __init__(self, model, kv: KVConfig | None = None, num_blocks: int = 2048,
                  max_batch_tokens: int = 2048, chunk_size: int | None = None, max_num_seqs: int = 256,
-                 cuda_graph: bool = True, poison: bool = False, overlap: bool = True):
+                 cuda_graph: bool = True, poison: bool = False, overlap: bool = True,
+                 max_model_len: int | None = None):
         from dispec_b200.engine.runner import ModelRunner
         from dispec_b200.sampling.sampler import Sampler
 
         kv = kv or KVConfig()
         self.block_size = kv.block_size
         self.runner = ModelRunner(model, page_size=kv.block_size, num_pages=num_blocks,
-                                  max_num_seqs=max_num_seqs, poison=poison, cuda_graph=cuda_graph)
+                                  max_num_seqs=max_num_seqs, poison=poison, cuda_graph=cuda_graph,
+                                  max_model_len=max_model_len)
         self.sampler = Sampler(model.device)
         self.scheduler = Scheduler(self.runner.cache, max_batch_tokens, chunk_size,
-                                   max_model_len=model.spec.max_position or None,
+                                   max_model_len=max_model_len or model.spec.max_position or None,
                                    on_admit=self.runner.admit, on_free=self.runner.release)
         # overlap: step n + 1 is scheduled and launched while step n runs; its tokens are read
         # one step late (outputs and the queues lag by one step until has_work / collect_outputs /
