@@ -355,6 +355,42 @@ def test_captured_decode_steps_follow_the_context_into_the_next_class(tmp_path):
     assert (results[1] - ref).abs().max().item() < 0.03 * scale + 0.02
 
 
+def test_recorded_layer_sizes_bfloat16_against_the_32_bit_path():
+    """Three layers of the Qwen2.5-1.5B sizes (width 1536, 12 heads over 2 KV heads of 128, feed-forward
+    8960, vocabulary 151936, tied head), random weights: a 700-token prompt in two portions and six
+    decoded tokens (captured steps in bfloat16), the serving kernels against the true 32-bit path."""
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    from dispec_b200.weights import load_random_model
+    cfg = load_model_config(dict(
+        architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=3, hidden_size=1536,
+        num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936,
+        rope_theta=1000000.0, rms_norm_eps=1e-6, hidden_act="silu", tie_word_embeddings=True,
+        max_position_embeddings=4096, use_sliding_window=False))
+    ids = ru.random_ids(706, 151936, 5)
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        model = load_random_model(cfg, 2, 0.02, dtype, "cuda:0")
+        runner = ModelRunner(model, page_size=16, num_pages=64, max_num_seqs=4, cuda_graph=dtype == "bfloat16")
+        runner.admit("r")
+        runner.step([SeqEntry("r", ids[:512], 0, [])])
+        rows = [runner.step([SeqEntry("r", ids[512:700], 512, [187])]).float().cpu().clone()]
+        for i in range(700, 706):
+            rows.append(runner.step([SeqEntry("r", [ids[i]], i, [0])]).float().cpu().clone())
+        runner.check_device()
+        got[dtype] = torch.cat(rows)
+        del runner, model
+        torch.cuda.empty_cache()
+    ref, out = got["float32"], got["bfloat16"]
+    scale = ref.abs().max().item()
+    assert torch.isfinite(out).all() and scale > 0.5
+    assert (out - ref).abs().max().item() < 0.03 * scale + 0.02
+    # the same next token wherever the 32-bit path is sure of it
+    top2 = ref.topk(2, dim=-1).values
+    sure = (top2[:, 0] - top2[:, 1]) > 2 * (0.03 * scale + 0.02)
+    assert torch.equal(out.argmax(-1)[sure], ref.argmax(-1)[sure])
+
+
 def test_command_line_generate_and_random(tmp_path):
     """`python -m dispec_b200 random` writes a folder that `generate` serves; greedy output equals
     the plain implementation's."""
