@@ -355,19 +355,26 @@ def test_captured_decode_steps_follow_the_context_into_the_next_class(tmp_path):
     assert (results[1] - ref).abs().max().item() < 0.03 * scale + 0.02
 
 
-def test_recorded_layer_sizes_bfloat16_against_the_32_bit_path():
-    """Three layers of the Qwen2.5-1.5B sizes (width 1536, 12 heads over 2 KV heads of 128, feed-forward
-    8960, vocabulary 151936, tied head), random weights: a 700-token prompt in two portions and six
-    decoded tokens (captured steps in bfloat16), the serving kernels against the true 32-bit path."""
+@pytest.mark.parametrize("sizes", [
+    # the layer sizes of Qwen2.5-1.5B, 7B and 14B (groups of 6, 7 and 5 heads per KV head)
+    dict(num_hidden_layers=3, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+         intermediate_size=8960, vocab_size=151936, rms_norm_eps=1e-6, tie_word_embeddings=True),
+    dict(num_hidden_layers=2, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+         intermediate_size=18944, vocab_size=152064, rms_norm_eps=1e-6, tie_word_embeddings=False),
+    dict(num_hidden_layers=2, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+         intermediate_size=13824, vocab_size=152064, rms_norm_eps=1e-5, tie_word_embeddings=False),
+], ids=["1.5b", "7b", "14b"])
+def test_recorded_layer_sizes_bfloat16_against_the_32_bit_path(sizes):
+    """A few layers of the family's real sizes, random weights: a 700-token prompt in two portions
+    and six decoded tokens (captured steps in bfloat16), the serving kernels against the true
+    32-bit path."""
     from dispec_b200 import load_model_config
     from dispec_b200.engine import ModelRunner, SeqEntry
     from dispec_b200.weights import load_random_model
     cfg = load_model_config(dict(
-        architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=3, hidden_size=1536,
-        num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936,
-        rope_theta=1000000.0, rms_norm_eps=1e-6, hidden_act="silu", tie_word_embeddings=True,
-        max_position_embeddings=4096, use_sliding_window=False))
-    ids = ru.random_ids(706, 151936, 5)
+        architectures=["Qwen2ForCausalLM"], model_type="qwen2", head_dim=128, rope_theta=1000000.0,
+        hidden_act="silu", max_position_embeddings=4096, use_sliding_window=False, **sizes))
+    ids = ru.random_ids(706, sizes["vocab_size"], 5)
     got = {}
     for dtype in ("float32", "bfloat16"):
         model = load_random_model(cfg, 2, 0.02, dtype, "cuda:0")
