@@ -198,12 +198,13 @@ def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
     return ms, launches, mean_ctx
 
 
-def decode_e2e(model, prompts, steps, warmup, num_blocks):
+def decode_e2e(model, prompts, steps, warmup, num_blocks, max_model_len=None):
     """Through the public entry point: host token ids in, host token ids out."""
     import torch
     from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
     engine = ContinuousBatchingEngine(model, KVConfig(block_size=PAGE_SIZE), num_blocks=num_blocks,
-                                      max_batch_tokens=8192, max_num_seqs=max(len(prompts), 8))
+                                      max_batch_tokens=8192, max_num_seqs=max(len(prompts), 8),
+                                      max_model_len=max_model_len)
     for p in prompts:
         engine.add_request(p, warmup + steps + 8, SamplingParams(0.0))
     while engine.waiting or engine.prefilling:
@@ -263,7 +264,11 @@ def run_ours(args) -> dict:
     pages_per_req = (prompt_len + NEW_TOKENS + args.steps + args.warmup + PAGE_SIZE) // PAGE_SIZE + 1
     vocab = cfg_dict["vocab_size"]
 
-    def runner_for(batch, per_req=pages_per_req, max_len=None):
+    # more steps than the recorded context length has room for: the engine's limit is raised (and said)
+    longest = prompt_len + args.steps + args.warmup + 64
+    over = longest if longest > cfg_dict["max_position_embeddings"] else None
+
+    def runner_for(batch, per_req=pages_per_req, max_len=over):
         return ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(batch * per_req, 160),
                            max_num_seqs=max(batch, 8), cuda_graph=True, max_model_len=max_len)
 
@@ -271,7 +276,7 @@ def run_ours(args) -> dict:
         from dispec_b200.ops import attention
         attention.MAX_OUTER = args.max_key_ranges
     if args.only == "decode":
-        r = runner_for(args.batch, max_len=2 * args.context if args.context else None)
+        r = runner_for(args.batch, max_len=2 * args.context + args.steps + args.warmup if args.context else over)
         ms, launches, ctx = decode_direct(r, random_prompts(args.batch, prompt_len, vocab, 11), args.steps, args.warmup)
         step_bytes = weight_bytes + args.batch * ctx * kv_per_token
         return {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
@@ -297,7 +302,7 @@ def run_ours(args) -> dict:
     pflops = prefill_flops(PREFILL_TOKENS)
     del runner
     torch.cuda.empty_cache()
-    e2e_value, e2e_ms, h2d, d2h = decode_e2e(model, prompts, args.steps, args.warmup, BATCH * pages_per_req + 64)
+    e2e_value, e2e_ms, h2d, d2h = decode_e2e(model, prompts, args.steps, args.warmup, BATCH * pages_per_req + 64, over)
     points = {}
     for b in (1, 64):
         r = runner_for(b)
@@ -325,7 +330,7 @@ def run_ours(args) -> dict:
             "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
             "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
             "intermediate": cfg_dict["intermediate_size"], "vocab": vocab, "tied": cfg_dict["tie_word_embeddings"],
-            "global_batch": BATCH, "seq_len": PROMPT_LEN, "context_len": CONTEXT_LEN,
+            "global_batch": BATCH, "seq_len": PROMPT_LEN, "context_len": max(CONTEXT_LEN, over or 0),
             "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
             "weights": f"random N(0,{STD}) seed {seed}",
             "l2": "no flush: each step reads %.2f GB of weights, above the 126 MB L2" % (weight_bytes / 1e9),
