@@ -273,8 +273,8 @@ def run_ours(args) -> dict:
                            max_num_seqs=max(batch, 8), cuda_graph=True, max_model_len=max_len)
 
     if args.max_key_ranges:
-        from dispec_b200.ops import attention
-        attention.MAX_OUTER = args.max_key_ranges
+        from dispec_b200.ops import tuning
+        tuning.MAX_OUTER = args.max_key_ranges
     if args.only == "decode":
         r = runner_for(args.batch, max_len=2 * args.context + args.steps + args.warmup if args.context else over)
         ms, launches, ctx = decode_direct(r, random_prompts(args.batch, prompt_len, vocab, 11), args.steps, args.warmup)

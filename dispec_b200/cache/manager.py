@@ -24,16 +24,33 @@ class OutOfSlotsError(RuntimeError):
 
 
 @dataclass(frozen=True)
+class CacheTensor:
+    """One named tensor a mixer keeps per token: ``num_heads`` rows of ``width`` elements."""
+    name: str
+    num_heads: int
+    width: int
+
+
+def key_value_tensors(num_kv_heads: int, head_dim: int) -> tuple:
+    """The two tensors of ordinary attention: a key and a value of equal shape."""
+    return (CacheTensor("key", num_kv_heads, head_dim), CacheTensor("value", num_kv_heads, head_dim))
+
+
+@dataclass(frozen=True)
 class CacheGroupSpec:
-    """One group of layer caches with identical needs."""
-    num_kv_heads: int
-    head_dim: int
-    window: int = 0  # 0: all keys stay
+    """One group of layer caches with identical needs: the tensors every token leaves in a
+    layer cache (each with its own heads and width), the window, and how many layer caches."""
+    tensors: tuple  # of CacheTensor
+    window: int = 0  # 0: all tokens stay
     num_slots: int = 1  # layer caches in the group
 
+    @classmethod
+    def key_value(cls, num_kv_heads: int, head_dim: int, window: int = 0, num_slots: int = 1):
+        return cls(key_value_tensors(num_kv_heads, head_dim), window, num_slots)
+
     def page_elements(self, page_size: int) -> int:
-        """Elements (keys and values) of one page across the group's layer caches."""
-        return 2 * self.num_slots * self.num_kv_heads * page_size * self.head_dim
+        """Elements of one page across the group's layer caches and tensors."""
+        return self.num_slots * page_size * sum(t.num_heads * t.width for t in self.tensors)
 
 
 @dataclass
@@ -102,10 +119,22 @@ class CacheManager:
         return cap if cap is not None else 1 << 62
 
     def window_quota(self, group: int, max_total_len: int, max_chunk: int) -> int:
-        """Most pages a request ever holds at once in a window group."""
+        """Most pages a request ever holds at once in a window group: a step of ``max_chunk``
+        tokens needs the window - 1 positions before it and its own, which touch at most one page
+        more than they fill; never more than the pages of the ``max_total_len`` positions the
+        request ever stores."""
         w = self.groups[group].window
         bound = (w - 1 + max(1, max_chunk) + self.page_size - 1) // self.page_size + 1
         return min(bound, self.pages_for(max_total_len))
+
+    def largest_chunk(self) -> int:
+        """The largest portion of a prompt that one step may bring so that every window group's
+        quota (``window_quota``) still fits its pool; unbounded without window groups."""
+        cap = 1 << 62
+        for spec, pool in zip(self.groups, self.pools):
+            if spec.window > 0:
+                cap = min(cap, (pool.num_pages - 1) * self.page_size - spec.window + 1)
+        return cap
 
     # ---------------------------------------------------------------------- lifecycle
     def admission_need(self, prompt_len: int, max_total_len: int, max_chunk: int) -> list[int]:

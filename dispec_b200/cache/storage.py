@@ -1,9 +1,11 @@
-"""Device memory behind the cache manager: one key/value pool per cache group and one
-buffer per kind of fixed-size per-request state.
+"""Device memory behind the cache manager: per cache group one pool for each tensor the
+group's mixers keep per token (a key and a value for ordinary attention; any other named
+tensors, each with its own heads and width, for another mixer), and one buffer per kind of
+fixed-size per-request state.
 
-Pool layout: ``[layer cache, K|V, page, kv head, offset in page, head_dim]``, so that the
-``page_size x head_dim`` tile of one head of one page is contiguous (one 4 KB box at
-page 16, head 128, bfloat16).  The reference keeps ``[layer, slot, kv head, head_dim]``
+Pool layout: ``[layer cache, page, head, offset in page, width]``, so that the
+``page_size x width`` tile of one head of one page is contiguous (one 4 KB box at page 16,
+head size 128, bfloat16).  The reference keeps ``[layer, slot, kv head, head_dim]``
 (puneethgv/DiSpec dispec/kv/paged_cache.py:39-41).
 """
 from __future__ import annotations
@@ -18,28 +20,29 @@ class CacheStorage:
                  dtype: torch.dtype, device, poison: bool = False):
         self.page_size = page_size
         self.dtype = dtype
-        self.pools: list[torch.Tensor] = []
+        self.pools: list[dict[str, torch.Tensor]] = []  # per group: tensor name -> pool
         for spec, n in zip(groups, num_pages):
-            shape = (spec.num_slots, 2, n, spec.num_kv_heads, page_size, spec.head_dim)
-            pool = torch.empty(shape, dtype=dtype, device=device)
-            # the reference zero-fills (dispec/kv/paged_cache.py:39-41); NaN on request, so that a
-            # read of a never-written or stale slot shows in tests
-            pool.fill_(float("nan") if poison else 0.0)
-            self.pools.append(pool)
+            named = {}
+            for t in spec.tensors:
+                pool = torch.empty((spec.num_slots, n, t.num_heads, page_size, t.width), dtype=dtype, device=device)
+                # the reference zero-fills (dispec/kv/paged_cache.py:39-41); NaN on request, so that a
+                # read of a never-written or stale slot shows in tests
+                pool.fill_(float("nan") if poison else 0.0)
+                named[t.name] = pool
+            self.pools.append(named)
 
-    def key_pool(self, group: int, slot: int) -> torch.Tensor:
-        return self.pools[group][slot, 0]
-
-    def value_pool(self, group: int, slot: int) -> torch.Tensor:
-        return self.pools[group][slot, 1]
+    def layer_tensors(self, group: int, slot: int) -> dict:
+        """name -> ``[page, head, offset in page, width]`` of one layer cache."""
+        return {name: pool[slot] for name, pool in self.pools[group].items()}
 
     def poison_pages(self, group: int, pages: list[int]) -> None:
         if pages:
-            idx = torch.tensor(pages, device=self.pools[group].device, dtype=torch.long)
-            self.pools[group][:, :, idx] = float("nan")
+            for pool in self.pools[group].values():
+                idx = torch.tensor(pages, device=pool.device, dtype=torch.long)
+                pool[:, idx] = float("nan")
 
     def memory_bytes(self) -> int:
-        return sum(p.numel() * p.element_size() for p in self.pools)
+        return sum(p.numel() * p.element_size() for named in self.pools for p in named.values())
 
 
 class StateStorage:

@@ -32,6 +32,7 @@ CORE_SOURCES = [
     "attn_generic.cu",
     "attn_combine.cu",
     "sampling.cu",
+    "random_fill.cu",
 ]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -149,7 +150,7 @@ def specialised_library(name: str, source: str, defines: dict[str, int]) -> str:
 
 def build_all(head_dims=(16, 32, 64, 128)) -> list[str]:
     """Everything a first call could need, for the head sizes given."""
-    libs = [core_library(), skinny_library()]
+    libs = [core_library()]
     for d in head_dims:
         libs.append(attention_library(d))
         if d in (64, 128):
@@ -159,13 +160,6 @@ def build_all(head_dims=(16, 32, 64, 128)) -> list[str]:
 
 def attention_library(head_dim: int) -> str:
     return specialised_library(f"attn_mma_d{head_dim}", "attn_mma.cu", {"DSP_HEAD_DIM": head_dim})
-
-
-def skinny_library() -> str:
-    """The mma.sync product for few rows (an alternative to the streaming tcgen05 product, and the
-    one with an RMSNorm prologue): built when first asked for; its undefined runtime symbols
-    (error message, device error word) resolve against the core library, loaded before it."""
-    return _build("libdispec_b200_gemm_skinny", ["gemm_skinny.cu"], [])
 
 
 def prefill_attention_library(head_dim: int) -> str:

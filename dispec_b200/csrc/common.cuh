@@ -22,6 +22,7 @@ enum DspDeviceError {
 extern "C" const char* dsp_last_error();
 void dsp_set_error(const char* fmt, ...);
 int* dsp_device_error_ptr();  // device address of the error word (per current device)
+int dsp_num_sms();            // streaming multiprocessors of the current device (0 if unknown)
 
 #define DSP_REQUIRE(cond, ...)  \
   do {                          \

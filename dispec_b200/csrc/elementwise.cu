@@ -286,7 +286,8 @@ extern "C" int dsp_swiglu(const void* gate_up, void* out, int T, int inter, int 
   if (inter % N == 0 && (block == 0 || block % N == 0) && ((uintptr_t)gate_up % 16) == 0 &&
       ((uintptr_t)out % 16) == 0) {
     const size_t total = (size_t)T * (inter / N);
-    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    const size_t cap = (size_t)(dsp_num_sms() > 0 ? dsp_num_sms() : 1) * 16;  // grid-stride loop beyond that
+    const int blocks = (int)((total + 255) / 256 > cap ? cap : (total + 255) / 256);
     if (dtype == DSP_F32)
       launch_pdl(swiglu_vec_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, inter, total, block);
     else

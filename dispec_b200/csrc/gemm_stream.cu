@@ -427,10 +427,14 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, in
 }  // namespace
 
 // epilogue: 0 plain (bias, residual allowed); 1 SwiGLU over W rows alternating in blocks of 16
-// (C is [M, N/2]; no bias, no residual).  target_ctas: SMs the launch may fill by splitting K.
+// (C is [M, N/2]; no bias, no residual).  target_ctas: resident CTA slots the launch may fill by
+// splitting K (0: one per SM).  late_trigger_bytes: a product that streams at least this many bytes
+// of W lets the next kernel start only when its own last tile is on its way (what the next kernels
+// request before their wait would otherwise compete with a long stream); shorter products let it
+// start at once; 0 or less: always at once.
 extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const void* bias, const void* residual,
                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int target_ctas,
-                               int epilogue, cudaStream_t stream) {
+                               int epilogue, long late_trigger_bytes, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   DSP_REQUIRE(M <= 64, "dsp_gemm_stream: M=%d above 64 rows", M);
   DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_stream: K=%d and the row stride must be multiples of 8", K);
@@ -470,11 +474,7 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   a.K = K;
   a.kb_per_split = kb_per_split;
   a.epilogue = epilogue;
-  // A long stream (gate/up, down, the output head) lets the next kernel start only when its own
-  // last tile is on its way: what the next kernels request before their wait (weight rings, key
-  // tiles) would otherwise compete with this stream.  Short products let it start at once.
-  // Measured on the captured decode step of the 1.5B shape: 1.334 ms -> 1.312 ms.
-  a.late_trigger = (long)kb_total * n_blocks >= 1000 ? 1 : 0;
+  a.late_trigger = (late_trigger_bytes > 0 && (long)N * K * 2 >= late_trigger_bytes) ? 1 : 0;
   if (out_dtype == DSP_BF16) {
     if (nb_rows == 16) return launch<16, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
     if (nb_rows == 32) return launch<32, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);

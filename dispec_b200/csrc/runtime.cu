@@ -30,6 +30,18 @@ int* dsp_device_error_ptr() {
   return cached[dev];
 }
 
+int dsp_num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // Reads and clears the device error word (synchronises the device).
 extern "C" int dsp_device_error() {
   int v = 0;

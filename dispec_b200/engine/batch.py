@@ -29,14 +29,21 @@ class SeqEntry:
 
 @dataclass
 class LayerCacheView:
-    key_pool: torch.Tensor  # [num_pages, KVH, page_size, D]
-    value_pool: torch.Tensor
+    tensors: dict  # name -> [num_pages, heads, page_size, width]: what the mixer keeps per token
     page_table: torch.Tensor  # [S, max_pages] int32, -1 where a page was given back
     group: int
     write: bool
     page_size: int
     num_pages: int
     window: int
+
+    @property
+    def key_pool(self) -> torch.Tensor:
+        return self.tensors["key"]
+
+    @property
+    def value_pool(self) -> torch.Tensor:
+        return self.tensors["value"]
 
 
 @dataclass
@@ -84,9 +91,10 @@ class StepContext:
 
     def cache_view(self, placement, write: bool) -> LayerCacheView:
         g = placement.group
-        pool = self.storage.pools[g]
-        return LayerCacheView(pool[placement.slot, 0], pool[placement.slot, 1], self.page_tables[g],
-                              g, write, self.page_size, pool.shape[2], self.cache_groups[g].window)
+        tensors = self.storage.layer_tensors(g, placement.slot)
+        num_pages = next(iter(tensors.values())).shape[0]
+        return LayerCacheView(tensors, self.page_tables[g], g, write, self.page_size, num_pages,
+                              self.cache_groups[g].window)
 
     def state_view(self, index: int) -> LayerStateView:
         return LayerStateView(self.states.buffers[index], self.state_slot)

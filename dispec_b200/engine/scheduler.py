@@ -97,6 +97,10 @@ class Scheduler:
         self.cache = cache
         self.max_batch_tokens = max_batch_tokens
         self.chunk_size = chunk_size or max_batch_tokens
+        # the largest portion a step brings: the caller's, the budget, and what the window groups'
+        # pools can hold beside the window (so that a request that was admitted once, and comes
+        # back after a preemption with a longer prompt, can always be admitted again)
+        self.max_portion = min(self.chunk_size, max_batch_tokens, cache.largest_chunk())
         self.max_model_len = max_model_len
         self.waiting: list[Request] = []
         self.prefilling: list[Request] = []
@@ -126,11 +130,27 @@ class Scheduler:
         if self.max_model_len is not None and total - 1 > self.max_model_len:
             raise ValueError(f"request of {len(prompt)} + {max_new_tokens} tokens exceeds the longest "
                              f"sequence the engine serves ({self.max_model_len})")
+        # admission asks every cache group for pages (the prompt's in a full group, the most the
+        # request ever holds at once in a window group): a request whose need exceeds a whole pool
+        # would wait forever at the head of the queue
+        if self.max_portion < 1:
+            raise ValueError("a window group's pool is too small to hold its window and one more token")
+        need = self.cache.admission_need(*self._admission_args(len(prompt), max_new_tokens))
+        for g, (n, pool) in enumerate(zip(need, self.cache.pools)):
+            if n > pool.num_pages:
+                raise ValueError(f"request of {len(prompt)} + {max_new_tokens} tokens needs {n} pages of cache "
+                                 f"group {g} at once, the pool has {pool.num_pages}")
         params = params or SamplingParams()
         req = Request(next(self._ids), prompt, params, max_new_tokens, eos_id, priority=priority,
                       rng=make_rng(params))
         self.waiting.append(req)
         return req.id
+
+    def _admission_args(self, feed_len: int, remaining_new: int) -> tuple:
+        """(prompt length, positions ever stored, largest portion) of a request that enters with
+        ``feed_len`` tokens to store and ``remaining_new`` tokens to emit; the last emitted token
+        is never stored."""
+        return (feed_len, feed_len + remaining_new - 1, max(1, min(self.max_portion, feed_len)))
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.prefilling or self.running)
@@ -209,15 +229,14 @@ class Scheduler:
                 break
             feed = req.feed
             if req.state == State.WAITING:
-                remaining_new = req.max_new_tokens - len(req.output_ids)
-                args = (len(feed), len(feed) + remaining_new, min(self.chunk_size, self.max_batch_tokens))
+                args = self._admission_args(len(feed), req.max_new_tokens - len(req.output_ids))
                 if not self.cache.can_admit(*args):
                     break
                 self._on_admit(req.id, *args)
                 req.state = State.PREFILLING
                 self.waiting.remove(req)
                 self.prefilling.append(req)
-            chunk = min(len(feed) - req.prefill_pos, self.chunk_size, budget)
+            chunk = min(len(feed) - req.prefill_pos, self.max_portion, budget)
             try:
                 self.cache.extend(req.id, req.prefill_pos + chunk)
             except OutOfPagesError:
@@ -354,7 +373,14 @@ class ContinuousBatchingEngine:
             self.flush()
         plan = sched.schedule()
         if not plan.entries:
+            had_inflight = self._inflight is not None
             self.flush()
+            if not had_inflight and sched.has_work():
+                # nothing ran, nothing was in flight, and requests remain: no later step can differ
+                raise RuntimeError(
+                    f"the scheduler is stuck: {len(sched.waiting)} waiting, {len(sched.prefilling)} in "
+                    f"prefill, {len(sched.running)} running, and no step can be scheduled "
+                    f"(free pages per group: {[p.available for p in sched.cache.pools]})")
             return
         feed = self._inflight[1] if self._inflight is not None else None
         logits = self.runner.step(plan.entries, feed_tokens=feed)
@@ -394,8 +420,11 @@ class ContinuousBatchingEngine:
         return self.scheduler.has_work()
 
     def run_until_done(self, max_steps: int = 100_000) -> None:
+        """Steps until every request has finished; raises if ``max_steps`` do not suffice."""
         steps = 0
         while (self.scheduler.has_work() or self._inflight is not None) and steps < max_steps:
             self.step()
             steps += 1
         self.flush()
+        if self.scheduler.has_work():
+            raise RuntimeError(f"{max_steps} steps did not finish the requests")

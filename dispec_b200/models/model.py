@@ -10,7 +10,7 @@ import torch
 
 from dispec_b200.cache.manager import CacheGroupSpec
 from dispec_b200.models.spec import LayerCall, ModelSpec
-from dispec_b200.parts.base import KVNeed, Part, PartSpec, StateNeed
+from dispec_b200.parts.base import CacheNeed, Part, PartSpec, StateNeed
 from dispec_b200.registry import part_class
 
 
@@ -41,8 +41,6 @@ def build_part(spec: PartSpec, built: dict, bindings: list, prefix: str = "") ->
 
 
 class DecoderModel:
-    fuse_final_norm = False  # final norm inside the head's product: measured slower than two kernels
-
     def __init__(self, spec: ModelSpec, config=None):
         self.spec = spec
         self.config = config
@@ -61,7 +59,7 @@ class DecoderModel:
     # ------------------------------------------------------------------ cache planning
     def _plan_caches(self) -> None:
         """One layer cache per distinct cache label; caches with equal needs share a group."""
-        needs: dict[int, KVNeed] = {}
+        needs: dict[int, CacheNeed] = {}
         writers: dict[int, int] = {}
         self.state_needs: list[StateNeed] = []
         self.call_state: list[int | None] = []
@@ -90,7 +88,7 @@ class DecoderModel:
                 self.state_needs.append(sneed)
             else:
                 self.call_state.append(None)
-        group_keys: list[KVNeed] = []
+        group_keys: list[CacheNeed] = []
         members: list[list[int]] = []
         self.placement: dict[int, CachePlacement] = {}
         for label in sorted(needs):
@@ -101,7 +99,7 @@ class DecoderModel:
             g = group_keys.index(need)
             self.placement[label] = CachePlacement(g, len(members[g]))
             members[g].append(label)
-        self.cache_groups = [CacheGroupSpec(k.num_kv_heads, k.head_dim, k.window, len(m))
+        self.cache_groups = [CacheGroupSpec(tuple(k.tensors), k.window, len(m))
                              for k, m in zip(group_keys, members)]
         tiles: set = set()
         for c in self.schedule:
@@ -147,12 +145,6 @@ class DecoderModel:
 
     def logits(self, ctx, x, pending, rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits at the given flat token rows (int32 device tensor)."""
-        if (self.fuse_final_norm and pending is None and ctx.logit_rows_are_all
-                and hasattr(self.head, "forward_normed")
-                and hasattr(self.final_norm, "as_linear_prologue")):
-            out = self.head.forward_normed(ctx, x, self.final_norm)
-            if out is not None:
-                return out
         if pending is None:
             h = self.final_norm.forward(ctx, x, rows=rows)
         else:

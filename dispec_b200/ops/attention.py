@@ -6,10 +6,12 @@ import ctypes
 import torch
 
 from dispec_b200.ops import library as L
+from dispec_b200.ops import tuning
+from dispec_b200.ops.tuning import CLUSTER_MAX_SPLITS
 
 ROWS_PER_TILE = 64  # query rows (token, head-in-group pairs) one tensor-core tile holds
 PREFILL_ROWS_PER_TILE = 128  # rows of a tile of the tcgen05 kernel for portions of prompts
-PREFILL_BACKEND = "tcgen05"  # "mma": portions of prompts on the mma.sync kernel as well
+DECODE_KERNEL_MAX_GROUP = 16  # query heads per KV head the warp-parallel single-token kernel holds
 
 
 def tokens_per_tile(group_size: int) -> int | None:
@@ -26,7 +28,7 @@ def prefill_tokens_per_tile(group_size: int) -> int:
 
 def tcgen05_supported(head_dim: int, group_size: int, page_size: int, dtype: torch.dtype) -> bool:
     """The tcgen05 kernel is built for head sizes 64 and 128 and pages of 8 to 64 tokens."""
-    return (PREFILL_BACKEND == "tcgen05" and dtype == torch.bfloat16 and head_dim in (64, 128)
+    return (dtype == torch.bfloat16 and head_dim in (64, 128)
             and group_size <= ROWS_PER_TILE and page_size in (8, 16, 32, 64))
 
 
@@ -59,12 +61,6 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
 _MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
                3: "operands must be 16-byte aligned with strides in whole 16-byte pieces",
                4: "shared memory opt-in failed"}
-MAX_SPLITS = 32
-USE_CLUSTER_COMBINE = True
-USE_DECODE_KERNEL = True  # warp-parallel kernel for single tokens whose group fits 16 rows
-FUSE_DECODE_ROPE = True  # that kernel rotates q and the token's key itself and writes key and value to the cache
-DECODE_KERNEL_MAX_SPLITS = 8  # every split count the cluster merge allows
-TARGET_CTAS = 148 * 2
 _partials: dict = {}
 _retired: list = []
 _err_addr: dict = {}
@@ -106,31 +102,15 @@ def _device_error_address(device) -> int:
     return _err_addr[key]
 
 
-def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int) -> int:
-    """Key splits for single-token rows, so that the launch covers the SMs about twice."""
-    if num_decode_tiles <= 0:
-        return 1
-    # measured (12 heads over 2 KV heads, 1,100 keys): the best split count keeps the launch within
-    # two CTAs per SM: 8 at batch 8, 4 at 32, 2 at 64, 1 at 128
-    want = max(1, TARGET_CTAS // (num_decode_tiles * num_kv_heads))
-    limit = CLUSTER_MAX_SPLITS if USE_CLUSTER_COMBINE else MAX_SPLITS
-    return max(1, min(want, limit, -(-max_ctx // 256)))
+def choose_splits(num_decode_tiles: int, num_kv_heads: int, max_ctx: int, device=None) -> int:
+    """Key splits for single-token rows on this device (see ``tuning.choose_splits``)."""
+    return tuning.choose_splits(num_decode_tiles, num_kv_heads, max_ctx, tuning.attention_target_ctas(device))
 
 
-CLUSTER_MAX_SPLITS = 8  # splits that merge on chip (one thread-block cluster per tile)
-OUTER_MIN_KEYS = 256  # a CTA of a row cut into ranges still reads at least this many keys
-MAX_OUTER = 32
-
-
-def choose_outer(num_decode_tiles: int, num_kv_heads: int, max_ctx: int, splits: int) -> int:
-    """Key ranges per single-token row on top of the cluster's ``splits``: when a full cluster
-    per row and KV head still leaves SMs idle (few rows) and the context is long enough to share.
-    Measured (12 heads over 2 KV heads, head size 128): the best count brings the launch to about
-    256 CTAs (16 ranges at batch 1 and 32,768 keys, 2 at batch 8), as long as a CTA keeps 256 keys."""
-    if num_decode_tiles <= 0 or splits < CLUSTER_MAX_SPLITS or not USE_DECODE_KERNEL:
-        return 1
-    want = TARGET_CTAS // (num_decode_tiles * num_kv_heads * splits)
-    return max(1, min(want, MAX_OUTER, max_ctx // (splits * OUTER_MIN_KEYS)))
+def choose_outer(num_decode_tiles: int, num_kv_heads: int, max_ctx: int, splits: int, device=None) -> int:
+    """Key ranges per single-token row beyond the cluster (see ``tuning.choose_outer``)."""
+    return tuning.choose_outer(num_decode_tiles, num_kv_heads, max_ctx, splits,
+                               tuning.attention_target_ctas(device))
 
 
 def decode_rope_fusable(ctx, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
@@ -138,11 +118,9 @@ def decode_rope_fusable(ctx, num_heads: int, num_kv_heads: int, head_dim: int, r
     """Whether the single tokens of this step go through the kernel that rotates q and k itself
     (then the separate rotation kernel must skip them)."""
     group = num_heads // num_kv_heads
-    return (FUSE_DECODE_ROPE and USE_DECODE_KERNEL and USE_CLUSTER_COMBINE and ctx.num_decode_seqs > 0
-            and tensor_core_supported(head_dim, group, dtype) and group <= 16
-            and tokens_per_tile(group) in ctx.attention_tiles
-            and 0 < rotary_dim <= head_dim and rotary_dim % 16 == 0
-            and DECODE_KERNEL_MAX_SPLITS >= CLUSTER_MAX_SPLITS)
+    return (ctx.num_decode_seqs > 0 and tensor_core_supported(head_dim, group, dtype)
+            and group <= DECODE_KERNEL_MAX_GROUP and tokens_per_tile(group) in ctx.attention_tiles
+            and 0 < rotary_dim <= head_dim and rotary_dim % 16 == 0)
 
 
 def _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0,
@@ -184,7 +162,8 @@ _TCGEN05_ERRORS = {1: "launch failed", 2: "unsupported head/group counts or page
 
 def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                           tile_tok0, num_tiles, num_decode_tiles, out, H, KVH, D, window, scale,
-                          splits: int, prefill_tiles=None, fused_rope=None, outer: int = 1) -> torch.Tensor:
+                          splits: int, prefill_tiles=None, fused_rope=None, outer: int = 1,
+                          decode_kernel: bool | None = None) -> torch.Tensor:
     """Tensor-core attention over a tile list whose first ``num_decode_tiles`` tiles are single
     tokens (run with ``splits`` key splits and merged), the rest portions of prompts.  With
     ``prefill_tiles`` = (tile_seq, tile_tok0, num_tiles) of the 128-row tiling (single tokens
@@ -192,23 +171,27 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
     rotary_dim, write_kv): ``q`` are the fused q/k/v rows and the single tokens' rows are not
     rotated yet; their kernel rotates them and stores key and value (see ``decode_rope_fusable``).
     ``outer`` > 1 cuts each single token's keys into that many ranges, each run by a cluster of
-    ``splits`` CTAs; a second kernel merges the ranges (long contexts at small batches)."""
+    ``splits`` CTAs; a second kernel merges the ranges (long contexts at small batches).
+    ``decode_kernel``: whether single tokens take the warp-parallel kernel (default: whenever
+    the group of query heads per KV head fits it) or the tile kernel."""
     assert q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
     tpt = tokens_per_tile(H // KVH)
+    group = H // KVH
+    if decode_kernel is None:
+        decode_kernel = group <= DECODE_KERNEL_MAX_GROUP
+    decode_kernel = decode_kernel and group <= DECODE_KERNEL_MAX_GROUP
     if num_decode_tiles > 0:
-        if splits <= CLUSTER_MAX_SPLITS and USE_CLUSTER_COMBINE and (
-                (USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS) or splits > 1):
+        if splits <= CLUSTER_MAX_SPLITS and (decode_kernel or splits > 1):
             # single tokens: the cluster kernels (warp-parallel keys when the group fits 16 rows)
-            decode_only = USE_DECODE_KERNEL and H // KVH <= 16 and splits <= DECODE_KERNEL_MAX_SPLITS
-            if outer > 1 and not decode_only:
+            if outer > 1 and not decode_kernel:
                 outer = 1
             part_o = part_ml = None
             if outer > 1:
                 part_o, part_ml = _partial_buffers(q.device, num_decode_tiles * H, outer, D)
             _launch_mma(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq,
                         tile_tok0, 0, num_decode_tiles, out, part_o, part_ml, H, KVH, D, tpt, window,
-                        splits, scale, cluster_combine=splits > 1, decode_only=decode_only,
+                        splits, scale, cluster_combine=splits > 1, decode_only=decode_kernel,
                         fused_rope=fused_rope, outer=outer)
             if outer > 1:
                 L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out),
@@ -243,9 +226,11 @@ def paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, q_start, ctx_
 
 def paged_attention_tensor_core(q, q_stride, k_pool, v_pool, page_table, positions, seq_of_token, out,
                                 num_heads, num_kv_heads, head_dim, window, scale, q_lens, ctx_lens,
-                                splits=None) -> torch.Tensor:
+                                splits=None, decode_kernel=None, prefill_kernel=None) -> torch.Tensor:
     """Stand-alone form (tests, tools): builds the tile list for sequences given by their
-    ``q_lens`` and ``ctx_lens`` (single-token sequences must come first)."""
+    ``q_lens`` and ``ctx_lens`` (single-token sequences must come first).  ``prefill_kernel``
+    "mma" keeps portions of prompts on the mma.sync kernel where the tcgen05 kernel would take
+    them; ``decode_kernel`` False keeps single tokens on the tile kernel."""
     dev_ = q.device
     group = num_heads // num_kv_heads
     tpt = tokens_per_tile(group)
@@ -266,14 +251,14 @@ def paged_attention_tensor_core(q, q_stride, k_pool, v_pool, page_table, positio
         starts.append(starts[-1] + n)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev_)
     if splits is None:
-        splits = choose_splits(n_dec, num_kv_heads, max(ctx_lens))
+        splits = choose_splits(n_dec, num_kv_heads, max(ctx_lens), q.device)
     prefill_tiles = None
-    if tcgen05_supported(head_dim, group, k_pool.shape[2], q.dtype):
+    if prefill_kernel != "mma" and tcgen05_supported(head_dim, group, k_pool.shape[2], q.dtype):
         bs, b0, _ = tile_list(prefill_tokens_per_tile(group))
         prefill_tiles = (i32(bs), i32(b0), len(bs))
     return paged_attention_tiles(q, q_stride, k_pool, v_pool, page_table, i32(starts), i32(ctx_lens),
                                  i32(ts), i32(t0), len(ts), n_dec, out, num_heads, num_kv_heads,
-                                 head_dim, window, scale, splits, prefill_tiles)
+                                 head_dim, window, scale, splits, prefill_tiles, decode_kernel=decode_kernel)
 
 
 def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tensor, num_heads: int,
@@ -286,9 +271,9 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
     if tensor_core_supported(head_dim, group, q.dtype) and tpt in ctx.attention_tiles:
         tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
         splits = ctx.decode_splits if ctx.decode_splits else choose_splits(
-            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len)
+            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len, q.device)
         outer = ctx.decode_outer if ctx.decode_outer else choose_outer(
-            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len, splits)
+            ctx.num_decode_seqs, num_kv_heads, ctx.max_ctx_len, splits, q.device)
         prefill_tiles = None
         big = prefill_tokens_per_tile(group)
         if big in ctx.attention_tiles and tcgen05_supported(head_dim, group, cache.key_pool.shape[2], q.dtype):

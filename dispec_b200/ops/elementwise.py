@@ -102,3 +102,17 @@ def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
         L.ptr(qkv), L.ptr(positions), L.ptr(seq_of_token), L.ptr(page_table), page_table.stride(0),
         L.ptr(k_pool), L.ptr(v_pool), L.ptr(inv_freq), T, num_heads, num_kv_heads, head_dim,
         rotary_dim, page_size, num_pages, int(write_kv), L.dtype_code(qkv.dtype), L.stream_handle()))
+
+
+def fill_normal(out: torch.Tensor, seed: int, ordinal: int, std: float, mean: float = 0.0,
+                through_bf16: bool = False) -> torch.Tensor:
+    """out.flatten()[i] = mean + std * z(seed, ordinal, i): the counter-based normal numbers of
+    ``dispec_b200.weights.counter_rng`` (same bits), rounded once to out's type (float32 or
+    bfloat16).  ``through_bf16`` rounds to bfloat16 first even when out is float32."""
+    _cuda(out)
+    assert out.is_contiguous() and 0 <= ordinal < (1 << 32) and 0 <= seed < (1 << 64)
+    with torch.cuda.device(out.device):
+        L.check(L.core().dsp_fill_normal(L.ptr(out), L.i64(out.numel()), ctypes.c_ulonglong(seed),
+                                         ctypes.c_uint(ordinal), ctypes.c_float(mean), ctypes.c_float(std),
+                                         L.dtype_code(out.dtype), int(through_bf16), L.stream_handle()))
+    return out

@@ -43,16 +43,6 @@ def core() -> ctypes.CDLL:
     return _core
 
 
-def skinny() -> ctypes.CDLL:
-    """The mma.sync product for few rows, in a library of its own (built at first use)."""
-    if "gemm_skinny" not in _special:
-        core()
-        with _lock:
-            if "gemm_skinny" not in _special:
-                _special["gemm_skinny"] = ctypes.CDLL(build.skinny_library())
-    return _special["gemm_skinny"]
-
-
 def attention_library(head_dim: int) -> ctypes.CDLL:
     key = f"attn_mma_d{head_dim}"
     if key not in _special:

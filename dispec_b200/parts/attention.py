@@ -13,8 +13,7 @@ import torch
 
 from dispec_b200 import ops
 from dispec_b200.ops import attention as attn_ops
-from dispec_b200.ops import gemm as gemm_ops
-from dispec_b200.parts.base import KVNeed, Mixer, TensorSpec
+from dispec_b200.parts.base import CacheNeed, Mixer, TensorSpec
 from dispec_b200.registry import register_part
 
 
@@ -32,7 +31,9 @@ class GQAAttention(Mixer):
         self.qkv_bias = qkv_bias
         self.out_bias = out_bias
         self.window = window
-        self.scale = head_dim ** -0.5 if scale is None else scale
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        if not self.scale > 0.0:
+            raise ValueError(f"the attention scale must be positive, got {self.scale}")
         self.position_encoding = position_encoding
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
@@ -62,7 +63,7 @@ class GQAAttention(Mixer):
         self.b_o = tensors.get("o_proj.bias")
 
     def cache_need(self):
-        return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed.key_value(self.num_kv_heads, self.head_dim, self.window)
 
     def tokens_per_attention_tile(self):
         group = self.num_heads // self.num_kv_heads
@@ -71,31 +72,29 @@ class GQAAttention(Mixer):
             return (small, attn_ops.prefill_tokens_per_tile(group))  # portions of prompts: 128-row tiles
         return small
 
-    fuses_norm_and_residual = True
+    adds_residual = True
 
-    def forward(self, ctx, x, cache, state, pre_norm=None, residual=None):
-        """``pre_norm``: x is not normalised yet and this norm is applied on the way into the first
-        product.  ``residual``: added by the last product, so that the sum comes back."""
+    def forward(self, ctx, x, cache, state, residual=None):
+        """``residual``: added by the last product (32-bit sum, rounded once), so that the sum
+        comes back."""
         H, KVH, D = self.num_heads, self.num_kv_heads, self.head_dim
-        if pre_norm is not None:
-            gain, eps = pre_norm.as_linear_prologue()
-            qkv = gemm_ops.linear_rms_norm(x, gain, eps, self.w_qkv, self.b_qkv)
-        else:
-            qkv = ops.linear(x, self.w_qkv, self.b_qkv)
-        pe = self.position_encoding
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        rot = self.position_encoding.rotation()
+        inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
+        scale = self.scale * self.position_encoding.score_scale()
         # single tokens come first in the batch: when their attention kernel rotates q and k itself and
         # stores the new key and value, the rotation kernel runs on the portions of prompts only
         n_dec = ctx.num_decode_seqs
         fused = None
-        if attn_ops.decode_rope_fusable(ctx, H, KVH, D, pe.rotary_dim, qkv.dtype):
-            fused = (pe.inv_freq, pe.rotary_dim, cache.write)
+        if attn_ops.decode_rope_fusable(ctx, H, KVH, D, rotary_dim, qkv.dtype):
+            fused = (inv_freq, rotary_dim, cache.write)
         first = n_dec if fused else 0
         if qkv.shape[0] > first:
             ops.rope_kv_store(qkv[first:], ctx.positions[first:], ctx.seq_of_token[first:], cache.page_table,
                               cache.key_pool if cache.write else None,
                               cache.value_pool if cache.write else None,
-                              pe.inv_freq, H, KVH, D, pe.rotary_dim, write_kv=cache.write)
+                              inv_freq, H, KVH, D, rotary_dim, write_kv=cache.write)
         out = torch.empty((x.shape[0], H * D), dtype=x.dtype, device=x.device)
         attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
-                                 self.scale, fused_rope=fused)
+                                 scale, fused_rope=fused)
         return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual)

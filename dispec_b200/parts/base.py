@@ -11,10 +11,10 @@ Roles and their required methods:
 * ``Norm.forward(ctx, x, rows=None) -> y`` and
   ``Norm.forward_add(ctx, residual, delta) -> y`` (adds ``delta`` into ``residual`` in
   place in 32-bit, then normalises the sum).
-* ``PositionEncoding``: whatever its mixers consume; the rotary one exposes
-  ``inv_freq`` and ``rotary_dim`` for the q/k rotation kernel.
-* ``Mixer.forward(ctx, x, cache, state) -> y``; ``cache_need()`` says what kind of
-  key/value cache a call of this mixer needs (or None), ``state_need()`` what
+* ``PositionEncoding.rotation() -> Rotation(inv_freq, rotary_dim) | None`` and
+  ``PositionEncoding.score_scale() -> float``: what the attention mixer asks of it.
+* ``Mixer.forward(ctx, x, cache, state) -> y``; ``cache_need()`` says which named tensors
+  a call of this mixer keeps per token in the paged cache (or None), ``state_need()`` what
   fixed-size per-request state (or None).
 * ``FeedForward.forward(ctx, x) -> y``.
 * ``Block.forward(ctx, x, cache, state) -> x``: the arrangement of two norms, a mixer
@@ -26,6 +26,8 @@ from dataclasses import dataclass, field
 from typing import Any
 
 import torch
+
+from dispec_b200.cache.manager import CacheTensor, key_value_tensors  # noqa: F401  (CacheTensor re-exported)
 
 
 @dataclass(frozen=True)
@@ -53,12 +55,19 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
-class KVNeed:
-    """Key/value cache one mixer call needs. ``window`` 0: all keys stay; W > 0: only
-    the last W positions are ever read, older pages can be given back."""
-    num_kv_heads: int
-    head_dim: int
+class CacheNeed:
+    """What one mixer call keeps per token in the paged cache: a tuple of named tensors
+    (``CacheTensor(name, num_heads, width)``), each with its own heads and width.  Ordinary
+    attention keeps two of equal shape, "key" and "value" (``CacheNeed.key_value``); a mixer
+    that caches one latent tensor, or keys and values of different widths, lists those instead
+    and finds them by name in ``LayerCacheView.tensors``.  ``window`` 0: every token stays;
+    W > 0: only the last W positions are ever read, older pages can be given back."""
+    tensors: tuple
     window: int = 0
+
+    @classmethod
+    def key_value(cls, num_kv_heads: int, head_dim: int, window: int = 0) -> "CacheNeed":
+        return cls(key_value_tensors(num_kv_heads, head_dim), window)
 
 
 @dataclass(frozen=True)
@@ -92,12 +101,31 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class Rotation:
+    """Rotation of query and key heads: the pair (i, i + rotary_dim/2) of every head is turned
+    by the angle position * inv_freq[i]; dimensions from ``rotary_dim`` on pass unchanged."""
+    inv_freq: Any  # float32 [rotary_dim / 2] on the device
+    rotary_dim: int
+
+
 class PositionEncoding(Part):
-    pass
+    """What a mixer asks of its position encoding.  ``rotation()``: how it turns queries and
+    keys before the scores (None: not at all).  ``score_scale()``: a factor the encoding puts on
+    the attention scores beside the mixer's own scale.  ``prepare(device)`` (optional) builds
+    device tables once the weights are loaded.  An encoding of another kind (an offset added to
+    the stream, a bias on the scores) adds a method of its own and is consumed by a mixer that
+    knows that method; the built-in attention mixer uses the two below."""
+
+    def rotation(self) -> Rotation | None:
+        return None
+
+    def score_scale(self) -> float:
+        return 1.0
 
 
 class Mixer(Part):
-    def cache_need(self) -> KVNeed | None:
+    def cache_need(self) -> CacheNeed | None:
         return None
 
     def state_need(self) -> StateNeed | None:

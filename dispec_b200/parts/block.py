@@ -20,32 +20,18 @@ class PreNormBlock(Block):
         self.ffn_norm = ffn_norm
         self.feed_forward = feed_forward
 
-    # RMSNorm applied inside the first product of the mixer / feed-forward (few rows only).
-    # Off: measured slower than a norm kernel of its own followed by the plain product.
-    fuse_norm_into_linear = False
-
     def _takes_residual(self) -> bool:
-        return (getattr(self.mixer, "fuses_norm_and_residual", False)
-                and getattr(self.feed_forward, "fuses_norm_and_residual", False))
-
-    def _norm_fusable(self, x) -> bool:
-        from dispec_b200.ops import gemm
-        return (self.fuse_norm_into_linear and gemm.fused_prologue_supported(x, x)
-                and hasattr(self.mixer_norm, "as_linear_prologue")
-                and hasattr(self.ffn_norm, "as_linear_prologue"))
+        return (getattr(self.mixer, "adds_residual", False)
+                and getattr(self.feed_forward, "adds_residual", False))
 
     def forward(self, ctx, x, pending, cache, state):
         if pending is None and self._takes_residual():
             # the sums into the residual stream happen in the epilogue of the last product of the
             # mixer and of the feed-forward (32-bit sum, rounded once)
-            if self._norm_fusable(x):
-                x = self.mixer.forward(ctx, x, cache, state, pre_norm=self.mixer_norm, residual=x)
-                x = self.feed_forward.forward(ctx, x, pre_norm=self.ffn_norm, residual=x)
-            else:
-                h = self.mixer_norm.forward(ctx, x)
-                x = self.mixer.forward(ctx, h, cache, state, residual=x)
-                h = self.ffn_norm.forward(ctx, x)
-                x = self.feed_forward.forward(ctx, h, residual=x)
+            h = self.mixer_norm.forward(ctx, x)
+            x = self.mixer.forward(ctx, h, cache, state, residual=x)
+            h = self.ffn_norm.forward(ctx, x)
+            x = self.feed_forward.forward(ctx, h, residual=x)
             return x, None
         if pending is None:
             h = self.mixer_norm.forward(ctx, x)

@@ -44,11 +44,3 @@ class LinearHead(Part):
 
     def forward(self, ctx, h):
         return ops.linear(h, self.weight, out_dtype=torch.float32)
-
-    def forward_normed(self, ctx, x, norm):
-        """Logits of every row of x with ``norm`` applied on the way in; None if not possible."""
-        from dispec_b200.ops import gemm
-        if not gemm.fused_prologue_supported(x, self.weight):
-            return None
-        gain, eps = norm.as_linear_prologue()
-        return gemm.linear_rms_norm(x, gain, eps, self.weight, out_dtype=torch.float32)

@@ -22,10 +22,6 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = tensors["weight"]
 
-    def as_linear_prologue(self):
-        """(gain, eps) for kernels that apply this norm on their way in."""
-        return self.weight, self.eps
-
     def forward(self, ctx, x, rows=None):
         return ops.rms_norm(x, self.weight, self.eps, rows=rows)
 

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from dispec_b200.parts.base import PositionEncoding
+from dispec_b200.parts.base import PositionEncoding, Rotation
 from dispec_b200.registry import register_part
 
 
@@ -26,12 +26,12 @@ class RotaryEncoding(PositionEncoding):
         exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
         self.inv_freq = (1.0 / (self.theta ** exponent)).to(torch.float32).to(device)
 
+    def rotation(self):
+        if self.inv_freq is None:
+            raise RuntimeError("the rotary encoding was not prepared (load the model first)")
+        return Rotation(self.inv_freq, self.rotary_dim)
+
 
 @register_part("position_encoding", "none")
 class NoPositionEncoding(PositionEncoding):
-    """Keys and queries go to the scores as they are."""
-    rotary_dim = 0
-    inv_freq = None
-
-    def prepare(self, device):
-        pass
+    """Keys and queries go to the scores as they are (``rotation()`` is None)."""

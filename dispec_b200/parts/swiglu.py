@@ -36,19 +36,13 @@ class SwiGLUFeedForward(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
-    fuses_norm_and_residual = True
+    adds_residual = True
 
-    def forward(self, ctx, x, pre_norm=None, residual=None):
-        """``pre_norm``: x is not normalised yet, the norm is applied on the way into the first
-        product.  ``residual``: added by the last product, so that the sum comes back."""
-        norm = pre_norm.as_linear_prologue() if pre_norm is not None else None
-        if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up) and (
-                norm is None or x.shape[0] <= gemm_ops.FUSED_MAX_ROWS):
-            act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up, norm)
+    def forward(self, ctx, x, residual=None):
+        """``residual``: added by the last product (32-bit sum, rounded once), so that the sum
+        comes back."""
+        if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up):
+            act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up)
         else:
-            if norm is not None:
-                gate_up = gemm_ops.linear_rms_norm(x, norm[0], norm[1], self.w_gate_up)
-            else:
-                gate_up = ops.linear(x, self.w_gate_up)
-            act = ops.swiglu(gate_up, block=self.block)
+            act = ops.swiglu(ops.linear(x, self.w_gate_up), block=self.block)
         return ops.linear(act, self.w_down, residual=residual, out=residual)

@@ -6,7 +6,9 @@ import pytest
 
 from dispec_b200.engine import SeqEntry
 from dispec_b200.engine.runner import GRAPH_CONTEXT_CLASSES, ModelRunner
-from dispec_b200.ops import attention as A
+from dispec_b200.ops import tuning as A
+
+SLOTS = 2 * 148  # resident CTA slots of the device the plan is made for (two per SM)
 
 
 @pytest.mark.parametrize("rows", [1, 2, 3, 8, 31, 64, 256])
@@ -14,23 +16,23 @@ from dispec_b200.ops import attention as A
 def test_key_sharing_of_single_token_rows(rows, kv_heads):
     last = 0
     for ctx in (1, 100, 255, 256, 1100, 2048, 4096, 8192, 32768, 131072, 1 << 20):
-        splits = A.choose_splits(rows, kv_heads, ctx)
-        outer = A.choose_outer(rows, kv_heads, ctx, splits)
+        splits = A.choose_splits(rows, kv_heads, ctx, SLOTS)
+        outer = A.choose_outer(rows, kv_heads, ctx, splits, SLOTS)
         assert 1 <= splits <= A.CLUSTER_MAX_SPLITS and 1 <= outer <= A.MAX_OUTER
         if outer > 1:
             assert splits == A.CLUSTER_MAX_SPLITS  # ranges only on top of a full cluster
             assert ctx // (splits * outer) >= A.OUTER_MIN_KEYS  # and only while a CTA keeps enough keys
-            assert rows * kv_heads * splits * outer <= A.TARGET_CTAS
+            assert rows * kv_heads * splits * outer <= SLOTS
         assert splits * outer >= last  # a longer context is never shared among fewer CTAs
         last = splits * outer
-    assert A.choose_splits(0, kv_heads, 4096) == 1 and A.choose_outer(0, kv_heads, 4096, 8) == 1
+    assert A.choose_splits(0, kv_heads, 4096, SLOTS) == 1 and A.choose_outer(0, kv_heads, 4096, 8, SLOTS) == 1
 
 
 def test_key_ranges_fill_the_gpu_for_one_long_request():
-    splits = A.choose_splits(1, 2, 32768)
-    outer = A.choose_outer(1, 2, 32768, splits)
-    assert 2 * splits * outer >= 148  # at least one CTA per SM
-    assert A.choose_outer(64, 2, 32768, A.choose_splits(64, 2, 32768)) == 1  # many rows need none
+    splits = A.choose_splits(1, 2, 32768, SLOTS)
+    outer = A.choose_outer(1, 2, 32768, splits, SLOTS)
+    assert 2 * splits * outer >= SLOTS // 2  # at least one CTA per SM
+    assert A.choose_outer(64, 2, 32768, A.choose_splits(64, 2, 32768, SLOTS), SLOTS) == 1  # many rows need none
 
 
 @pytest.mark.parametrize("limit", [512, 2048, 5000, 40000, 1 << 21])

@@ -19,7 +19,7 @@ def test_pool_hands_out_the_highest_id_first_and_refuses_double_free():
 
 
 def test_pages_grow_only_when_full_and_return_on_free():
-    m = CacheManager([CacheGroupSpec(2, 16)], page_size=4, num_pages=8, max_num_seqs=2)
+    m = CacheManager([CacheGroupSpec.key_value(2, 16)], page_size=4, num_pages=8, max_num_seqs=2)
     m.admit("a")
     m.extend("a", 3)
     assert len(m.block_table("a")) == 1
@@ -37,7 +37,7 @@ def test_pages_grow_only_when_full_and_return_on_free():
 
 
 def test_extend_takes_nothing_when_it_cannot_take_all():
-    groups = [CacheGroupSpec(1, 8), CacheGroupSpec(1, 8, window=4)]
+    groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=4)]
     m = CacheManager(groups, page_size=2, num_pages=[10, 2], max_num_seqs=2)
     m.admit("a")
     with pytest.raises(OutOfPagesError):
@@ -47,7 +47,7 @@ def test_extend_takes_nothing_when_it_cannot_take_all():
 
 
 def test_window_group_gives_pages_back_as_the_window_passes_them():
-    groups = [CacheGroupSpec(1, 8), CacheGroupSpec(1, 8, window=5)]
+    groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=5)]
     m = CacheManager(groups, page_size=4, num_pages=[16, 4], max_num_seqs=2)
     m.admit("a")
     stored = 0
@@ -74,7 +74,7 @@ def test_window_group_gives_pages_back_as_the_window_passes_them():
 
 
 def test_reservation_guarantees_the_prompt_and_is_returned():
-    m = CacheManager([CacheGroupSpec(1, 8)], page_size=4, num_pages=6, max_num_seqs=4)
+    m = CacheManager([CacheGroupSpec.key_value(1, 8)], page_size=4, num_pages=6, max_num_seqs=4)
     assert m.can_admit(16, 20, 8)
     m.admit("a", 16, 20, 8)  # reserves 4 pages
     assert m.num_available_pages() == 2 and m.num_free_pages() == 6
@@ -95,7 +95,7 @@ def test_reservation_guarantees_the_prompt_and_is_returned():
 
 
 def test_state_slots_are_unique_and_run_out():
-    m = CacheManager([CacheGroupSpec(1, 8)], page_size=4, num_pages=4, max_num_seqs=2)
+    m = CacheManager([CacheGroupSpec.key_value(1, 8)], page_size=4, num_pages=4, max_num_seqs=2)
     a, b = m.admit("a"), m.admit("b")
     assert {a, b} == {0, 1}
     with pytest.raises(OutOfSlotsError):
@@ -109,7 +109,7 @@ def test_state_slots_are_unique_and_run_out():
 @pytest.mark.parametrize("seed", range(8))
 def test_random_orders_keep_every_invariant(seed):
     rng = random.Random(seed)
-    groups = [CacheGroupSpec(2, 16, 0, 3), CacheGroupSpec(2, 16, window=rng.choice([3, 8, 21]), num_slots=2)]
+    groups = [CacheGroupSpec.key_value(2, 16, 0, 3), CacheGroupSpec.key_value(2, 16, window=rng.choice([3, 8, 21]), num_slots=2)]
     page = rng.choice([2, 4, 8])
     m = CacheManager(groups, page_size=page, num_pages=[rng.randint(12, 40), rng.randint(8, 20)],
                      max_num_seqs=5)

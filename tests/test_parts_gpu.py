@@ -75,7 +75,8 @@ def test_rotary_part_matches_the_plain_tables():
     pos = torch.tensor([0, 1, 77, 4000])
     cos, sin = plain.rope_tables(pos, 48, 50000.0)
     ang = pos.float()[:, None] * pe.inv_freq.cpu()[None]
-    assert torch.equal(torch.cat([ang, ang], -1).cos(), cos) and pe.rotary_dim == 48
+    assert torch.equal(torch.cat([ang, ang], -1).cos(), cos)
+    assert pe.rotation().rotary_dim == 48 and pe.rotation().inv_freq is pe.inv_freq and pe.score_scale() == 1.0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -122,10 +123,10 @@ def test_attention_part_in_two_portions(dtype, window):
     specs = mixer.tensor_specs()
     cpu = {n: rnd(s.shape, 10 + i, 0.15).to(dtype) for i, (n, s) in enumerate(specs.items())}
     mixer.load({n: t.to(DEV) for n, t in cpu.items()})
-    assert mixer.cache_need().window == window
+    assert mixer.cache_need().window == window and [t.name for t in mixer.cache_need().tensors] == ["key", "value"]
     T = 29
     x = rnd((T, hidden), 40).to(dtype)
-    groups = [CacheGroupSpec(KVH, D, window, 1)]
+    groups = [CacheGroupSpec.key_value(KVH, D, window, 1)]
     tiles = _tile_sizes(mixer)
     from dispec_b200.models.model import CachePlacement
     out, harness, pos = [], None, 0
@@ -183,7 +184,7 @@ def test_pre_norm_block_alone(dtype):
     block = PreNormBlock(parts["n1"], parts["mixer"], parts["n2"], parts["ffn"])
     T = 23
     x = rnd((T, hidden), 300).to(dtype)
-    groups = [CacheGroupSpec(KVH, D, 0, 1)]
+    groups = [CacheGroupSpec.key_value(KVH, D, 0, 1)]
     out, harness, pos = [], None, 0
     for n in (9, 14):
         e = [SeqEntry("s", list(range(n)), pos, [])]
@@ -432,7 +433,7 @@ def register_routed_toy():
     from dispec_b200 import register_architecture, register_part
     from dispec_b200.config.model_config import ModelConfig
     from dispec_b200.models.spec import LayerCall, ModelSpec
-    from dispec_b200.parts.base import FeedForward, PartSpec, PositionEncoding, TensorSpec
+    from dispec_b200.parts.base import FeedForward, PartSpec, PositionEncoding, Rotation, TensorSpec
     from dispec_b200.registry import architectures
 
     if "ToyRoutedForCausalLM" in architectures():
@@ -473,7 +474,9 @@ def register_routed_toy():
 
     @register_part("position_encoding", "toy_slow_half_rotary")
     class SlowHalfRotary(PositionEncoding):
-        """Rotates the first half of each head with frequencies divided by ``factor``."""
+        """Rotates the first half of each head with frequencies divided by ``factor`` and puts a
+        factor of its own on the attention scores (``SCORE_SCALE``)."""
+        SCORE_SCALE = 1.3
 
         def __init__(self, head_dim, theta, factor):
             self.rotary_dim = head_dim // 2
@@ -483,6 +486,12 @@ def register_routed_toy():
         def prepare(self, device):
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
             self.inv_freq = (1.0 / (self.theta ** exponent) / self.factor).to(torch.float32).to(device)
+
+        def rotation(self):
+            return Rotation(self.inv_freq, self.rotary_dim)
+
+        def score_scale(self):
+            return self.SCORE_SCALE
 
     @dataclass(frozen=True)
     class RoutedConfig(ModelConfig):
@@ -566,7 +575,8 @@ def plain_routed(weights, cfg, ids):
             lo, hi, rest = t[..., :rot // 2], t[..., rot // 2:rot], t[..., rot:]
             return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin, rest], dim=-1)
 
-        o = plain.causal_attention(rotate(q), rotate(k), v)
+        # the toy encoding of the odd layers scales the scores by 1.3 (folded into q here)
+        o = plain.causal_attention(rotate(q) * (1.3 if odd else 1.0), rotate(k), v)
         x = x + o.reshape(T, -1) @ weights[p + "attn.o"].T
         h = plain.rms_norm(x, weights[p + "n2"], cfg["eps"])
         if odd:
@@ -595,7 +605,9 @@ def test_toy_routed_feed_forward_and_toy_position_encoding_in_alternate_layers(t
     weights = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
     model = load_model(str(tmp_path), "float32", DEV)
     assert [type(l.feed_forward).__name__ for l in model.layers] == ["SwiGLUFeedForward", "Top1Experts"] * 2
-    assert model.layers[1].mixer.position_encoding.rotary_dim == 8 and model.layers[0].mixer.position_encoding.rotary_dim == 16
+    assert model.layers[1].mixer.position_encoding.rotation().rotary_dim == 8
+    assert model.layers[0].mixer.position_encoding.rotation().rotary_dim == 16
+    assert model.layers[0].mixer.position_encoding.score_scale() == 1.0
     runner = ModelRunner(model, page_size=8, num_pages=16, max_num_seqs=2, poison=True)
     a, b = ru.random_ids(29, 77, 8), ru.random_ids(13, 77, 9)
     ref_a, ref_b = plain_routed(weights, cfg_dict, a), plain_routed(weights, cfg_dict, b)
@@ -611,3 +623,163 @@ def test_toy_routed_feed_forward_and_toy_position_encoding_in_alternate_layers(t
     scale = max(1.0, ref_a.abs().max().item())
     assert (torch.cat(got_a).cpu() - ref_a).abs().max().item() < 2e-4 * scale
     assert (torch.cat(got_b).cpu() - ref_b).abs().max().item() < 2e-4 * scale
+
+
+# ----------------------------------------- a mixer that caches one tensor of a width of its own
+
+def register_latent_toy():
+    """A toy mixer that keeps ONE tensor per token in the paged cache (a latent of a width that is
+    neither a head size nor a multiple of 16) and attends over it: it is key and value at once.
+    Registered from here; the package's cache planning, page pools, block tables and step function
+    serve it as they are."""
+    from dispec_b200 import register_architecture, register_part
+    from dispec_b200.config.model_config import ModelConfig
+    from dispec_b200.models.spec import ModelSpec
+    from dispec_b200.parts.base import CacheNeed, CacheTensor, Mixer, PartSpec, TensorSpec
+    from dispec_b200.registry import architectures
+
+    if "ToyLatentForCausalLM" in architectures():
+        return
+
+    @register_part("mixer", "toy_latent_attention")
+    class LatentAttention(Mixer):
+        """c_t = h_t Wc^T (cached); s_tj = (h_t Wq^T) . c_j / sqrt(latent) for j <= t;
+        y_t = (sum_j softmax(s_t)_j c_j) Wo^T."""
+        graph_safe = False  # walks the sequences of the step on the host
+
+        def __init__(self, hidden_size, latent_size):
+            self.h, self.l = hidden_size, latent_size
+
+        def tensor_specs(self):
+            return {"q.weight": TensorSpec((self.l, self.h)), "c.weight": TensorSpec((self.l, self.h)),
+                    "o.weight": TensorSpec((self.h, self.l))}
+
+        def load(self, tensors):
+            self.wq, self.wc, self.wo = tensors["q.weight"], tensors["c.weight"], tensors["o.weight"]
+
+        def cache_need(self):
+            return CacheNeed((CacheTensor("latent", 1, self.l),), window=0)
+
+        def forward(self, ctx, x, cache, state):
+            assert set(cache.tensors) == {"latent"}
+            pool = cache.tensors["latent"]  # [pages, 1, page_size, latent]
+            assert pool.shape[1:] == (1, cache.page_size, self.l)
+            q = x.float() @ self.wq.float().T
+            c = (x.float() @ self.wc.float().T).to(pool.dtype)
+            pos, seq = ctx.positions.long(), ctx.seq_of_token.long()
+            page = cache.page_table[seq, pos // cache.page_size].long()
+            pool[page, 0, pos % cache.page_size] = c
+            out = torch.empty_like(q)
+            for s in range(ctx.num_seqs):
+                a, b, n = ctx.host_q_start[s], ctx.host_q_start[s + 1], ctx.host_ctx_len[s]
+                pages = cache.page_table[s, :(n + cache.page_size - 1) // cache.page_size].long()
+                keys = pool[pages, 0].reshape(-1, self.l)[:n].float()  # every stored latent of the request
+                scores = q[a:b] @ keys.T / self.l ** 0.5
+                first = n - (b - a)  # position of the portion's first token
+                hidden = torch.arange(n, device=x.device)[None, :] > (first + torch.arange(b - a, device=x.device))[:, None]
+                out[a:b] = torch.softmax(scores.masked_fill(hidden, float("-inf")), dim=-1) @ keys
+            return (out @ self.wo.float().T).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class LatentConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyLatentForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+        latent_size: int = 0
+        intermediate_size: int = 0
+        num_layers: int = 0
+        eps: float = 0.0
+        KEYS: ClassVar[tuple] = ("vocab_size", "hidden_size", "latent_size", "intermediate_size", "num_layers", "eps")
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(**{k: d[k] for k in cls.KEYS})
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in self.KEYS})
+
+    def build(cfg):
+        h = cfg.hidden_size
+        layers = []
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            norm = lambda n: PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": p + n})
+            mixer = PartSpec("mixer", "toy_latent_attention", {"hidden_size": h, "latent_size": cfg.latent_size},
+                             {f"{n}.weight": f"{p}mix.{n}" for n in "qco"})
+            ffn = PartSpec("feed_forward", "swiglu", {"hidden_size": h, "intermediate_size": cfg.intermediate_size},
+                           {f"{n}_proj.weight": p + "ffn." + n for n in ("gate", "up", "down")})
+            layers.append(PartSpec("block", "pre_norm", {"mixer_norm": norm("n1"), "mixer": mixer,
+                                                         "ffn_norm": norm("n2"), "feed_forward": ffn}))
+        return ModelSpec("ToyLatentForCausalLM",
+                         PartSpec("embedding", "token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                         layers,
+                         PartSpec("norm", "rms_norm", {"hidden_size": h, "eps": cfg.eps}, {"weight": "final"}),
+                         PartSpec("head", "linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                         vocab_size=cfg.vocab_size, max_position=4096)
+
+    register_architecture("ToyLatentForCausalLM", LatentConfig, build)
+
+
+def plain_latent(weights, cfg, ids, cache_dtype):
+    T, l = len(ids), cfg["latent_size"]
+    x = weights["emb"][torch.as_tensor(ids)]
+    visible = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
+    for i in range(cfg["num_layers"]):
+        p = f"layers.{i}."
+        h = plain.rms_norm(x, weights[p + "n1"], cfg["eps"])
+        q = h @ weights[p + "mix.q"].T
+        c = (h @ weights[p + "mix.c"].T).to(cache_dtype).float()
+        s = (q @ c.T / l ** 0.5).masked_fill(~visible, float("-inf"))
+        x = x + (torch.softmax(s, dim=-1) @ c) @ weights[p + "mix.o"].T
+        h = plain.rms_norm(x, weights[p + "n2"], cfg["eps"])
+        x = x + plain.swiglu_mlp(h, weights[p + "ffn.gate"], weights[p + "ffn.up"], weights[p + "ffn.down"])
+    return plain.rms_norm(x, weights["final"], cfg["eps"]) @ weights["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_that_caches_one_latent_tensor(tmp_path, dtype):
+    """The cache a mixer asks for is a list of named tensors, each with its own heads and width:
+    one latent of width 24 here instead of a key and a value.  Two requests, cut anywhere, with
+    so few pages that a finished request's pages are used again (freed pages hold NaN)."""
+    from safetensors.torch import load_file
+    from dispec_b200 import load_model, load_model_config, write_random_model
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    register_latent_toy()
+    cfg_dict = dict(architectures=["ToyLatentForCausalLM"], vocab_size=83, hidden_size=40, latent_size=24,
+                    intermediate_size=64, num_layers=2, eps=1e-5)
+    cfg = load_model_config(cfg_dict)
+    write_random_model(cfg, str(tmp_path), seed=11, std=0.2, dtype="bfloat16")
+    weights = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+    model = load_model(str(tmp_path), dtype, DEV)
+    group = model.cache_groups[0]
+    assert len(model.cache_groups) == 1 and group.num_slots == 2
+    assert [(t.name, t.num_heads, t.width) for t in group.tensors] == [("latent", 1, 24)]
+    assert group.page_elements(8) == 2 * 8 * 24
+    runner = ModelRunner(model, page_size=8, num_pages=6, max_num_seqs=2, poison=True)
+    assert set(runner.storage.pools[0]) == {"latent"} and runner.storage.pools[0]["latent"].shape == (2, 6, 1, 8, 24)
+    cache_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    a, b, c = ru.random_ids(27, 83, 1), ru.random_ids(13, 83, 2), ru.random_ids(19, 83, 3)
+    ref = {n: plain_latent(weights, cfg_dict, ids, cache_dtype) for n, ids in (("a", a), ("b", b), ("c", c))}
+    got = {"a": [], "b": [], "c": []}
+    runner.admit("a")
+    runner.admit("b")
+    got["a"].append(runner.step([SeqEntry("a", a[:10], 0, list(range(10)))]))
+    l = runner.step([SeqEntry("a", a[10:11], 10, [0]), SeqEntry("b", b[:9], 0, list(range(9)))])
+    got["a"].append(l[:1]); got["b"].append(l[1:])
+    l = runner.step([SeqEntry("b", b[9:10], 9, [0]), SeqEntry("a", a[11:], 11, list(range(16)))])
+    got["b"].append(l[:1]); got["a"].append(l[1:])
+    got["b"].append(runner.step([SeqEntry("b", b[10:], 10, list(range(3)))]))
+    runner.release("a")  # four pages go back, filled with NaN, and are handed to c
+    runner.admit("c")
+    got["c"].append(runner.step([SeqEntry("c", c[:17], 0, list(range(17)))]))
+    got["c"].append(runner.step([SeqEntry("c", c[17:], 17, [0, 1])]))
+    tol = 2e-4 if dtype == "float32" else 0.06
+    for name in got:
+        out = torch.cat(got[name]).cpu()
+        assert torch.isfinite(out).all()
+        scale = max(1.0, ref[name].abs().max().item())
+        assert (out - ref[name]).abs().max().item() < tol * scale, name
+    runner.release("b")
+    runner.release("c")
+    runner.cache.check()
+    assert runner.cache.num_free_pages(0) == 6

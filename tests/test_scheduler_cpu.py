@@ -11,7 +11,7 @@ VOCAB = 97
 
 
 def make(pages=64, page_size=4, budget=2048, chunk=None, slots=16, groups=None):
-    cache = CacheManager(groups or [CacheGroupSpec(1, 8)], page_size, pages, slots)
+    cache = CacheManager(groups or [CacheGroupSpec.key_value(1, 8)], page_size, pages, slots)
     return Scheduler(cache, max_batch_tokens=budget, chunk_size=chunk), cache
 
 
@@ -185,7 +185,7 @@ def test_many_requests_through_a_small_pool_all_finish_with_the_right_tokens():
 
 
 def test_window_group_requests_finish_under_their_promise():
-    groups = [CacheGroupSpec(1, 8), CacheGroupSpec(1, 8, window=6)]
+    groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=6)]
     sched, cache = make(pages=[40, 8], page_size=4, budget=16, chunk=8, slots=4, groups=groups)
     model = FakeModel()
     wire(sched, cache, model)
@@ -203,6 +203,66 @@ def test_a_request_that_can_never_fit_is_refused():
     sched.add_request(list(range(8)), 1)  # 8 stored positions fit exactly
     with pytest.raises(ValueError):
         sched.add_request([], 2)
+
+
+def test_window_pool_bounds_the_portions_and_a_pool_below_the_window_refuses():
+    """Admission asks a window group for the most pages the request ever holds at once, which
+    grows with the portion a step brings.  Portions are therefore capped by what the window
+    group's pool holds beside the window, so that no request waits forever at the head of the
+    queue (and blocks everything behind it); a pool that cannot even hold the window and one
+    token refuses every request when it is added."""
+    groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=5)]
+    sched, cache = make(pages=[20, 6], page_size=4, budget=32, slots=4, groups=groups)
+    # window 5, six pages of 4: a portion of up to (6 - 1) * 4 - 5 + 1 = 16 tokens, not the budget's 32
+    assert sched.max_portion == 16
+    model = FakeModel()
+    wire(sched, cache, model)
+    a = sched.add_request(list(range(24)), 9)
+    b = sched.add_request(list(range(10)), 15)
+    plan = sched.schedule()
+    assert [len(e.tokens) for e in plan.entries] == [16]  # and the window pool is promised to a alone
+    for r in sched.process(plan, model.step(plan, cache)):
+        model.forget(r.id)
+    run(sched, cache, model)
+    assert sched.collect_outputs()[a] == expected(range(24), 9)
+    assert sched.collect_outputs()[b] == expected(range(10), 15)
+    cache.check()
+    tiny, _ = make(pages=[20, 2], page_size=4, budget=32, slots=4, groups=groups)
+    with pytest.raises(ValueError, match="too small"):
+        tiny.add_request([1, 2, 3], 2)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_workloads_with_a_window_group_finish_or_are_refused(seed):
+    """Random pools, windows, budgets and requests over a full and a window group: every request
+    is either refused when added or finishes with the right tokens; no step with work left
+    schedules nothing; every page and promise comes back."""
+    import random
+    rng = random.Random(1000 + seed)
+    page_size = rng.choice([2, 4, 8])
+    window = rng.choice([3, 5, 9, 17, 40])
+    pages = [rng.randint(4, 24), rng.randint(3, 12)]
+    groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=window)]
+    budget = rng.choice([4, 16, 32, 64])
+    chunk = rng.choice([None, 3, 8, 20])
+    sched, cache = make(pages=pages, page_size=page_size, budget=budget, chunk=chunk, slots=4, groups=groups)
+    model = FakeModel()
+    wire(sched, cache, model)
+    accepted = {}
+    for _ in range(rng.randint(3, 10)):
+        prompt = [rng.randrange(VOCAB) for _ in range(rng.randint(1, 40))]
+        new = rng.randint(1, 30)
+        try:
+            accepted[sched.add_request(prompt, new, priority=rng.choice([0, 0, 1]))] = (prompt, new)
+        except ValueError:
+            pass
+    run(sched, cache, model)
+    out = sched.collect_outputs()
+    for rid, (prompt, new) in accepted.items():
+        assert out[rid] == expected(prompt, new), rid
+    cache.check()
+    for g, pool in enumerate(cache.pools):
+        assert pool.num_free == pool.num_pages and pool.reserved == 0, g
 
 
 # ------------------------------------------------------------------- overlapped steps
