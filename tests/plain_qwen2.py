@@ -158,9 +158,10 @@ def decoder_layer(x, w: dict, prefix: str, c: dict, cos, sin, window: int) -> to
                           w[m + "down_proj.weight"])
 
 
-def forward_logits(weights: dict, config: dict, token_ids, dtype=torch.float32) -> torch.Tensor:
-    """Logits (T, vocab) of one whole sequence starting at position 0.
-    dispec/engine/model_runner.py:188-231."""
+def forward_logits(weights: dict, config: dict, token_ids, dtype=torch.float32, rows=None) -> torch.Tensor:
+    """Logits (T, vocab) of one whole sequence starting at position 0; with ``rows`` (a list of
+    positions) only those rows, (len(rows), vocab), as the reference's ``logits(hidden, indices)``
+    does.  dispec/engine/model_runner.py:188-231."""
     c = read_config(config)
     w = {k: v.to(dtype) for k, v in weights.items()}
     ids = torch.as_tensor(token_ids, dtype=torch.long)
@@ -169,6 +170,8 @@ def forward_logits(weights: dict, config: dict, token_ids, dtype=torch.float32) 
     x = embed(w["model.embed_tokens.weight"], ids)
     for i in range(c["layers"]):
         x = decoder_layer(x, w, f"model.layers.{i}.", c, cos, sin, c["windows"][i])
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rms_norm(x, w["model.norm.weight"], c["eps"])
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
     return x @ head.T
@@ -279,3 +282,80 @@ def random_weights(config: dict, seed: int, std: float, head_std: float | None =
         out[name] = t
     return out
 
+
+
+# ------------------------------------------------ counter-based random weights (scalar restatement)
+
+def _philox4x32_10(counter, key):
+    """Philox-4x32 with ten rounds on Python integers (the published algorithm: two 32x32 -> 64
+    multiplications per round, the key bumped by the golden-ratio and sqrt(3) constants)."""
+    c0, c1, c2, c3 = counter
+    k0, k1 = key
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * c0, 0xCD9E8D57 * c2
+        c0, c1, c2, c3 = (p1 >> 32) ^ c1 ^ k0, p1 & 0xFFFFFFFF, (p0 >> 32) ^ c3 ^ k1, p0 & 0xFFFFFFFF
+        k0, k1 = (k0 + 0x9E3779B9) & 0xFFFFFFFF, (k1 + 0xBB67AE85) & 0xFFFFFFFF
+    return c0, c1, c2, c3
+
+
+def counter_normal_element(seed: int, ordinal: int, index: int):
+    """Element ``index`` of tensor ``ordinal`` under ``seed`` as the engine's random-weights mode
+    defines it, one element at a time with numpy float32 scalars (every operation rounded once):
+    Philox block index // 4, Box-Muller on words (0, 1) for elements 0 and 1 of the block and on
+    words (2, 3) for elements 2 and 3, uniforms = odd multiples of 2^-24 from the top 23 bits,
+    logarithm by the atanh series, sine and cosine by octant reduction and Taylor polynomials."""
+    import numpy as np
+    f = np.float32
+    block, lane = divmod(index, 4)
+    words = _philox4x32_10((block & 0xFFFFFFFF, block >> 32, ordinal, 0), (seed & 0xFFFFFFFF, seed >> 32))
+    w0, w1 = words[2 * (lane // 2)], words[2 * (lane // 2) + 1]
+    u = f(2 * (w0 >> 9) + 1) * f(5.96046448e-08)
+    bits = int(np.array(u, dtype=np.float32).view(np.uint32))
+    e = (bits >> 23) - 127
+    m = np.array((bits & 0x007FFFFF) | 0x3F800000, dtype=np.uint32).view(np.float32)[()]
+    if m > f(1.41421354):
+        m, e = m * f(0.5), e + 1
+    t = m - f(1.0)
+    s = t / (t + f(2.0))
+    z = s * s
+    p = z * f(0.222222224) + f(0.285714298)
+    p = z * p + f(0.400000006)
+    p = z * p + f(0.666666687)
+    p = z * p + f(2.0)
+    log_u = f(e) * f(0.693147182) + s * p
+    radius = np.sqrt(f(-2.0) * log_u)
+    n = 2 * (w1 >> 9) + 1
+    octant, r = n >> 21, n & 0x1FFFFF
+    if octant & 1:
+        r = 0x200000 - r
+    a = (f(r) * f(4.76837158e-07)) * f(0.785398185)
+    a2 = a * a
+    ps = a2 * f(2.75573188e-06) + f(-1.98412701e-04)
+    ps = a2 * ps + f(8.33333377e-03)
+    ps = a2 * ps + f(-0.166666672)
+    ps = a2 * ps + f(1.0)
+    sin_a = a * ps
+    pc = a2 * f(-2.75573188e-07) + f(2.48015876e-05)
+    pc = a2 * pc + f(-1.38888892e-03)
+    pc = a2 * pc + f(4.16666679e-02)
+    pc = a2 * pc + f(-0.5)
+    cos_a = a2 * pc + f(1.0)
+    sin_t, cos_t = {0: (sin_a, cos_a), 1: (cos_a, sin_a), 2: (cos_a, -sin_a), 3: (sin_a, -cos_a),
+                    4: (-sin_a, -cos_a), 5: (-cos_a, -sin_a), 6: (-cos_a, sin_a), 7: (-sin_a, cos_a)}[octant]
+    return radius * (cos_t if lane % 2 == 0 else sin_t)
+
+
+def counter_random_tensor(names, name: str, shape, seed: int, std: float, mean: float = 0.0,
+                          indices=None) -> torch.Tensor:
+    """Float32 values (before the rounding to the storage type) of tensor ``name`` of a checkpoint
+    whose tensor names are ``names``: ordinal = place of the name in sorted order; value =
+    mean + std * z.  ``indices``: flat element indices to compute (default: all)."""
+    import numpy as np
+    ordinal = sorted(names).index(name)
+    total = 1
+    for d in shape:
+        total *= d
+    idx = range(total) if indices is None else indices
+    vals = [np.float32(mean) + np.float32(std) * counter_normal_element(seed, ordinal, int(i)) for i in idx]
+    t = torch.tensor(np.array(vals, dtype=np.float32))
+    return t.reshape(shape) if indices is None else t

@@ -79,22 +79,26 @@ def random_ids(n, vocab, seed):
 
 
 class Trace:
-    """Accumulates steps; remembers which (request, position) each written row belongs to."""
+    """Accumulates steps; remembers which (request, position) each written row belongs to.
+    ``want(request id, position) -> bool`` says which positions' logits are asked for
+    (default: all)."""
 
-    def __init__(self):
+    def __init__(self, want=None):
         self.steps = []
         self.rows = {}  # step -> list of (request, position)
         self._stored = {}
+        self._want = want or (lambda rid, pos: True)
 
     def step(self, entries, end=()):
-        """entries: list of (request id, tokens); every token's logits are wanted."""
+        """entries: list of (request id, tokens)."""
         n = len(self.steps)
         rec = {"step": n, "entries": [], "end": list(end)}
         rows = []
         for rid, tokens in entries:
             start = self._stored.get(rid, 0)
-            rec["entries"].append({"id": rid, "tokens": list(tokens), "want": list(range(len(tokens)))})
-            rows += [(rid, start + i) for i in range(len(tokens))]
+            want = [i for i in range(len(tokens)) if self._want(rid, start + i)]
+            rec["entries"].append({"id": rid, "tokens": list(tokens), "want": want})
+            rows += [(rid, start + i) for i in want]
             self._stored[rid] = start + len(tokens)
         for rid in end:
             self._stored.pop(rid, None)
@@ -106,12 +110,15 @@ class Trace:
         return dict(self._stored)
 
 
-def run_trace(model_dir, dtype, trace, max_tokens, out_dir, page_size=16, poison=True, timeout=600):
-    """Runs bin/trace_run on the trace; returns {(request, position): logits row}."""
+def run_trace(model_dir, dtype, trace, max_tokens, out_dir, page_size=16, poison=True, timeout=600,
+              cuda_graph=False):
+    """Runs bin/trace_run on the trace; returns {(step, request, position): logits row}."""
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
            "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
     if poison:
         cmd.append("--poison-freed-pages")
+    if cuda_graph:
+        cmd.append("--cuda-graph")
     text = "".join(json.dumps(s) + "\n" for s in trace.steps)
     proc = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
     if proc.returncode != 0:
@@ -129,18 +136,20 @@ def run_trace(model_dir, dtype, trace, max_tokens, out_dir, page_size=16, poison
     return out
 
 
-def build_four_mode_trace(prompts, page_size):
+def build_four_mode_trace(prompts, page_size, want=None):
     """One trace holding all four ways of running the same requests.
 
-    prompts: {name: token ids}.  Request ids are ``<mode>/<name>``.  Returns (trace, max live
-    tokens rounded as the program's --max-tokens wants them).
+    prompts: {name: token ids}.  Request ids are ``<mode>/<name>``.  ``want(name, position)``
+    limits the positions whose logits are asked for.  Returns (trace, max live tokens rounded as
+    the program's --max-tokens wants them).
     """
-    tr = Trace()
+    tr = Trace((lambda rid, pos: want(rid.split("/")[1], pos)) if want else None)
     peak = 0
+    unit = max(64, page_size)
 
     def note_peak():
         nonlocal peak
-        live = sum((n + 63) // 64 * 64 for n in tr.live_tokens().values())
+        live = sum((n + unit - 1) // unit * unit for n in tr.live_tokens().values())
         peak = max(peak, live)
 
     # 1. each request alone and whole
@@ -200,3 +209,43 @@ def build_four_mode_trace(prompts, page_size):
         note_peak()
         live = [it for it in live if it[0] not in ended]
     return tr, peak
+
+
+# A few layers of the real layer sizes (fewer layers are not a smaller configuration; smaller
+# layers would be): head size 128, groups of 6, 7 and 5 query heads per KV head, the real widths
+# and vocabularies, tied and untied heads.
+REAL_SHAPES = {
+    "1.5b": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=3,
+                             hidden_size=1536, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                             intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                             hidden_act="silu", tie_word_embeddings=True, max_position_embeddings=4096,
+                             use_sliding_window=False), seed=2, std=0.02, page_size=16),
+    "7b": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+                           hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                           intermediate_size=18944, vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                           hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=4096,
+                           use_sliding_window=False), seed=3, std=0.02, page_size=16),
+    "14b": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+                            hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                            intermediate_size=13824, vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-5,
+                            hidden_act="silu", tie_word_embeddings=False, max_position_embeddings=4096,
+                            use_sliding_window=False), seed=4, std=0.02, page_size=16),
+}
+
+
+def make_real_model_folder(folder, name, device="cuda:0"):
+    """A folder of a real layer size, its tensors filled on the device (the counter-based
+    generator gives the same bits on either side; the CPU would take minutes here).  Returns
+    (config dict, weights read back with the safetensors library as float32)."""
+    from safetensors.torch import load_file
+
+    from dispec_b200.config import load_model_config
+    from dispec_b200.weights import write_random_model
+
+    spec = REAL_SHAPES[name]
+    cfg = load_model_config(spec["config"])
+    write_random_model(cfg, folder, seed=spec["seed"], std=spec["std"], dtype="bfloat16", device=device)
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    weights = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    return config, weights

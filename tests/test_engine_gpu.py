@@ -49,6 +49,30 @@ def replay_sampling(weights, config, prompt, tokens, params):
     return out, margin
 
 
+def assert_tokens_within_margin(weights, config, prompt, tokens, params, rel=0.03, floor=0.02):
+    """Every token of a bfloat16 stream, teacher-forced: equal to the plain implementation's, or
+    the plain decision at that position is closer than bfloat16 can resolve (greedy: top-2 gap
+    below 2 * (rel * largest logit + floor); sampled: the uniform number lies within that mass of
+    an edge of the cumulative distribution)."""
+    rng = random.Random(params.seed)
+    ids = list(prompt)
+    for i, tok in enumerate(tokens):
+        logits = plain.forward_logits(weights, config, ids)[-1]
+        reach = 2 * (rel * logits.abs().max().item() + floor)
+        if params.temperature <= 0:
+            top2 = torch.topk(logits, 2).values
+            assert tok == int(logits.argmax()) or float(top2[0] - top2[1]) < reach, (i, tok)
+        else:
+            u = min(rng.random(), 1.0 - 2.0 ** -24)
+            probs = plain.sampling_distribution(logits, params.temperature, params.top_k, params.top_p)
+            want = plain.draw_inverse_cdf(probs, u)
+            cdf = probs.cumsum(-1)
+            # a logit error e moves cumulative masses by at most about e / T of the mass
+            edge = float((cdf - u * cdf[-1]).abs().min())
+            assert tok == want or edge < reach / max(params.temperature, 1e-3), (i, tok, want, edge)
+        ids.append(tok)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["a", "b"])
 def test_greedy_generation_through_llm_engine(folders, name, dtype):
@@ -107,8 +131,10 @@ def test_continuous_batching_chunked_mixed_greedy_and_temperature(folders, dtype
         if dtype == "float32":
             assert got == want or margin < 1e-5, (rid, got, want, margin)
         else:
-            agree = sum(g == w for g, w in zip(got, want))
-            assert agree >= 10, (rid, got, want)
+            # teacher-forced on the engine's own tokens, so every position is compared on its own:
+            # a token may differ only where the plain margin (top-2 gap, or the distance of the
+            # uniform number from an edge of the cumulative distribution) is within bfloat16's reach
+            assert_tokens_within_margin(weights, config, prompt, got, params)
     assert engine.runner.cache.num_free_pages() == 48
 
 
@@ -424,3 +450,126 @@ def test_command_line_generate_and_random(tmp_path):
         want, gaps = plain.greedy_generate(weights, config, prompt, 6)
         n = next((i for i, g in enumerate(gaps) if g < 1e-4), 6)
         assert ln["output_ids"][:n] == want[:n]
+
+
+# -------------------------------------------- anchored on the reference scheduler's own output
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_engine_streams_match_the_reference_scheduler(name, tmp_path):
+    """Greedy token streams that DiSpec's own ContinuousBatchingEngine produced on the CPU in
+    float32 (stored by tests/golden/make_golden.py: portions of 16 under a budget of 32 tokens, 24
+    pages) against this engine in float32 with the same settings and the same weights, token by
+    token up to the first position whose top-2 margin is below 1e-4."""
+    import json
+    import os
+    from test_plain_vs_golden import GOLDEN, streams_agree
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams, load_model
+    from dispec_b200.weights import write_safetensors
+    g = torch.load(os.path.join(GOLDEN, f"golden_{name}.pt"))
+    weights = plain.random_weights(g["config"], g["seed"], g["std"])
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(g["config"], f)
+    write_safetensors(str(tmp_path / "model.safetensors"), weights)
+    st = g["streams"]
+    page = 16 if name == "a" else 8
+    for overlap in (False, True):
+        engine = ContinuousBatchingEngine(load_model(str(tmp_path), "float32", "cuda:0"), KVConfig(block_size=page),
+                                          num_blocks=st["num_blocks"], max_batch_tokens=st["max_batch_tokens"],
+                                          chunk_size=st["chunk_size"], overlap=overlap)
+        ids = [engine.add_request(p, st["new_tokens"], SamplingParams(0.0)) for p in g["prompts"]]
+        engine.run_until_done()
+        out = engine.collect_outputs()
+        compared = 0
+        for rid, prompt, want in zip(ids, g["prompts"], st["tokens"]):
+            assert len(out[rid]) == len(want)
+            compared += streams_agree(weights, g["config"], prompt, out[rid], want)
+        assert compared >= 2 * len(ids)
+        if not overlap:
+            assert engine.num_steps == st["steps"]  # the same schedule as the reference's, step for step
+        assert engine.runner.cache.num_free_pages() == st["num_blocks"]
+
+
+# ------------------------------------- bfloat16, captured graphs, overlap and preemption together
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_bfloat16_graphs_and_overlap_under_page_pressure(folders, seed):
+    """The random thirty-request workload through a pool so small that requests are preempted and
+    recomputed, in bfloat16 with captured decode steps: overlapped steps against waiting for every
+    step, and every token against the plain implementation where its margin allows."""
+    import random as pyrandom
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    folder, config, weights = folders["b"]
+    model = load(folder, "bfloat16")
+    rnd_ = pyrandom.Random(100 + seed)
+    reqs = []
+    for i in range(30):
+        n = rnd_.randrange(1, 40)
+        reqs.append(dict(prompt=ru.random_ids(n, config["vocab_size"], 1900 + 31 * seed + i),
+                         max_new=rnd_.randrange(1, 24), eos=rnd_.choice([None, None, rnd_.randrange(config["vocab_size"])]),
+                         temperature=rnd_.choice([0.0, 0.0, 0.9]), priority=rnd_.choice([0, 0, 1]), wave=i % 3))
+
+    def run(overlap):
+        engine = ContinuousBatchingEngine(model, KVConfig(block_size=8), num_blocks=28, max_batch_tokens=48,
+                                          chunk_size=16, max_num_seqs=8, overlap=overlap, cuda_graph=True, poison=True)
+        assert engine.runner.cuda_graph
+        ids = {}
+        for wave in range(3):
+            for i, r in enumerate(reqs):
+                if r["wave"] == wave:
+                    ids[i] = engine.add_request(r["prompt"], r["max_new"],
+                                                SamplingParams(temperature=r["temperature"], seed=70 + i),
+                                                eos_id=r["eos"], priority=r["priority"])
+            for _ in range(7):
+                engine.step()
+        engine.run_until_done()
+        out = engine.collect_outputs()
+        assert engine.runner.cache.num_free_pages() == 28 and not engine.has_work()
+        engine.runner.cache.check()
+        engine.runner.check_device()
+        assert engine.runner._graphs, "no step was replayed from a captured graph"
+        return [out[ids[i]] for i in range(len(reqs))], engine.num_preemptions
+
+    waited, pre_waited = run(False)
+    overlapped, pre_overlapped = run(True)
+    assert pre_waited > 0 and pre_overlapped > 0, "the pool was meant to be too small"
+    for i, (r, toks, toks2) in enumerate(zip(reqs, waited, overlapped)):
+        params = SamplingParams(temperature=r["temperature"], seed=70 + i)
+        for stream in (toks, toks2):
+            assert 1 <= len(stream) <= r["max_new"]
+            if r["eos"] is not None and r["eos"] in stream:
+                assert stream.index(r["eos"]) == len(stream) - 1
+        assert_tokens_within_margin(weights, config, r["prompt"], toks, params)
+        if toks2 != toks:  # the same kernels on the same inputs: only a preemption at another step
+            assert_tokens_within_margin(weights, config, r["prompt"], toks2, params)  # may change a near-tie
+
+
+# ------------------------------------------------------------- more than 64 requests at once
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("live", [65, 100, 130])
+def test_many_live_requests(folders, live, dtype):
+    """65, 100 and 130 requests decoding side by side: more single-token rows than the few-row
+    matrix product takes (they go to the many-row product), and the captured steps of 128 and 256
+    padded rows.  Greedy, against the plain implementation."""
+    from dispec_b200 import ContinuousBatchingEngine, KVConfig, SamplingParams
+    folder, config, weights = folders["b"]
+    engine = ContinuousBatchingEngine(load(folder, dtype), KVConfig(block_size=8), num_blocks=live * 4 + 8,
+                                      max_batch_tokens=4096, max_num_seqs=256, cuda_graph=True)
+    prompts = [ru.random_ids(1 + (7 * i) % 19, config["vocab_size"], 3000 + i) for i in range(live)]
+    ids = [engine.add_request(p, 6, SamplingParams()) for p in prompts]
+    engine.step()
+    assert len(engine.running) + len(engine.finished) == live  # every request is live after one step
+    engine.run_until_done()
+    out = engine.collect_outputs()
+    if dtype == "bfloat16":
+        assert any(bucket >= 128 for bucket, _ in engine.runner._graphs), engine.runner._graphs.keys()
+    for rid, prompt in list(zip(ids, prompts))[::3]:
+        got = out[rid]
+        assert len(got) == 6
+        if dtype == "float32":
+            want, margin = replay_sampling(weights, config, prompt, got, SamplingParams())
+            assert got == want or margin < 1e-4, (rid, got, want, margin)
+        else:
+            assert_tokens_within_margin(weights, config, prompt, got, SamplingParams())
+    assert engine.runner.cache.num_free_pages() == live * 4 + 8
+    engine.runner.check_device()

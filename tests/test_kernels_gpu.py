@@ -686,3 +686,81 @@ def test_decode_attention_that_rotates_and_stores_itself(H, KVH, D, rot, page, w
         torch.testing.assert_close(b[written], a[written], atol=1e-2, rtol=1e-2)
         assert torch.equal(b[~written], a[~written])  # nothing else was touched
     ops.raise_on_device_error("decode attention with rotation")
+
+
+# ------------------------------------------------------------------ counter-based random fill
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1,), (7, 13), (1023,), (3, 5, 17), (257, 96)])
+def test_fill_normal_equals_the_cpu_generator_bit_for_bit(dtype, shape):
+    import numpy as np
+    import plain_qwen2 as plain
+    from dispec_b200 import ops
+    from dispec_b200.weights import counter_rng
+    seed, ordinal, std, mean = 2 ** 35 + 11, 41, 0.02, 1.0
+    out = ops.fill_normal(torch.empty(shape, dtype=dtype, device=dev()), seed, ordinal, std, mean)
+    want = torch.from_numpy(counter_rng.normal(seed, ordinal, shape, std, mean))
+    assert torch.equal(out.cpu(), want.to(dtype))
+    z = ops.fill_normal(torch.empty(shape, dtype=torch.float32, device=dev()), seed, ordinal, 1.0, 0.0).cpu().flatten()
+    for i in sorted({0, z.numel() // 2, z.numel() - 1}):
+        assert np.float32(z[i].item()) == plain.counter_normal_element(seed, ordinal, i)
+    # rounded through bfloat16 into a float32 buffer: what loading a bfloat16 file into the 32-bit engine gives
+    via = ops.fill_normal(torch.empty(shape, dtype=torch.float32, device=dev()), seed, ordinal, std, mean, through_bf16=True)
+    assert torch.equal(via.cpu(), want.to(torch.bfloat16).float())
+
+
+def test_fill_normal_of_a_large_tensor_is_fast_and_any_slice_can_be_recomputed():
+    """The output matrix of the largest shape (152,064 x 5,120, 1.5 GB in bfloat16) is filled in
+    place on the device; slices anywhere in it equal the CPU generator started at that element."""
+    import time
+    from dispec_b200 import ops
+    from dispec_b200.weights import counter_rng
+    rows, cols = 152064, 5120
+    out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev())
+    ops.fill_normal(out[:8], 4, 290, 0.02)  # first call: library load
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ops.fill_normal(out, 4, 290, 0.02)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 2.0
+    flat = out.view(-1)
+    for start in (0, 5119, 123_456_789, rows * cols - 1000):
+        want = torch.from_numpy(np_f32(counter_rng.standard_normal(4, 290, 1000, start=start)) * np_f32(0.02))
+        assert torch.equal(flat[start:start + 1000].cpu(), want.to(torch.bfloat16)), start
+    sample = flat[::997].float()
+    assert abs(sample.mean().item()) < 2e-4 and abs(sample.std().item() - 0.02) < 2e-4
+
+
+def np_f32(x):
+    import numpy as np
+    return np.float32(x) if not hasattr(x, "dtype") else x.astype(np.float32, copy=False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_model_filled_on_the_device_equals_the_written_folder(tmp_path, dtype):
+    """load_random_model (device fill) and write_random_model (CPU generator) + load_model give
+    the same weights, hence the same logits bit for bit."""
+    import replay_util as ru
+    from dispec_b200 import load_model, load_model_config
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    from dispec_b200.weights import load_random_model, write_random_model
+    cfg = load_model_config(ru.CONFIG_B)
+    overrides = {"lm_head.weight": 0.5}
+    write_random_model(cfg, str(tmp_path), seed=1, std=0.05, dtype="bfloat16", overrides=overrides)
+    from_file = load_model(str(tmp_path), dtype, dev())
+    on_device = load_random_model(cfg, 1, 0.05, dtype, dev(), overrides=overrides)
+    assert torch.equal(from_file.embedding.weight, on_device.embedding.weight)
+    assert torch.equal(from_file.layers[2].mixer.w_qkv, on_device.layers[2].mixer.w_qkv)
+    assert torch.equal(from_file.layers[1].mixer_norm.weight, on_device.layers[1].mixer_norm.weight)
+    ids = ru.random_ids(21, ru.CONFIG_B["vocab_size"], 3)
+    logits = []
+    for model in (from_file, on_device):
+        runner = ModelRunner(model, page_size=8, num_pages=8, max_num_seqs=2)
+        runner.admit("s")
+        logits.append(runner.step([SeqEntry("s", ids, 0, list(range(len(ids))))]))
+    assert torch.equal(logits[0], logits[1])
+    # a folder written from device-filled tensors is the same file content
+    write_random_model(cfg, str(tmp_path / "dev"), seed=1, std=0.05, dtype="bfloat16", overrides=overrides, device=dev())
+    a = open(tmp_path / "model.safetensors", "rb").read()
+    b = open(tmp_path / "dev" / "model.safetensors", "rb").read()
+    assert a == b

@@ -14,14 +14,15 @@ LENGTHS = {"a": [5, 17, 33, 70], "b": [1, 9, 40, 64, 131], "c": [3, 50, 97, 150]
            "e": [4, 66, 130, 300]}
 
 
-def check(name, dtype, tmp_path):
+def check(name, dtype, tmp_path, cuda_graph=False):
     spec = ru.TINY[name]
     model_dir = str(tmp_path / "model")
     config, weights = ru.make_model_folder(model_dir, name, dtype="bfloat16")
     vocab = config["vocab_size"]
     prompts = {f"p{n}": ru.random_ids(n, vocab, 100 + n) for n in LENGTHS[name]}
     trace, peak = ru.build_four_mode_trace(prompts, spec["page_size"])
-    got = ru.run_trace(model_dir, dtype, trace, peak, str(tmp_path / "out"), page_size=spec["page_size"])
+    got = ru.run_trace(model_dir, dtype, trace, peak, str(tmp_path / "out"), page_size=spec["page_size"],
+                       cuda_graph=cuda_graph)
     refs = {n: plain.forward_logits(weights, config, ids) for n, ids in prompts.items()}
     worst = {}
     for (step, rid, pos), row in got.items():
@@ -51,3 +52,11 @@ def test_replay_float32(name, tmp_path):
 @pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_replay_bfloat16(name, tmp_path):
     check(name, "bfloat16", tmp_path)
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
+def test_replay_bfloat16_single_token_steps_from_captured_graphs(name, tmp_path):
+    """The same with --cuda-graph: the steps made of single tokens only (the last 32 tokens of the
+    second mode, and the all-decode steps of the mixed mode) are replayed from captured CUDA
+    graphs, which is how serving runs them."""
+    check(name, "bfloat16", tmp_path, cuda_graph=True)
