@@ -15,7 +15,9 @@ goes to standard output:
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   bytes a decode step must read (every weight once + the live requests' cache)
              divided by its time, against the measured copy bandwidth
-  points     decode at batch 1 and 64
+  points     decode at batch 1 and 64 (with the fraction of the copy bandwidth), one request at
+             32,768 tokens of context, and, for the Qwen2.5-7B and 14B layer sizes with every layer
+             of each, decode at batch 1 / 8 / 64 and the 2,048-token prefill with their fractions
 
 Peaks come from MEASURED_PEAKS.json beside this file when present ("of measured"), else the
 fallback 6.65 TB/s and 1.59 PFLOP/s ("of fallback").  ``--impl reference`` runs the unmodified
@@ -67,28 +69,55 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples SM clocks and throttle reasons while a region is timed: through NVML (a read takes
+    well under a millisecond, so that a timed region of a few tens of milliseconds still gets ten
+    samples and more), or through nvidia-smi where the NVML binding is missing.  Only reads."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self):
-        self.samples = []
+    def __init__(self, period_s: float = 0.002):
+        self.samples = []  # [sm_mhz, sm_max_mhz, {reason: bool}]
+        self.period_s = period_s
         self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            self._max = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001 - fall back to nvidia-smi
+            self._nvml = None
+
+    def _read_nvml(self):
+        n = self._nvml
+        mhz = n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)
+        bits = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle) if hasattr(
+            n, "nvmlDeviceGetCurrentClocksEventReasons") else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        masks = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        return [mhz, self._max, {k: bool(bits & m) for k, m in masks.items()}]
+
+    def _read_smi(self):
+        out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
+        if not out:
+            return None
+        f = [x.strip() for x in out[0].split(",")]
+        return [int(f[0]), int(f[1]), {n: v.lower().startswith("active") for n, v in zip(self.NAMES, f[2:])}]
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip().splitlines()
-                if out:
-                    self.samples.append([x.strip() for x in out[0].split(",")])
+                sample = self._read_nvml() if self._nvml else self._read_smi()
+                if sample:
+                    self.samples.append(sample)
             except Exception:  # noqa: BLE001 - sampling must never break the run
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(self.period_s if self._nvml else 0.05)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -100,12 +129,28 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self) -> dict:
-        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
-        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:]) if v.lower().startswith("active")})
+        mhz = [s[0] for s in self.samples]
+        mx = [s[1] for s in self.samples]
+        reasons = sorted({n for s in self.samples for n, on in s[2].items() if on})
         return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(mhz)}
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(mhz),
+                "source": "nvml" if self._nvml else "nvidia-smi"}
+
+
+def bench_config(shape: str, cfg_dict: dict, layers: int, full_layers: int, context_len: int, seed: int,
+                 weight_bytes: int, peaks_source: str) -> dict:
+    """The ``config`` of the JSON line: every size by name, flat, the same keys in both arms."""
+    return {
+        "model": f"Qwen2.5-{shape.upper()} shape", "layers": layers, "layers_full": full_layers,
+        "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
+        "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
+        "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
+        "tied": cfg_dict["tie_word_embeddings"], "global_batch": BATCH, "seq_len": PROMPT_LEN,
+        "context_len": context_len, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE,
+        "parallelism": "single GPU", "weights": f"random N(0,{STD}) seed {seed}",
+        "l2": "no flush: each step reads %.2f GB of weights, above the 126 MB L2" % (weight_bytes / 1e9),
+        "peaks": "of " + peaks_source,
+    }
 
 
 def random_prompts(n, length, vocab, seed):
@@ -130,9 +175,10 @@ def model_bytes_and_flops(cfg: dict, layers: int):
 
 # ------------------------------------------------------------------------------ our arm
 
-def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
+def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192, clocks=None):
     """Step function + argmax, no scheduler: returns (ms per step, launches in the timed region,
-    mean context length over the timed steps)."""
+    mean context length over the timed steps).  ``clocks``: a ClockSampler that runs during the
+    timed steps only."""
     import torch
     from dispec_b200 import ops
     from dispec_b200.engine import SeqEntry
@@ -185,11 +231,15 @@ def decode_direct(runner, prompts, steps, warmup, max_batch_tokens=8192):
     ctx0 = statistics.mean(pos.values())
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n0 = LaunchCounter.n
+    if clocks is not None:
+        clocks.__enter__()
     start.record()
     for _ in range(steps):
         one_step()
     end.record()
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.__exit__()
     ms = start.elapsed_time(end) / steps
     launches = LaunchCounter.n - n0
     mean_ctx = (ctx0 + statistics.mean(pos.values())) / 2
@@ -237,6 +287,44 @@ def prefill_time(runner, prompt, repeats=5):
         ts.append(s.elapsed_time(e))
         runner.release("p")
     return statistics.median(ts[2:])
+
+
+def measure_shape(shape: str, args, pk: dict) -> dict:
+    """Decode at batch 1, 8 and 64 and a 2,048-token prefill for one of the larger shapes, with
+    every layer of the shape: tokens a second and the fraction of the measured roofline."""
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+    cfg_dict = dict(BENCH_CONFIG)
+    cfg_dict.update(OTHER_SHAPES[shape][0])
+    seed = OTHER_SHAPES[shape][1]
+    layers = cfg_dict["num_hidden_layers"]
+    t0 = time.time()
+    model = load_random_model(load_model_config(cfg_dict), seed, STD, "bfloat16", "cuda:0")
+    torch.cuda.synchronize()
+    print(f"bench: {shape} model ({layers} layers) filled on the device in {time.time() - t0:.1f}s",
+          file=sys.stderr, flush=True)
+    weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg_dict, layers)
+    steps, warmup = max(20, min(args.steps, 50)), max(3, args.warmup // 2)
+    per_req = (PROMPT_LEN + NEW_TOKENS + steps + warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    out = {f"{shape}_layers": layers}
+    for b in (1, 8, 64):
+        r = ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(b * per_req, 160), max_num_seqs=max(b, 8),
+                        cuda_graph=True)
+        ms, _, ctx = decode_direct(r, random_prompts(b, PROMPT_LEN, cfg_dict["vocab_size"], 13 + b), steps, warmup)
+        out[f"{shape}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        out[f"{shape}_decode_b{b}_hbm_frac"] = round(
+            (weight_bytes + b * ctx * kv_per_token) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        if b == 1:
+            pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, cfg_dict["vocab_size"], 12)[0], repeats=3)
+            out[f"{shape}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)
+            out[f"{shape}_prefill_frac"] = round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+        del r
+        torch.cuda.empty_cache()
+    del model
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args) -> dict:
@@ -292,8 +380,8 @@ def run_ours(args) -> dict:
     # headline: batch 8
     runner = runner_for(BATCH)
     prompts = random_prompts(BATCH, PROMPT_LEN, vocab, 11)
-    with ClockSampler() as clocks:
-        ms, launches, mean_ctx = decode_direct(runner, prompts, args.steps, args.warmup)
+    clocks = ClockSampler()
+    ms, launches, mean_ctx = decode_direct(runner, prompts, args.steps, args.warmup, clocks=clocks)
     value = BATCH * 1000.0 / ms
     step_bytes = weight_bytes + BATCH * mean_ctx * kv_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -307,12 +395,13 @@ def run_ours(args) -> dict:
     for b in (1, 64):
         r = runner_for(b)
         steps = max(20, min(args.steps, 100))
-        bms, _, _ = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, max(3, args.warmup // 2))
+        bms, _, bctx = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, max(3, args.warmup // 2))
         points[f"decode_b{b}"] = round(b * 1000.0 / bms, 1)
+        points[f"decode_b{b}_hbm_frac"] = round((weight_bytes + b * bctx * kv_per_token) / (bms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         del r
         torch.cuda.empty_cache()
-    # beyond the recorded configuration: one request with a long context (its keys are shared
-    # among clusters, see profiles/attn_decode_long_context.md)
+    # beyond the recorded configuration: one request with a long context (its keys are shared among
+    # several clusters and merged by a second kernel)
     steps = max(20, min(args.steps, 100))
     r = runner_for(1, (LONG_CONTEXT + steps + 64) // PAGE_SIZE + 2, 2 * LONG_CONTEXT)
     bms, _, _ = decode_direct(r, random_prompts(1, LONG_CONTEXT, vocab, 31), steps, max(3, args.warmup // 2))
@@ -320,22 +409,20 @@ def run_ours(args) -> dict:
     del r
     torch.cuda.empty_cache()
     from dispec_b200.ops import library
+    libraries = [os.path.basename(p) for p in library.loaded_libraries()]
+    if args.shape == "1.5b" and not args.layers and not args.no_other_shapes:
+        # the two larger shapes of the family, every layer of each: decode at batch 1 / 8 / 64, prefill
+        del model
+        torch.cuda.empty_cache()
+        for shape in ("7b", "14b"):
+            points.update(measure_shape(shape, args, pk))
     return {
         "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "ours",
-        "config": {
-            "model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "layers_full": full_layers,
-            "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
-            "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
-            "intermediate": cfg_dict["intermediate_size"], "vocab": vocab, "tied": cfg_dict["tie_word_embeddings"],
-            "global_batch": BATCH, "seq_len": PROMPT_LEN, "context_len": max(CONTEXT_LEN, over or 0),
-            "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-            "weights": f"random N(0,{STD}) seed {seed}",
-            "l2": "no flush: each step reads %.2f GB of weights, above the 126 MB L2" % (weight_bytes / 1e9),
-            "peaks": "of " + pk["source"],
-        },
+        "config": bench_config(args.shape, cfg_dict, layers, full_layers, max(CONTEXT_LEN, over or 0), seed,
+                               weight_bytes, pk["source"]),
         "clocks": clocks.summary(),
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -345,7 +432,7 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
-        "kernel_libraries": [os.path.basename(p) for p in library.loaded_libraries()],
+        "kernel_libraries": libraries,
     }
 
 
@@ -370,16 +457,19 @@ def run_reference(args) -> dict:
     model.eval()
     model.requires_grad_(False)
     pages = BATCH * ((PROMPT_LEN + NEW_TOKENS + args.steps + args.warmup) // PAGE_SIZE + 2) + 64
+    weight_bytes, _, _ = model_bytes_and_flops(BENCH_CONFIG, cfg["num_hidden_layers"])
+    longest = PROMPT_LEN + args.steps + args.warmup + 64
+    over = longest if longest > BENCH_CONFIG["max_position_embeddings"] else None
     eng = ContinuousBatchingEngine(model, num_blocks=pages, max_batch_tokens=8192,
                                    attn_backend="triton", fuse=True)
     for p in random_prompts(BATCH, PROMPT_LEN, cfg["vocab_size"], 11):
         eng.add_request(p, args.warmup + args.steps + 8, SamplingParams(0.0))
     while eng.waiting or eng.prefilling:
         eng.step()
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
     with ClockSampler() as clocks:
-        for _ in range(args.warmup):
-            eng.step()
-        torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         s.record()
@@ -394,9 +484,10 @@ def run_reference(args) -> dict:
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "reference",
-        "config": {"model": "Qwen2.5-1.5B shape", "layers": cfg["num_hidden_layers"], "global_batch": BATCH,
-                   "seq_len": PROMPT_LEN, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-                   "path": "dispec ContinuousBatchingEngine(attn_backend=triton, fuse=True)"},
+        "config": bench_config("1.5b", BENCH_CONFIG, cfg["num_hidden_layers"], cfg["num_hidden_layers"],
+                               max(CONTEXT_LEN, over or 0), SEED, weight_bytes, peaks()["source"]),
+        "path": "dispec ContinuousBatchingEngine(attn_backend=triton, fuse=True); weights from the model "
+                "library's own initialiser (normal, std 0.02) under torch.manual_seed",
         "clocks": clocks.summary(),
         "e2e": {"value": round(BATCH * args.steps / wall, 1), "unit": "tok/s"},
     }
@@ -419,6 +510,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0,
                     help="prompt length of the --only decode phase (default: the recorded configuration's)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--no-other-shapes", action="store_true",
+                    help="skip the 7B and 14B points of the default run (shorter run while developing)")
     args = ap.parse_args()
     globals()["PAGE_SIZE"] = args.page_size
     if args.gpus != 1:

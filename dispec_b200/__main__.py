@@ -8,8 +8,10 @@ and cache options carry the names of its dataclasses (dispec/config.py:31-51: ``
 ``num_blocks``, ``max_batch_tokens``, ``chunk_size``).  Token ids in, token ids out: the
 tokenizer is not part of the engine.
 
-    generate        generate from prompts given as token ids
+    generate        generate from prompts given as token ids (--model DIR, or --random CONFIG for
+                    random weights filled on the device)
     random          write a model folder with random weights from a config.json and a seed
+    replay          feed given token ids step by step and write logits (the program of bin/trace_run)
     throughput      continuous-batching throughput at several concurrency levels
     prefill-bench   time to first token for prompts of given lengths
     env-check       what the engine needs, and whether it is there
@@ -23,11 +25,21 @@ import sys
 import time
 
 
-def _engine_args(ap):
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+def _engine_args(ap, random_weights=False):
+    if random_weights:
+        src = ap.add_mutually_exclusive_group(required=True)
+        src.add_argument("--model", help="folder with config.json and model.safetensors")
+        src.add_argument("--random", metavar="CONFIG", help="a config.json (or a folder holding one): the model "
+                         "gets random weights, filled on the device")
+        ap.add_argument("--weights-seed", type=int, default=None, help="seed of --random (default: --seed)")
+        ap.add_argument("--std", type=float, default=0.02, help="standard deviation of --random")
+    else:
+        ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--num-blocks", type=int, default=2048, help="pages per cache group")
+    ap.add_argument("--block-size", "--page-size", dest="block_size", type=int, default=16,
+                    help="tokens per cache page")
+    ap.add_argument("--num-blocks", "--num-pages", dest="num_blocks", type=int, default=2048,
+                    help="pages per cache group")
     ap.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget of one step")
     ap.add_argument("--chunk-size", type=int, default=None, help="largest prompt portion per step")
     ap.add_argument("--no-cuda-graph", action="store_true", help="run decode steps without graph replay")
@@ -36,7 +48,12 @@ def _engine_args(ap):
 
 def _make_engine(args):
     from dispec_b200 import ContinuousBatchingEngine, KVConfig, load_model
-    model = load_model(args.model, args.dtype, args.device)
+    if getattr(args, "random", None):
+        from dispec_b200 import load_model_config, load_random_model
+        seed = args.seed if args.weights_seed is None else args.weights_seed
+        model = load_random_model(load_model_config(args.random), seed, args.std, args.dtype, args.device)
+    else:
+        model = load_model(args.model, args.dtype, args.device)
     return ContinuousBatchingEngine(model, KVConfig(block_size=args.block_size), num_blocks=args.num_blocks,
                                     max_batch_tokens=args.max_batch_tokens, chunk_size=args.chunk_size,
                                     cuda_graph=not args.no_cuda_graph), model
@@ -151,7 +168,7 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="generate from prompts given as token ids")
-    _engine_args(g)
+    _engine_args(g, random_weights=True)
     g.add_argument("--prompt-ids", action="append", help="one prompt as token ids: '5,17,3' (repeatable)")
     g.add_argument("--prompt-file", help="one prompt per line: ids separated by spaces/commas, or a JSON list")
     g.add_argument("--random-prompts", type=int, nargs="+", help="lengths of uniform random prompts")
@@ -186,9 +203,17 @@ def main(argv=None) -> int:
     p.add_argument("--label", default="")
     p.set_defaults(fn=cmd_prefill_bench)
 
+    rp = sub.add_parser("replay", add_help=False,
+                        help="trace replay: steps on standard input, logits to files (options as bin/trace_run)")
+    rp.set_defaults(fn=None)
+
     e = sub.add_parser("env-check", help="what the engine needs, and whether it is there")
     e.set_defaults(fn=lambda a: __import__("dispec_b200.env_check", fromlist=["main"]).main())
 
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":  # the replay program parses its own options
+        from dispec_b200.engine.replay import main as replay_main
+        return replay_main(argv[1:])
     args = ap.parse_args(argv)
     from dispec_b200.config.model_config import ConfigError
     from dispec_b200.registry import RegistryError

@@ -125,7 +125,11 @@ class Qwen2Config(ModelConfig):
                 raise ConfigError(f"{where}: layer_types has {len(layer_types)} entries for {layers} layers")
             for i, t in enumerate(layer_types):
                 if t == "sliding_attention":
-                    _require(d, ["sliding_window"], where)
+                    # a file that marks a layer as sliding while it switches windows off contradicts
+                    # itself; which of the two wins is not for the engine to guess
+                    if d.get("use_sliding_window") is False or d.get("sliding_window") is None:
+                        raise ConfigError(f"{where}: layer_types[{i}] is 'sliding_attention' but "
+                                          f"use_sliding_window is false or sliding_window is missing")
                     windows[i] = int(d["sliding_window"])
                 elif t != "full_attention":
                     raise ConfigError(f"{where}: layer_types[{i}]={t!r} is not implemented")

@@ -128,6 +128,11 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
   const int my_begin = kt_begin + split * per;
   const int my_end = min(kt_end, my_begin + per);
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
+  // set when a key tile met a page id outside the pool: from then on the mask looks every key's page
+  // up again and hides the keys of such pages (their rows were zero-filled, not loaded)
+  __shared__ int bad_page_seen;
+  if (tid == 0) bad_page_seen = 0;
+  __syncthreads();
 
   // ---- Q tile: two threads per row
   {
@@ -151,7 +156,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
       const int within = p.page_shift >= 0 ? (b & (p.page_size - 1)) : (b % p.page_size);
       const int page = table[lp];
       if (page < 0 || page >= p.num_pages) {
-        if (b >= lo && half == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        if (b >= lo && half == 0) {
+          atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          bad_page_seen = 1;
+        }
         valid = false;
       } else {
         off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D;
@@ -207,6 +215,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
         }
       }
       // mask, scale, online softmax
+      const bool check_pages = bad_page_seen != 0;  // the same for the whole CTA (read after the barrier)
       float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt)
@@ -214,7 +223,11 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const Params p, int t
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
           const int key = kt * BN + nt * 8 + 2 * c4 + (e & 1);
-          const bool vis = row_ok[r] && key <= pos_r[r] && (p.window == 0 || key > pos_r[r] - p.window);
+          bool vis = row_ok[r] && key <= pos_r[r] && (p.window == 0 || key > pos_r[r] - p.window);
+          if (check_pages && vis) {
+            const int page = table[key / p.page_size];
+            vis = page >= 0 && page < p.num_pages;
+          }
           const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
           s[nt][e] = v;
           tmax[r] = fmaxf(tmax[r], v);
@@ -443,9 +456,16 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const int last_page = my_begin < my_end ? min(pos, my_end * DK - 1) / p.page_size : -1;
   const int n_pages = last_page - first_page + 1;
   const bool cached = n_pages <= DEC_MAXP;
-  if (cached)
-    for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = table[first_page + i];
-  __syncthreads();
+  // page ids outside the pool among this CTA's keys: recorded when their tile is loaded; here they
+  // only switch on the mask's look at every key's page, so that such keys are hidden from the softmax
+  int bad_here = 0;
+  for (int i = tid; i < n_pages; i += THREADS) {
+    const int page = table[first_page + i];
+    if (cached) pages_s[i] = page;
+    const int key0 = (first_page + i) * p.page_size;  // pages the window has passed hold -1 and no key in use
+    if (key0 + p.page_size > lo && key0 <= pos) bad_here |= (page < 0 || page >= p.num_pages) ? 1 : 0;
+  }
+  const bool check_pages = __syncthreads_or(bad_here) != 0;
 
   // a tile lies within one page when the page size is a multiple of the tile (the usual case): one
   // page lookup per tile, and a lane's pieces differ by a constant row stride
@@ -658,7 +678,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
         const int key = kt * DK + nt * 8 + 2 * c4 + (e & 1);
-        const bool vis = row_ok[r] && key <= pos && key >= lo;
+        bool vis = row_ok[r] && key <= pos && key >= lo;
+        if (check_pages && vis) {
+          const int page = table[key / p.page_size];
+          vis = page >= 0 && page < p.num_pages;
+        }
         const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
         s[nt][e] = v;
         tmax[r] = fmaxf(tmax[r], v);

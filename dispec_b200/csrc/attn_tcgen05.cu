@@ -134,6 +134,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
   __shared__ float merge_m[BM], merge_l[BM];          // group 1's running maximum and sum per row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
+  __shared__ uint32_t bad_pages[STAGES];  // bit j: page j of the key tile in this stage had no valid id (not loaded)
 
   pdl_launch_dependents();
   pdl_wait();
@@ -225,12 +226,16 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         if (lane == 0) failed = 1;
         break;
       }
-      if (pg != -2 && (pg < 0 || pg >= p.num_pages)) {
+      // a page id outside the pool: recorded, not loaded, and its keys are hidden from every row
+      const bool bad = pg != -2 && (pg < 0 || pg >= p.num_pages);
+      if (bad) {
         atomicOr(p.err, DSP_ERR_BAD_PAGE);
         pg = -1;
       }
+      const uint32_t bad_bits = __ballot_sync(0xffffffffu, bad);
       const uint32_t live = __ballot_sync(0xffffffffu, pg >= 0);
       if (lane == 0) {
+        bad_pages[s] = bad_bits;  // published by the arrival on kv_full below
         if (live == 0) mbar_arrive(&kv_full[s]);
         else mbar_expect_tx(&kv_full[s], (uint32_t)__popc(live) * page_bytes);
       }
@@ -319,6 +324,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     const uint32_t o_addr = lane_addr + (uint32_t)(O_COL + g * D);
     const uint32_t p_row = smem_u32(p_s + g * P_BYTES) + (uint32_t)r * 128u;
     const float scale = p.scale_log2;
+    const int page_shift = __ffs(p.page_size) - 1;  // page sizes are powers of two here
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     int j = 0;  // tiles of this group so far
@@ -345,11 +351,12 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[g]);
       // tiles every row of the CTA sees whole (most of them) skip the mask
-      if (!(key0 + BN - 1 <= pos0 && key0 >= lo_top)) {
+      const uint32_t bad = bad_pages[i % STAGES];
+      if (!(key0 + BN - 1 <= pos0 && key0 >= lo_top) || bad != 0u) {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const int key = key0 + c;
-          const bool vis = row_ok && key <= pos_r && key >= lo_r;
+          const bool vis = row_ok && key <= pos_r && key >= lo_r && !((bad >> (c >> page_shift)) & 1u);
           sv[c] = vis ? sv[c] : 0xff800000u;  // -inf
         }
       }
@@ -409,7 +416,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         st_shared16(p_row + (uint32_t)((c ^ (r & 7)) << 4),
                     make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]));
       // value rows no row of this tile may see: zero them (whole 128-byte rows, every slice)
-      if (key0 < lo || key0 + BN - 1 > pos_last) {
+      if (key0 < lo || key0 + BN - 1 > pos_last || bad != 0u) {
         if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[i % STAGES], (i / STAGES) & 1))) {
           ok = false;
           break;

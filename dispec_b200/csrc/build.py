@@ -33,6 +33,7 @@ CORE_SOURCES = [
     "attn_combine.cu",
     "sampling.cu",
     "random_fill.cu",
+    "selftest.cu",
 ]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -23,7 +23,9 @@
  * cudaFree nor any routine that allocates.
  *
  * First call on a device: it looks up the array's device address (cudaGetSymbolAddress, with
- * that device current) and keeps it.  Make that first call outside any stream capture.
+ * that device current) and keeps it.  Make that first call outside any stream capture.  Several
+ * host threads may make their first call on a device at the same time: each looks the same
+ * address up and stores the same value, no lock is needed.
  *
  * Sharing: all calls on a device use the same array, and it keeps the previous call's
  * contents.  Nothing in it has to start at zero: every slot a call reads was written by that

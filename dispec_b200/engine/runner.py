@@ -53,7 +53,12 @@ class ModelRunner:
         # otherwise (angles are computed from the position, so no table stands in the way of more)
         limit = max_model_len or model.spec.max_position or (1 << 30)
         self.max_model_len = min(limit, self.cache.capacity_tokens())
-        self._graph_pages = [max(1, min(c, -(-self.max_model_len // page_size))) for c in counts]
+        # page-table width of a captured step: a full group never holds more pages than its pool has;
+        # a window group's table is indexed by logical page (holes behind the window), so its
+        # length follows the context, not the pool
+        longest = max(1, -(-self.max_model_len // page_size))
+        self._graph_pages = [longest if g.window > 0 else max(1, min(c, longest))
+                             for g, c in zip(groups, counts)]
         self._graphs: dict = {}
 
     # ---------------------------------------------------------------- request lifecycle

@@ -56,6 +56,11 @@ def test_rejections_are_clear():
         load_model_config(dict(ru.CONFIG_A, rope_scaling={"rope_type": "yarn", "factor": 4.0}))
     with pytest.raises(ConfigError, match="even"):
         load_model_config(dict(ru.CONFIG_A, head_dim=15))
+    # a layer marked as sliding in a file that switches windows off contradicts itself
+    with pytest.raises(ConfigError, match="use_sliding_window is false"):
+        load_model_config(dict(ru.CONFIG_C, use_sliding_window=False))
+    with pytest.raises(ConfigError, match="sliding_window is missing"):
+        load_model_config(dict(ru.CONFIG_C, sliding_window=None))
     with pytest.raises(RegistryError, match="Qwen2ForCausalLM"):
         load_model_config(dict(ru.CONFIG_A, architectures=["NoSuchModel"]))
     with pytest.raises(ConfigError, match="architectures"):

@@ -450,6 +450,22 @@ def test_command_line_generate_and_random(tmp_path):
         want, gaps = plain.greedy_generate(weights, config, prompt, 6)
         n = next((i for i, g in enumerate(gaps) if g < 1e-4), 6)
         assert ln["output_ids"][:n] == want[:n]
+    # the same model without a folder: random weights filled on the device from the configuration and
+    # the seed, with the other spellings of the cache options
+    proc2 = subprocess.run([sys.executable, "-m", "dispec_b200", "generate", "--random", str(cfg_path), "--weights-seed", "5",
+                            "--std", "0.08", "--dtype", "float32", "--prompt-ids", "5,17,3,99", "--prompt-ids", "7 8 9",
+                            "--max-new", "6", "--page-size", "8", "--num-pages", "32", "--max-batch-tokens", "16",
+                            "--chunk-size", "4"], check=True, env=env, cwd=ru.ROOT, capture_output=True, text=True)
+    assert [json.loads(ln) for ln in proc2.stdout.splitlines() if ln.startswith("{")] == lines
+    # and the replay program as a sub-command
+    step = {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3, 99], "want": [3]}], "end": ["a"]}
+    proc3 = subprocess.run([sys.executable, "-m", "dispec_b200", "replay", "--model", str(out_dir), "--dtype", "float32",
+                            "--out", str(tmp_path / "logits"), "--max-tokens", "64", "--page-size", "8"],
+                           input=json.dumps(step) + "\n", check=True, env=env, cwd=ru.ROOT, capture_output=True, text=True)
+    assert proc3.stdout.split() == ["done", "0"]
+    import numpy as np
+    row = torch.from_numpy(np.fromfile(tmp_path / "logits" / "0.f32", dtype="<f4"))
+    assert (row - plain.forward_logits(weights, config, [5, 17, 3, 99])[-1]).abs().max().item() < 1e-4
 
 
 # -------------------------------------------- anchored on the reference scheduler's own output

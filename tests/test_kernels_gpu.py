@@ -284,6 +284,46 @@ def test_sampling_matches_plain_inverse_cdf():
         assert got[r] == want, (r, got[r], want)
 
 
+@pytest.mark.parametrize("V", [151936, 152064])
+def test_sampling_at_the_real_vocabulary_sizes(V):
+    """The radix selection and the fixed-point mass of the sampling kernel at the vocabularies the
+    benchmark shapes have, against the plain inverse CDF in float64: the cases of the small test,
+    top-p at 0.999 over a flat tail behind a few heavy tokens, and top-k with thousands of ties."""
+    import plain_qwen2 as plain
+    from dispec_b200 import ops
+    g = torch.Generator().manual_seed(V)
+    cases = [(0.8, 0, 1.0), (1.3, 10, 1.0), (0.7, 0, 0.9), (1.0, 50, 0.5), (0.0, 0, 1.0),
+             (2.0, 1, 1.0), (0.5, 0, 0.01), (1.0, 2000, 0.999), (1.0, 0, 0.999), (1.0, 0, 0.999), (1.5, 100, 1.0)]
+    us = [0.03, 0.5, 0.77, 0.999, 0.4, 0.6, 0.9, 0.25, 0.9985, 0.31, 0.62]
+    logits = torch.randn(len(cases), V, generator=g) * 3
+    flat = torch.zeros(V)  # a flat tail (every token the same) behind three heavy tokens
+    flat[[5, V // 2, V - 1]] = torch.tensor([14.0, 13.5, 13.0])
+    logits[8] = logits[9] = flat
+    ties = torch.full((V,), -2.0)  # 5,000 tokens tie at the top: top_k = 100 keeps all of them
+    ties[torch.randperm(V, generator=g)[:5000]] = 1.0
+    logits[10] = ties
+    t = torch.tensor([c[0] for c in cases], dtype=torch.float32, device=dev())
+    k = torch.tensor([c[1] for c in cases], dtype=torch.int32, device=dev())
+    p = torch.tensor([c[2] for c in cases], dtype=torch.float32, device=dev())
+    u = torch.tensor(us, dtype=torch.float32, device=dev())
+    got = ops.sample(logits.to(dev()), t, k, p, u).cpu().tolist()
+    exact = 0
+    for r, (temp, tk, tp) in enumerate(cases):
+        probs = plain.sampling_distribution(logits[r], temp, tk, tp)
+        want = plain.draw_inverse_cdf(probs, float(u[r].item())) if temp > 0 else int(logits[r].argmax())
+        assert probs[got[r]] > 0, (r, got[r])
+        if got[r] == want:
+            exact += 1
+            continue
+        # 32-bit exponentials against 64-bit ones: the draw may land on a neighbour only when the
+        # uniform number is within 1e-6 of the mass of an edge of the cumulative distribution
+        cdf = probs.cumsum(-1)
+        assert float((cdf - float(u[r].item()) * cdf[-1]).abs().min()) < 1e-6, (r, got[r], want)
+    assert exact >= len(cases) - 2
+    kept = plain.sampling_distribution(logits[10], 1.5, 100, 1.0)
+    assert int((kept > 0).sum()) == 5000
+
+
 def test_sampling_distribution_is_the_masked_softmax():
     import plain_qwen2 as plain
     from dispec_b200 import ops
