@@ -456,16 +456,13 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const int last_page = my_begin < my_end ? min(pos, my_end * DK - 1) / p.page_size : -1;
   const int n_pages = last_page - first_page + 1;
   const bool cached = n_pages <= DEC_MAXP;
-  // page ids outside the pool among this CTA's keys: recorded when their tile is loaded; here they
-  // only switch on the mask's look at every key's page, so that such keys are hidden from the softmax
-  int bad_here = 0;
-  for (int i = tid; i < n_pages; i += THREADS) {
-    const int page = table[first_page + i];
-    if (cached) pages_s[i] = page;
-    const int key0 = (first_page + i) * p.page_size;  // pages the window has passed hold -1 and no key in use
-    if (key0 + p.page_size > lo && key0 <= pos) bad_here |= (page < 0 || page >= p.num_pages) ? 1 : 0;
-  }
-  const bool check_pages = __syncthreads_or(bad_here) != 0;
+  if (cached)
+    for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = table[first_page + i];
+  // keys of a tile whose page id lies outside the pool (bit r: key r of the tile), per warp and ring
+  // slot: written when the tile is requested, read when its scores are masked (such keys are hidden)
+  __shared__ uint32_t bad_keys[4][DSTAGES];
+  bool warp_bad = false;  // this warp met such a page: only then are the masks written and read
+  __syncthreads();
 
   // a tile lies within one page when the page size is a multiple of the tile (the usual case): one
   // page lookup per tile, and a lane's pieces differ by a constant row stride
@@ -477,7 +474,12 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       const int lp = b0 / p.page_size;
       const int page = cached ? pages_s[lp - first_page] : table[lp];
       const bool page_ok = page >= 0 && page < p.num_pages;
-      if (!page_ok && lane == 0 && b0 <= pos && b0 + DK > lo) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+      const bool bad = !page_ok && b0 <= pos && b0 + DK > lo;  // the same for every lane
+      if (bad) warp_bad = true;
+      if (warp_bad && lane == 0) {
+        if (bad) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        bad_keys[warp][stage] = bad ? 0xffffu : 0u;
+      }
       const size_t base = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + (b0 % p.page_size)) * D;
       constexpr int ROWS_PER_PASS = 32 / CHUNKS > 0 ? 32 / CHUNKS : 1;
       if constexpr (32 % CHUNKS == 0) {  // whole rows per pass of the warp
@@ -503,6 +505,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       }
       return;
     }
+    uint32_t bad_mine = 0u;
 #pragma unroll 4
     for (int i = lane; i < DK * CHUNKS; i += 32) {
       const int r = i / CHUNKS, chunk = i % CHUNKS;
@@ -515,6 +518,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
         const int page = cached ? pages_s[lp - first_page] : table[lp];
         if (page < 0 || page >= p.num_pages) {
           if (chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          bad_mine |= 1u << r;
           valid = false;
         } else {
           off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D + chunk * 8;
@@ -522,6 +526,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       }
       cp_async16(k_s + sw(r, chunk), p.k_pool + off, valid);
       cp_async16(v_s + sw(r, chunk), p.v_pool + off, valid);
+    }
+    if (__any_sync(0xffffffffu, bad_mine != 0u)) warp_bad = true;
+    if (warp_bad) {
+      bad_mine = __reduce_or_sync(0xffffffffu, bad_mine);
+      if (lane == 0) bad_keys[warp][stage] = bad_mine;
     }
   };
 
@@ -630,7 +639,13 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       const int lp = pos / p.page_size;
       const int page = cached ? pages_s[lp - first_page] : table[lp];
       const bool page_ok = page >= 0 && page < p.num_pages;
-      if (!page_ok && lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+      if (!page_ok) {  // not stored, and hidden like every key of such a page
+        if (lane == 0) {
+          atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          bad_keys[warp][stage] = (warp_bad ? bad_keys[warp][stage] : 0u) | (1u << r);
+        }
+        warp_bad = true;
+      }
       const size_t dst = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + pos % p.page_size) * D;
       bf16* k_out = const_cast<bf16*>(p.k_pool) + dst;
       bf16* v_out = const_cast<bf16*>(p.v_pool) + dst;
@@ -671,6 +686,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       mma_bf16(s[0], qa[kk], b[0], b[1]);
       mma_bf16(s[1], qa[kk], b[2], b[3]);
     }
+    uint32_t bad = 0u;
+    if (warp_bad) {  // never in a run with sound page tables
+      __syncwarp();
+      bad = bad_keys[warp][stage];  // written by this warp when it requested the tile
+    }
     float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < DK / 8; ++nt)
@@ -678,11 +698,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
         const int key = kt * DK + nt * 8 + 2 * c4 + (e & 1);
-        bool vis = row_ok[r] && key <= pos && key >= lo;
-        if (check_pages && vis) {
-          const int page = table[key / p.page_size];
-          vis = page >= 0 && page < p.num_pages;
-        }
+        const bool vis = row_ok[r] && key <= pos && key >= lo && !((bad >> (nt * 8 + 2 * c4 + (e & 1))) & 1u);
         const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
         s[nt][e] = v;
         tmax[r] = fmaxf(tmax[r], v);

@@ -45,7 +45,7 @@ def _tcgen05(x, w, bias, residual, out, pairs: bool = True, epilogue=EPI_PLAIN):
 
 def _stream(x, w, bias, residual, out, epilogue=EPI_PLAIN, target_ctas: int | None = None):
     """The few-row product; ``target_ctas``: resident CTA slots the launch may fill by splitting K
-    over a cluster (default: two per SM of the device)."""
+    over a cluster (default: one per SM of the device)."""
     M = x.shape[0]
     N, K = w.shape
     if target_ctas is None:

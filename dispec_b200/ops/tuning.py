@@ -23,9 +23,11 @@ def sm_count(device=None) -> int:
 
 
 # ---- few-row matrix product (gemm_stream.cu) ------------------------------------------------
-# Its CTAs keep about 100 KB of W on their way each, so two are resident per SM; K is split over
-# a cluster until the launch fills that many slots.
-STREAM_CTAS_PER_SM = 2
+# Its CTAs keep about 100 KB of W on their way each, so two are resident per SM (the second slot is
+# for the next kernel's CTAs, which fill their rings while this kernel drains).  K is split over a
+# cluster until the launch has one CTA per SM; measured at 8 and at 64 rows: splitting further, to
+# both resident slots, is slower (the gate/up product of 140 blocks cut in two: 8 % on the whole step).
+STREAM_CTAS_PER_SM = 1
 
 
 def stream_target_ctas(device=None) -> int:
