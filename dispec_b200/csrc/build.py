@@ -38,6 +38,10 @@ CORE_SOURCES = [
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# DISPEC_B200_STAMPS=1: a build of its own (another hash) whose weight-streaming product records
+# timestamps at eight points of every CTA's life (measurements only)
+if os.environ.get("DISPEC_B200_STAMPS") == "1":
+    COMMON_FLAGS = COMMON_FLAGS + ["-DDSP_STAMPS"]
 
 _lock = threading.Lock()
 

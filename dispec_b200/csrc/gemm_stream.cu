@@ -34,7 +34,8 @@ namespace {
 using namespace tc;
 constexpr int ROWS_W = 128, BK = 64, UMMA_K = 16;
 constexpr int W_BYTES = ROWS_W * BK * 2;
-constexpr int THREADS = 192;  // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
+// warp 0: TMA; then ISSUERS warps whose first lanes issue the products (the first of them also owns
+// the tensor memory); then four epilogue warps
 constexpr int MAX_SPLITS = 8;
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
@@ -44,7 +45,18 @@ template <int NB> struct Cfg {
   // about 100 KB of ring per CTA, so that two CTAs fit an SM: the next kernel's CTA (programmatic
   // dependent launch) fills its ring with W while this kernel's CTA is still streaming
   static constexpr int STAGES = NB == 16 ? 5 : NB == 32 ? 5 : 4;
-  static constexpr int TMEM_COLS = 2 * NB < 32 ? 32 : 2 * NB;
+  // One thread issues a tcgen05.mma about every 131 cycles, whatever its shape (measured with the
+  // operands resident: 131 cycles at N 16 as at N 256; two issuing threads of different warps get
+  // two per 131 cycles, four get one per 39 at N 16).  A product of 128 x 16 x 16 consumes 4 KB of W,
+  // so a single issuer caps an SM at 55 GB/s, which is what W arrives at.  The four k steps of a
+  // k block therefore belong to ISSUERS threads, each with a partial accumulator of its own, which
+  // the epilogue adds up in a fixed order.  Two CTAs share the SM's 512 columns of tensor memory.
+  static constexpr int PARTS = NB == 64 ? 2 : 4;
+  static constexpr int ISSUERS = PARTS;
+  static constexpr int FIRST_EPI_WARP = 1 + ISSUERS;
+  static constexpr int THREADS = 32 * (1 + ISSUERS + 4);
+  static constexpr int ACC_COLS = PARTS * NB;  // one accumulator buffer
+  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   // K split over a cluster, up to 16 rows of A: every CTA sends the rows of its partial tile to the
   // CTA that finishes them (row m to rank m % splits), into an inbox beside the ring:
   // [source rank][rows per CTA][128] floats, at most (16 + 8) rows
@@ -52,7 +64,24 @@ template <int NB> struct Cfg {
   static constexpr int INBOX_BYTES = PUSH ? (16 + MAX_SPLITS) * ROWS_W * 4 : 0;
 };
 
+// Timestamps for measurements, compiled in only with -DDSP_STAMPS (DISPEC_B200_STAMPS=1 at build
+// time): every CTA of a launch records the global timer at up to twelve points of its life.
+#ifdef DSP_STAMPS
+__device__ unsigned long long g_stamps[1 << 21];
+#define STAMP(pt)                                                                                      \
+  do {                                                                                                 \
+    if (a.stamp_base >= 0) {                                                                           \
+      unsigned long long t__;                                                                          \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                          \
+      g_stamps[(size_t)a.stamp_base + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 12 + (pt)] = t__; \
+    }                                                                                                  \
+  } while (0)
+#else
+#define STAMP(pt)
+#endif
+
 struct Args {
+  long stamp_base;  // first slot of this launch's timestamps, or -1
   const bf16* bias;
   const void* residual;
   long ldr;
@@ -73,8 +102,44 @@ __device__ __forceinline__ void finish(const Args& a, float v, int m, int n) {
   reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>(v);
 }
 
+// The accumulator of this thread's W row: the partial accumulators added in a fixed order.
+template <int NB, int PARTS>
+__device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[NB]) {
+  if constexpr (NB == 16) {
+    // the partial accumulators lie side by side: one load of PARTS x 16 columns, one wait
+    static_assert(PARTS == 4 || PARTS == 2, "loads of 32 or 64 columns");
+    uint32_t all[PARTS * 16];
+    if constexpr (PARTS == 4) {
+      tmem_ld32_nowait(taddr, reinterpret_cast<uint32_t(&)[32]>(all[0]));
+      tmem_ld32_nowait(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(all[32]));
+      tmem_ld_wait();
+    } else {
+      tmem_ld32(taddr, reinterpret_cast<uint32_t(&)[32]>(all[0]));
+    }
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      float sum = __uint_as_float(all[c]);
+#pragma unroll
+      for (int p = 1; p < PARTS; ++p) sum += __uint_as_float(all[p * 16 + c]);
+      v[c] = __float_as_uint(sum);
+    }
+  } else {
+#pragma unroll
+    for (int c0 = 0; c0 < NB; c0 += 32) {
+      uint32_t part[32];
+      tmem_ld32(taddr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+#pragma unroll
+      for (int p = 1; p < PARTS; ++p) {
+        tmem_ld32(taddr + (uint32_t)(p * NB + c0), part);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c0 + c] = __float_as_uint(__uint_as_float(v[c0 + c]) + __uint_as_float(part[c]));
+      }
+    }
+  }
+}
+
 template <int NB, typename TOut>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(Cfg<NB>::THREADS, 2)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const Args a, int* err) {
   using C = Cfg<NB>;
@@ -88,6 +153,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
+  if (threadIdx.x == 0) STAMP(0);  // entry
   if (!a.late_trigger) pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int splits = gridDim.y, split = blockIdx.y;
@@ -100,16 +166,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], C::ISSUERS);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&accum_full[b], 1);
+      mbar_init(&accum_full[b], C::ISSUERS);
       mbar_init(&accum_empty[b], 4);
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == 1) {  // the first issuer warp owns the tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"(C::TMEM_COLS)
                  : "memory");
@@ -137,7 +203,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         mbar_expect_tx(&full_bar[it], C::STAGE_BYTES);
         tma_load_2d(smem + it * C::STAGE_BYTES, &map_w, &full_bar[it], k_of(it), w_row(it));
       }
+      STAMP(10);  // the ring's first tiles of W are requested
       pdl_wait();
+      STAMP(1);  // the predecessor is complete
       for (int it = 0; it < first; ++it)
         tma_load_2d(smem + it * C::STAGE_BYTES + W_BYTES, &map_x, &full_bar[it], k_of(it), 0);
       for (int it = first; it < total; ++it) {
@@ -152,10 +220,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tma_load_2d(dst, &map_w, &full_bar[s], k_of(it), w_row(it));
         tma_load_2d(dst + W_BYTES, &map_x, &full_bar[s], k_of(it), 0);
       }
+      STAMP(7);  // the last tile of W is requested
       if (a.late_trigger) pdl_launch_dependents();
     }
-  } else if (warp == 1) {
+  } else if (warp <= C::ISSUERS) {
     if (lane == 0) {
+      // issuer j owns the k steps j, j + ISSUERS, ... of every k block and the partial accumulator j
+      const int j = warp - 1;
       const uint32_t idesc = umma_idesc(ROWS_W, NB);
       int it = 0, local = 0;
       for (int nb = blockIdx.x; nb < n_blocks && !failed; nb += gridDim.x, ++local) {
@@ -165,7 +236,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * NB);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * C::ACC_COLS + j * NB);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t phase = (it / C::STAGES) & 1;
@@ -174,25 +245,31 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             break;
           }
           tc_fence_after();
+          if (it == 0 && j == 0) STAMP(2);  // the first stage (W tile and slice of A) has landed
           const uint32_t w_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t x_addr = w_addr + W_BYTES;
+          static_assert(BK / UMMA_K % C::ISSUERS == 0, "every issuer takes part in every k block");
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma(tmem_d, umma_desc(w_addr + k * 32), umma_desc(x_addr + k * 32), idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UMMA_K / C::ISSUERS; ++k) {
+            const int step = j + k * C::ISSUERS;
+            umma(tmem_d, umma_desc(w_addr + step * 32), umma_desc(x_addr + step * 32), idesc, (kb | k) != 0);
+          }
           umma_commit(&empty_bar[s]);
         }
         if (failed) break;
         umma_commit(&accum_full[buf]);
+        if (j == 0) STAMP(3);  // the last product of a block is issued
       }
     }
   }
 
-  // ---- epilogue.  Thread (quarter, lane) of warps 2..5 owns W row 32 * quarter + lane of the block.
+  // ---- epilogue.  Thread (quarter, lane) of the four epilogue warps owns W row 32 * quarter + lane of
+  // the block (a warp reaches the 32 lanes of tensor memory that its index modulo 4 names).
   const int quarter = warp & 3;
   const int row = quarter * 32 + lane;
   const bool swiglu = a.epilogue == EPI_SWIGLU;
   if (splits == 1) {
-    if (warp >= 2) {
+    if (warp >= C::FIRST_EPI_WARP) {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
       int local = 0;
       for (int nb = blockIdx.x; nb < n_blocks; nb += gridDim.x, ++local) {
@@ -202,14 +279,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           break;
         }
         tc_fence_after();
+        if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // an accumulator is complete (the last one stays)
         uint32_t v[NB];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * NB);
-        if constexpr (NB == 16) {
-          tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(v));
-        } else {
-#pragma unroll
-          for (int c0 = 0; c0 < NB; c0 += 32) tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
-        }
+        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * C::ACC_COLS), v);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
@@ -263,14 +335,18 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
       if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
     };
-    if (warp >= 2) {
+    if (warp >= C::FIRST_EPI_WARP) {
       fetch_own();
+#ifdef DSP_STAMPS
+      asm volatile("" ::"f"(own_res[0]), "f"(own_bias));  // bias and residual have arrived
+#endif
       const bool ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
       tc_fence_after();
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // the accumulator is complete
       if (ok) {
         uint32_t v[NB];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), reinterpret_cast<uint32_t(&)[16]>(v));
+        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16), v);
         int owner = 0, slot = 0;
 #pragma unroll
         for (int m = 0; m < NB; ++m) {
@@ -288,46 +364,60 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     tc_fence_before();
     __syncthreads();
     cluster.sync();
-    if (warp >= 2 && !failed) {
+    if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // every rank's partial rows have arrived
+    if (warp >= C::FIRST_EPI_WARP && !failed) {
       const int n = blockIdx.x * ROWS_W + row;
-#pragma unroll
-      for (int slot = 0; slot < MAX_OWN; ++slot) {
+      // Sums one row's partial values (all ranks' loads at once, added in rank order) and stores it.
+      // This is the last link before the next kernel may go on, and its instructions run once per
+      // CTA, cold: the usual case, one row per CTA, is straight code; further rows (more rows of A
+      // than ranks) take the loop behind a branch that the usual case never fetches.
+      auto finish_row = [&](int slot, float res) {
         const int m = rank + slot * splits;
-        if (slot < rows_per && m < a.M) {
-          float total = 0.f, total_up = 0.f;
-          for (int sp = 0; sp < splits; ++sp) {
-            const float* src = inbox + (sp * rows_per + slot) * ROWS_W + row;
-            total += src[0];
-            if (swiglu && lane < 16) total_up += src[16];
-          }
-          if (swiglu) {
-            if (lane < 16 && n + 16 < a.N)
-              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                  from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
-          } else if (n < a.N) {
-            // the same order of sums as finish(): bias, then residual
-            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>((total + own_bias) + own_res[slot]);
+        if (m >= a.M) return;
+        float part[MAX_SPLITS], part_up[MAX_SPLITS];
+#pragma unroll
+        for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+          const float* src = inbox + ((sp < splits ? sp : 0) * rows_per + slot) * ROWS_W + row;
+          part[sp] = src[0];
+          part_up[sp] = (swiglu && lane < 16) ? src[16] : 0.f;
+        }
+        float total = 0.f, total_up = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+          if (sp < splits) {
+            total += part[sp];
+            total_up += part_up[sp];
           }
         }
+        if (swiglu) {
+          if (lane < 16 && n + 16 < a.N)
+            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
+                from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+        } else if (n < a.N) {
+          // the same order of sums as finish(): bias, then residual
+          reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>((total + own_bias) + res);
+        }
+      };
+      finish_row(0, own_res[0]);
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(8);  // the first row is stored
+      if (rows_per > 1) {
+#pragma unroll
+        for (int slot = 1; slot < MAX_OWN; ++slot)
+          if (slot < rows_per) finish_row(slot, own_res[slot]);
       }
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // this CTA's rows are stored
     }
   } else {
     // one block per CTA; the cluster adds the partial tiles
     float* red = reinterpret_cast<float*>(smem);  // [NB][128], reuses the ring once it has drained
     bool ok = true;
-    if (warp >= 2) {
+    if (warp >= C::FIRST_EPI_WARP) {
       ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
       tc_fence_after();
       if (ok) {
         uint32_t v[NB];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if constexpr (NB == 16) {
-          tmem_ld16(taddr, reinterpret_cast<uint32_t(&)[16]>(v));
-        } else {
-#pragma unroll
-          for (int c0 = 0; c0 < NB; c0 += 32) tmem_ld32(taddr + c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
-        }
+        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16), v);
 #pragma unroll
         for (int m = 0; m < NB; ++m) red[m * ROWS_W + row] = __uint_as_float(v[m]);
       }
@@ -336,7 +426,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
-    if (warp >= 2 && !failed) {
+    if (warp >= C::FIRST_EPI_WARP && !failed) {
       pdl_wait();
       const int rank = (int)cluster.block_rank();
       const int n = blockIdx.x * ROWS_W + row;
@@ -384,6 +474,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     cluster.sync();  // nobody leaves while its shared memory may still be read
   }
 
+  __syncthreads();
+  if (threadIdx.x == 0) STAMP(6);  // every store of this CTA is issued
   if (failed) {
     if (threadIdx.x == 0) atomicOr(err, DSP_ERR_WAIT_LIMIT);
     // let copies that are still on their way land before the shared memory goes away
@@ -408,7 +500,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, in
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits > 1 ? n_blocks : (n_blocks < 2 * num_sms ? n_blocks : 2 * num_sms), splits, 1);
-  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.blockDim = dim3(C::THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -425,6 +517,43 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, in
   return 0;
 }
 }  // namespace
+
+#ifdef DSP_STAMPS
+namespace {
+long g_stamp_cursor = -1;  // -1: off
+long g_stamp_log[4096][4];  // per launch: first slot, CTAs, N, K
+int g_stamp_launches = 0;
+long stamp_next_base(long ctas, int N, int K) {
+  if (g_stamp_cursor < 0 || g_stamp_cursor + ctas * 12 > (1 << 21) || g_stamp_launches >= 4096) return -1;
+  const long base = g_stamp_cursor;
+  g_stamp_cursor += ctas * 12;
+  g_stamp_log[g_stamp_launches][0] = base;
+  g_stamp_log[g_stamp_launches][1] = ctas;
+  g_stamp_log[g_stamp_launches][2] = N;
+  g_stamp_log[g_stamp_launches][3] = K;
+  ++g_stamp_launches;
+  return base;
+}
+}  // namespace
+// The launches recorded so far: four numbers each (first slot, CTAs, N, K); returns how many.
+extern "C" int dsp_gemm_stream_stamps_log(long* out, int max_launches) {
+  const int n = g_stamp_launches < max_launches ? g_stamp_launches : max_launches;
+  for (int i = 0; i < n; ++i)
+    for (int j = 0; j < 4; ++j) out[i * 4 + j] = g_stamp_log[i][j];
+  return n;
+}
+// Starts (on = 1, from slot 0) or stops recording; returns the slots used so far.
+extern "C" long dsp_gemm_stream_stamps_control(int on) {
+  const long used = g_stamp_cursor < 0 ? 0 : g_stamp_cursor;
+  g_stamp_cursor = on ? 0 : -1;
+  if (on) g_stamp_launches = 0;
+  return used;
+}
+extern "C" int dsp_gemm_stream_stamps_read(unsigned long long* out, long n) {
+  DSP_CUDA(cudaMemcpyFromSymbol(out, g_stamps, (size_t)n * sizeof(unsigned long long)));
+  return 0;
+}
+#endif
 
 // epilogue: 0 plain (bias, residual allowed); 1 SwiGLU over W rows alternating in blocks of 16
 // (C is [M, N/2]; no bias, no residual).  target_ctas: resident CTA slots the launch may fill by
@@ -464,6 +593,10 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   const int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;
   Args a;
+  a.stamp_base = -1;
+#ifdef DSP_STAMPS
+  a.stamp_base = stamp_next_base(splits > 1 ? (long)n_blocks * splits : (n_blocks < 2 * num_sms ? n_blocks : 2 * num_sms), N, K);
+#endif
   a.bias = (const bf16*)bias;
   a.residual = residual;
   a.ldr = ldr;
