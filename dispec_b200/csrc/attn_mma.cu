@@ -39,7 +39,24 @@ constexpr int SW_MASK = (ROW_CHUNKS < 8 ? ROW_CHUNKS : 8) - 1;
 constexpr int ROW_BYTES = ROW_CHUNKS * 16;
 constexpr int TILE_BYTES = 64 * ROW_BYTES;
 
+// Timestamps of the single-token kernel for measurements, compiled in only with -DDSP_STAMPS.
+#ifdef DSP_STAMPS
+__device__ unsigned long long g_attn_stamps[1 << 20];
+#define ASTAMP(pt)                                                                                            \
+  do {                                                                                                        \
+    if (p.stamp_base >= 0) {                                                                                  \
+      unsigned long long t__;                                                                                 \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                                 \
+      g_attn_stamps[(size_t)p.stamp_base +                                                                    \
+                    (((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 12 + (pt)] = t__; \
+    }                                                                                                         \
+  } while (0)
+#else
+#define ASTAMP(pt)
+#endif
+
 struct Params {
+  long stamp_base;
   const bf16* q;
   long q_stride;
   const bf16* k_pool;
@@ -411,6 +428,7 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* c, co
 
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  if (threadIdx.x == 0) ASTAMP(0);  // entry
   const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g4 = lane >> 2, c4 = lane & 3;
@@ -458,27 +476,26 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const bool cached = n_pages <= DEC_MAXP;
   if (cached)
     for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = table[first_page + i];
-  // keys of a tile whose page id lies outside the pool (bit r: key r of the tile), per warp and ring
-  // slot: written when the tile is requested, read when its scores are masked (such keys are hidden)
-  __shared__ uint32_t bad_keys[4][DSTAGES];
-  bool warp_bad = false;  // this warp met such a page: only then are the masks written and read
   __syncthreads();
 
   // a tile lies within one page when the page size is a multiple of the tile (the usual case): one
   // page lookup per tile, and a lane's pieces differ by a constant row stride
   const bool tile_in_page = p.page_size % DK == 0;
+  // Tiles of this warp (bit n: its n-th tile, the first 32) that touch a page id outside the pool:
+  // recorded when the tile is requested, and the whole tile of 16 keys is hidden from the softmax
+  // (its rows were zero-filled, not loaded).  Nothing of this is in the loops over keys.
+  uint32_t bad_tiles = 0u;
   auto load_tile = [&](int kt, int stage) {  // by one warp: consecutive lanes take consecutive 16-byte pieces of a row
     const uint32_t k_s = ring + stage * 2 * DEC_TILE_BYTES, v_s = k_s + DEC_TILE_BYTES;
+    const int nth = (kt - (my_begin + warp)) >> 2;
     if (tile_in_page) {
       const int b0 = kt * DK;
       const int lp = b0 / p.page_size;
       const int page = cached ? pages_s[lp - first_page] : table[lp];
       const bool page_ok = page >= 0 && page < p.num_pages;
-      const bool bad = !page_ok && b0 <= pos && b0 + DK > lo;  // the same for every lane
-      if (bad) warp_bad = true;
-      if (warp_bad && lane == 0) {
-        if (bad) atomicOr(p.err, DSP_ERR_BAD_PAGE);
-        bad_keys[warp][stage] = bad ? 0xffffu : 0u;
+      if (!page_ok && b0 <= pos && b0 + DK > lo) {  // the same for every lane
+        if (lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        if (nth < 32) bad_tiles |= 1u << nth;
       }
       const size_t base = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + (b0 % p.page_size)) * D;
       constexpr int ROWS_PER_PASS = 32 / CHUNKS > 0 ? 32 / CHUNKS : 1;
@@ -505,7 +522,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       }
       return;
     }
-    uint32_t bad_mine = 0u;
+    bool met_bad = false;
 #pragma unroll 4
     for (int i = lane; i < DK * CHUNKS; i += 32) {
       const int r = i / CHUNKS, chunk = i % CHUNKS;
@@ -518,7 +535,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
         const int page = cached ? pages_s[lp - first_page] : table[lp];
         if (page < 0 || page >= p.num_pages) {
           if (chunk == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          bad_mine |= 1u << r;
+          met_bad = true;
           valid = false;
         } else {
           off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D + chunk * 8;
@@ -527,11 +544,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       cp_async16(k_s + sw(r, chunk), p.k_pool + off, valid);
       cp_async16(v_s + sw(r, chunk), p.v_pool + off, valid);
     }
-    if (__any_sync(0xffffffffu, bad_mine != 0u)) warp_bad = true;
-    if (warp_bad) {
-      bad_mine = __reduce_or_sync(0xffffffffu, bad_mine);
-      if (lane == 0) bad_keys[warp][stage] = bad_mine;
-    }
+    if (__any_sync(0xffffffffu, met_bad) && nth < 32) bad_tiles |= 1u << nth;
   };
 
   // this warp's tiles: my_begin + warp, + 4, ...; the tile that holds the newest position (always the
@@ -547,7 +560,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     ++issued;
   }
 
+  if (tid == 0) ASTAMP(1);  // page ids and the first tiles are requested
   pdl_wait();
+  if (tid == 0) ASTAMP(2);  // the predecessor is complete
   // the next kernel (the output projection) may start now and not earlier: its weight ring would
   // compete with the key tiles requested above (measured: 1.314 ms -> 1.294 ms per decode step)
   pdl_launch_dependents();
@@ -604,6 +619,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
   cp_async_wait<0>();
   __syncthreads();  // Q is complete for every warp (and this warp's first tiles with it)
+  if (tid == 0) ASTAMP(3);  // Q and the first tiles have landed
 
   float o[D / 8][4];
 #pragma unroll
@@ -639,12 +655,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       const int lp = pos / p.page_size;
       const int page = cached ? pages_s[lp - first_page] : table[lp];
       const bool page_ok = page >= 0 && page < p.num_pages;
-      if (!page_ok) {  // not stored, and hidden like every key of such a page
-        if (lane == 0) {
-          atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          bad_keys[warp][stage] = (warp_bad ? bad_keys[warp][stage] : 0u) | (1u << r);
-        }
-        warp_bad = true;
+      if (!page_ok) {  // not stored, and hidden with its tile
+        if (lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        if (n < 32) bad_tiles |= 1u << n;
       }
       const size_t dst = (((size_t)(page_ok ? page : 0) * p.KVH + kvh) * p.page_size + pos % p.page_size) * D;
       bf16* k_out = const_cast<bf16*>(p.k_pool) + dst;
@@ -686,11 +699,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       mma_bf16(s[0], qa[kk], b[0], b[1]);
       mma_bf16(s[1], qa[kk], b[2], b[3]);
     }
-    uint32_t bad = 0u;
-    if (warp_bad) {  // never in a run with sound page tables
-      __syncwarp();
-      bad = bad_keys[warp][stage];  // written by this warp when it requested the tile
-    }
+    const int pos_t = (n < 32 && ((bad_tiles >> n) & 1u)) ? -1 : pos;  // no key of such a tile is visible
     float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < DK / 8; ++nt)
@@ -698,7 +707,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
         const int key = kt * DK + nt * 8 + 2 * c4 + (e & 1);
-        const bool vis = row_ok[r] && key <= pos && key >= lo && !((bad >> (nt * 8 + 2 * c4 + (e & 1))) & 1u);
+        const bool vis = row_ok[r] && key <= pos_t && key >= lo;
         const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
         s[nt][e] = v;
         tmax[r] = fmaxf(tmax[r], v);
@@ -757,6 +766,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
+  if (tid == 0) ASTAMP(4);  // warp 0 is through its key tiles
   // ---- level 1: the warp's partial into its own (now free) ring memory, merged over the CTA's warps
   __syncwarp();
   {
@@ -775,6 +785,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     }
   }
   __syncthreads();
+  if (tid == 0) ASTAMP(5);  // every warp of the CTA is through
   const bool last_level = nsplit == 1;
   for (int row = warp; row < G; row += 4) {
     float m_w[4], l_w[4];
@@ -834,8 +845,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
   if (last_level) return;
   // ---- level 2: the CTAs of the cluster; the rows are dealt to its warps
+  if (tid == 0) ASTAMP(6);  // the CTA's partial is in its shared memory
   cg::cluster_group cluster = cg::this_cluster();
   cluster.sync();
+  if (tid == 0) ASTAMP(7);  // every CTA of the cluster is there
   for (int row = split * 4 + warp; row < G; row += nsplit * 4) {
     float m_c[8], l_c[8];
     const float* remote[8];
@@ -889,9 +902,36 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       if (d < D) dst[d] = __float2bfloat16(acc[j] * inv);
     }
   }
+  if (tid == 0) ASTAMP(8);  // this CTA's rows are stored
   cluster.sync();  // nobody leaves while its partials may still be read
+  if (tid == 0) ASTAMP(9);  // end
 }
 }  // namespace
+
+#ifdef DSP_STAMPS
+namespace {
+long g_astamp_cursor = -1;
+long g_astamp_log[4096][2];
+int g_astamp_launches = 0;
+}  // namespace
+extern "C" long DSP_CAT(dsp_attn_stamps_control_d, DSP_HEAD_DIM)(int on) {
+  const long used = g_astamp_cursor < 0 ? 0 : g_astamp_cursor;
+  g_astamp_cursor = on ? 0 : -1;
+  if (on) g_astamp_launches = 0;
+  return used;
+}
+extern "C" int DSP_CAT(dsp_attn_stamps_log_d, DSP_HEAD_DIM)(long* out, int max_launches) {
+  const int n = g_astamp_launches < max_launches ? g_astamp_launches : max_launches;
+  for (int i = 0; i < n; ++i) {
+    out[i * 2] = g_astamp_log[i][0];
+    out[i * 2 + 1] = g_astamp_log[i][1];
+  }
+  return n;
+}
+extern "C" int DSP_CAT(dsp_attn_stamps_read_d, DSP_HEAD_DIM)(unsigned long long* out, long n) {
+  return cudaMemcpyFromSymbol(out, g_attn_stamps, (size_t)n * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // Runs tiles [tile_offset, tile_offset + num_tiles) of the tile list.  With num_splits > 1 and no
 // cluster the partials go to part_o / part_ml, [row][num_splits], and dsp_attn_combine must follow.
@@ -961,7 +1001,20 @@ extern "C" int DSP_CAT(dsp_attn_mma_d, DSP_HEAD_DIM)(
   }
   dim3 grid(num_tiles, KVH, num_splits);
   // single decoded tokens whose group fits one 16-row tile: the warp-parallel kernel
+  p.stamp_base = -1;
   if (decode_only && p.G <= 16 && num_splits <= 8 && DEC_SMEM <= 227 * 1024) {
+#ifdef DSP_STAMPS
+    {
+      const long ctas = (long)num_tiles * num_outer * KVH * num_splits;
+      if (g_astamp_cursor >= 0 && g_astamp_cursor + ctas * 12 <= (1 << 20) && g_astamp_launches < 4096) {
+        p.stamp_base = g_astamp_cursor;
+        g_astamp_log[g_astamp_launches][0] = g_astamp_cursor;
+        g_astamp_log[g_astamp_launches][1] = ctas;
+        ++g_astamp_launches;
+        g_astamp_cursor += ctas * 12;
+      }
+    }
+#endif
     static bool dec_configured = false;
     if (!dec_configured) {
       if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM) != cudaSuccess)

@@ -36,7 +36,8 @@ using namespace tc;
 
 constexpr int D = DSP_HEAD_DIM;
 static_assert(D == 64 || D == 128, "this kernel is built for head sizes 64 and 128");
-constexpr int BM = 128, BN = 64, THREADS = 320, STAGES = 4;
+constexpr int BM = 128, BN = 64, THREADS = 352, STAGES = 4;
+constexpr int PV_WARP = 10;  // warp 0: TMA, warp 1: issues S = Q K^T, warps 2-9: softmax, warp 10: issues O += P V
 constexpr int KD = D / 64;            // 64-wide slices of the head dimension (128-byte rows)
 constexpr int Q_SLICE = BM * 128;     // bytes of one slice of the Q tile
 constexpr int KV_SLICE = BN * 128;    // bytes of one slice of a K or V tile
@@ -251,15 +252,12 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
       }
     }
   } else if (warp == 1) {
-    // ---- product issuer
+    // ---- issuer of the score products
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(BM, BN);
-      const uint32_t idesc_o = umma_idesc(BM, D) | (1u << 16);  // B (values) is N-major
       // descriptors are linear in the address: the tile's base once, a constant per k step
       const uint64_t q_desc = umma_desc(smem_u32(q_s));
       const uint64_t k_desc0 = umma_desc(smem_u32(k_s));
-      const uint64_t v_desc0 = umma_desc_mn(smem_u32(v_s), KV_SLICE);
-      const uint64_t p_desc0 = umma_desc(smem_u32(p_s));
       auto issue_scores = [&](int i) {
         const int s = i % STAGES;
         tc_fence_after();
@@ -272,42 +270,41 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         }
         umma_commit(&s_full[i & 1]);
       };
-      auto issue_output = [&](int i) {
-        const int g = i & 1, s = i % STAGES;
+      // One thread issues a tcgen05.mma about every 131 cycles whatever its shape, so the eight
+      // products of S and the four of O += P V of a key tile have a thread each (this one and
+      // warp PV_WARP): a tile then costs the issue of eight products, not of twelve.
+      // The scores of tile a need K[a] and, from the third tile on, that the group has read
+      // S[a % 2] (tile a - 2).
+      bool ok = true;
+      for (int a = 0; a < n_kt && ok; ++a) {
+        ok = mbar_wait(&kv_full[a % STAGES], (a / STAGES) & 1) &&
+             (a < 2 || mbar_wait(&s_free[a & 1], ((a - 2) >> 1) & 1));
+        if (ok) issue_scores(a);
+      }
+      if (!ok) failed = 1;
+    }
+  } else if (warp == PV_WARP) {
+    // ---- issuer of the output products: O[g] += P[b] V[b] needs P[b] (written, O rescaled, dead value rows zeroed)
+    if (lane == 0) {
+      const uint32_t idesc_o = umma_idesc(BM, D) | (1u << 16);  // B (values) is N-major
+      const uint64_t v_desc0 = umma_desc_mn(smem_u32(v_s), KV_SLICE);
+      const uint64_t p_desc0 = umma_desc(smem_u32(p_s));
+      bool ok = true;
+      for (int b = 0; b < n_kt && ok; ++b) {
+        ok = mbar_wait(&p_full[b & 1], (b >> 1) & 1);
+        if (!ok) break;
+        const int g = b & 1, st = b % STAGES;
         tc_fence_after();
-        const uint64_t v_desc = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
+        const uint64_t v_desc = v_desc0 + (uint64_t)(st * (KV_BYTES >> 4));
         const uint64_t p_desc = p_desc0 + (uint64_t)(g * (P_BYTES >> 4));
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
           umma(tmem_base + (uint32_t)(O_COL + g * D), p_desc + (uint64_t)(k * 2), v_desc + (uint64_t)(k * 128), idesc_o,
-               (i >= 2) || k != 0);
-        umma_commit(&kv_empty[s]);
+               (b >= 2) || k != 0);
+        // the scores of this tile were complete before its P was written, so every product that
+        // read the stage is behind these commits
+        umma_commit(&kv_empty[st]);
         umma_commit(&o_done[g]);
-      };
-      // Work in whatever order it becomes ready: the scores of tile a need K[a] and, from the third
-      // tile on, that the group has read S[a % 2] (tile a - 2); the output product of tile b needs P[b].
-      int a = 0, b = 0;
-      uint32_t polls = 0;
-      bool ok = true;
-      while (b < n_kt) {
-        bool progress = false;
-        if (a < n_kt && mbar_test(&kv_full[a % STAGES], (a / STAGES) & 1) &&
-            (a < 2 || mbar_test(&s_free[a & 1], ((a - 2) >> 1) & 1))) {
-          issue_scores(a);
-          ++a;
-          progress = true;
-        }
-        if (mbar_test(&p_full[b & 1], (b >> 1) & 1)) {
-          issue_output(b);
-          ++b;
-          progress = true;
-        }
-        if (progress) {
-          polls = 0;
-        } else if (++polls > (1u << 24)) {
-          ok = false;
-          break;
-        }
       }
       if (!ok) failed = 1;
     }

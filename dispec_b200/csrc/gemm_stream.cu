@@ -51,7 +51,7 @@ template <int NB> struct Cfg {
   // so a single issuer caps an SM at 55 GB/s, which is what W arrives at.  The four k steps of a
   // k block therefore belong to ISSUERS threads, each with a partial accumulator of its own, which
   // the epilogue adds up in a fixed order.  Two CTAs share the SM's 512 columns of tensor memory.
-  static constexpr int PARTS = NB == 64 ? 2 : 4;
+  static constexpr int PARTS = NB == 16 ? 4 : 2;
   static constexpr int ISSUERS = PARTS;
   static constexpr int FIRST_EPI_WARP = 1 + ISSUERS;
   static constexpr int THREADS = 32 * (1 + ISSUERS + 4);
@@ -150,6 +150,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
   __shared__ __align__(8) uint64_t accum_full[2];
   __shared__ __align__(8) uint64_t accum_empty[2];
+  __shared__ __align__(8) uint64_t inbox_bar;  // counts the bytes of partial rows other ranks send here
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -172,6 +173,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       mbar_init(&accum_full[b], C::ISSUERS);
       mbar_init(&accum_empty[b], 4);
     }
+    mbar_init(&inbox_bar, 1);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -312,9 +314,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
   } else if constexpr (C::PUSH) {
     // one block per CTA; every CTA sends each row of its partial tile to the CTA that finishes that
-    // row (plain remote stores, nobody waits for them), one cluster barrier, then each CTA adds what
-    // arrived in its own shared memory in rank order.  No CTA reads another's memory, so none has to
-    // wait for the others before it leaves.
+    // row: remote stores that count their bytes on a barrier of the receiving CTA.  A CTA waits only
+    // for the bytes that are due in its own inbox (never for the whole cluster), adds them in rank
+    // order and leaves; nobody reads another's memory.
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int rows_per = (a.M + splits - 1) / splits;
@@ -351,8 +353,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int m = 0; m < NB; ++m) {
           if (m < a.M) {
-            float* dst = cluster.map_shared_rank(inbox, owner) + ((rank * rows_per + slot) * ROWS_W + row);
-            *dst = __uint_as_float(v[m]);
+            const uint32_t dst = mapa_u32(smem_u32(inbox + ((rank * rows_per + slot) * ROWS_W + row)), (uint32_t)owner);
+            st_async_b32(dst, v[m], mapa_u32(smem_u32(&inbox_bar), (uint32_t)owner));
           }
           if (++owner == splits) {
             owner = 0;
@@ -361,9 +363,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     }
-    tc_fence_before();
-    __syncthreads();
-    cluster.sync();
+    // the rows this CTA finishes: rank, rank + splits, ...; every rank sends 128 floats of each
+    const int rows_own = rank < a.M ? (a.M - rank + splits - 1) / splits : 0;
+    if (threadIdx.x == 32 * C::FIRST_EPI_WARP) mbar_expect_tx(&inbox_bar, (uint32_t)(splits * rows_own * ROWS_W * 4));
+    if (warp >= C::FIRST_EPI_WARP && !__all_sync(0xffffffffu, mbar_wait(&inbox_bar, 0))) failed = 1;
     if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // every rank's partial rows have arrived
     if (warp >= C::FIRST_EPI_WARP && !failed) {
       const int n = blockIdx.x * ROWS_W + row;
@@ -400,9 +403,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       };
       finish_row(0, own_res[0]);
       if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(8);  // the first row is stored
-      if (rows_per > 1) {
+      if (rows_per > 1) finish_row(1, own_res[1]);  // up to 16 rows over 8 ranks
+      if (rows_per > 2) {
 #pragma unroll
-        for (int slot = 1; slot < MAX_OWN; ++slot)
+        for (int slot = 2; slot < MAX_OWN; ++slot)
           if (slot < rows_per) finish_row(slot, own_res[slot]);
       }
       if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // this CTA's rows are stored
@@ -474,6 +478,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     cluster.sync();  // nobody leaves while its shared memory may still be read
   }
 
+  // every warp is through with the tensor memory before it is given back
+  tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) STAMP(6);  // every store of this CTA is issued
   if (failed) {
