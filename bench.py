@@ -327,12 +327,110 @@ def measure_shape(shape: str, args, pk: dict) -> dict:
     return out
 
 
+def mma_issue_rate() -> dict:
+    """Cycles one thread needs per tcgen05.mma (128 x N x 16), for 1, 2 and 4 issuing threads."""
+    import ctypes
+    import torch
+    from dispec_b200.ops import library as L
+    out = torch.zeros(3, dtype=torch.int64, device="cuda:0")
+    table = {}
+    for n in (16, 64, 128):
+        for issuers in (1, 2, 4):
+            for _ in range(2):  # the second run is warm
+                L.check(L.core().dsp_selftest_mma_issue_rate(n, issuers, 200, ctypes.c_void_p(out.data_ptr()),
+                                                             L.stream_handle()))
+            issue, done, ok = out.tolist()
+            table[f"n{n}_issuers{issuers}"] = {"cycles_per_mma_per_thread": round(issue / 800, 1),
+                                               "cycles_per_mma_overall": round(done / 800 / issuers, 1), "ok": bool(ok)}
+    return {"only": "mma-rate", "shape_of_one_product": "128 x N x 16, bfloat16, operands in shared memory", "table": table}
+
+
+def decode_timeline(args) -> dict:
+    """Where the time of a decode step's kernels goes: the weight-streaming products and the
+    single-token attention of a captured step (few layers of the recorded shape) record the global
+    timer at points of every CTA's life; needs a build with DISPEC_B200_STAMPS=1 (set before the
+    package is imported, which main() does for this mode).  Microseconds, mean over CTAs / slowest CTA."""
+    import ctypes
+    import numpy as np
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner, SeqEntry
+    from dispec_b200.ops import library as L
+    from dispec_b200.weights import load_random_model
+    batch, layers = args.batch, args.layers or 4
+    cfg = dict(BENCH_CONFIG, num_hidden_layers=layers)
+    model = load_random_model(load_model_config(cfg), SEED, STD, "bfloat16", "cuda:0")
+    runner = ModelRunner(model, page_size=PAGE_SIZE, num_pages=batch * 90, max_num_seqs=max(batch, 8), cuda_graph=True)
+    ids = [f"r{i}" for i in range(batch)]
+    for rid, p in zip(ids, random_prompts(batch, PROMPT_LEN, cfg["vocab_size"], 11)):
+        runner.admit(rid)
+        runner.step([SeqEntry(rid, p, 0, [])])
+    core, attn = L.core(), L.attention_library(cfg["head_dim"])
+    a_ctl = getattr(attn, f"dsp_attn_stamps_control_d{cfg['head_dim']}")
+    a_log = getattr(attn, f"dsp_attn_stamps_log_d{cfg['head_dim']}")
+    a_read = getattr(attn, f"dsp_attn_stamps_read_d{cfg['head_dim']}")
+    core.dsp_gemm_stream_stamps_control.restype = ctypes.c_long
+    a_ctl.restype = ctypes.c_long
+    core.dsp_gemm_stream_stamps_control(1)
+    a_ctl(1)
+    pos = PROMPT_LEN
+    for _ in range(6):  # the captured step is replayed last: its launches' stamps are the ones read
+        runner.step([SeqEntry(rid, [5], pos, [0]) for rid in ids])
+        pos += 1
+    torch.cuda.synchronize()
+
+    def read(control, log_fn, read_fn, width):
+        log = (ctypes.c_long * (4096 * width))()
+        n = log_fn(log, 4096)
+        used = control(0)
+        buf = (ctypes.c_ulonglong * max(used, 1))()
+        read_fn(buf, ctypes.c_long(used))
+        stamps = np.frombuffer(buf, dtype=np.uint64).astype(np.int64)
+        return [tuple(log[i * width + j] for j in range(width)) for i in range(n)], stamps
+
+    g_launches, g = read(core.dsp_gemm_stream_stamps_control, core.dsp_gemm_stream_stamps_log,
+                         core.dsp_gemm_stream_stamps_read, 4)
+    a_launches, a = read(a_ctl, a_log, a_read, 2)
+
+    def phase(s, first, last):
+        m = (s[:, first] > 0) & (s[:, last] > 0)
+        v = (s[m, last] - s[m, first]) / 1000.0
+        return [round(float(v.mean()), 2), round(float(v.max()), 2)] if m.any() else None
+
+    kinds = {(cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]: "qkv",
+             2 * cfg["intermediate_size"]: "gate_up", cfg["vocab_size"]: "head"}
+    products, prev_end = {}, None
+    for base, ctas, N, K in g_launches[-(4 * layers + 1):][4:]:  # the first layer follows the embedding: left out
+        s = g[base:base + ctas * 12].reshape(ctas, 12)
+        name = kinds.get(N, "o_proj" if K == cfg["num_attention_heads"] * cfg["head_dim"] else "down")
+        row = {"ctas": int(ctas),
+               "end_of_previous_product_to_wait": round(float(s[:, 1].min() - prev_end) / 1000.0, 2) if prev_end else None,
+               "wait_to_first_stage": phase(s, 1, 2), "first_stage_to_last_product_issued": phase(s, 2, 3),
+               "last_w_requested_to_last_product": phase(s, 7, 3), "accumulator_to_partials_arrived": phase(s, 4, 5),
+               "partials_arrived_to_rows_stored": phase(s, 5, 9), "wait_to_end": phase(s, 1, 6)}
+        prev_end = s[:, 6].max()
+        products.setdefault(name, []).append(row)
+    attention = []
+    for base, ctas in a_launches[-layers:][1:]:
+        s = a[base:base + ctas * 12].reshape(ctas, 12)
+        attention.append({"ctas": int(ctas), "wait_to_q_ready": phase(s, 2, 3), "q_ready_to_warp0_done": phase(s, 3, 4),
+                          "warp0_done_to_cta_done": phase(s, 4, 5), "cta_done_to_partial": phase(s, 5, 6),
+                          "partial_to_cluster": phase(s, 6, 7), "cluster_to_stored": phase(s, 7, 8),
+                          "stored_to_end": phase(s, 8, 9), "wait_to_end": phase(s, 2, 9)})
+    return {"only": "timeline", "batch": batch, "layers": layers, "unit": "us, [mean over CTAs, slowest CTA]",
+            "products": {k: v[-1] for k, v in products.items()}, "attention": attention[-1] if attention else None}
+
+
 def run_ours(args) -> dict:
     import torch
     from dispec_b200 import load_model_config
     from dispec_b200.engine import ModelRunner
     from dispec_b200.weights import load_random_model
 
+    if args.only == "mma-rate":
+        return mma_issue_rate()
+    if args.only == "timeline":
+        return decode_timeline(args)
     cfg_dict = dict(BENCH_CONFIG)
     seed = SEED
     if args.shape != "1.5b":
@@ -502,8 +600,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="profiling aid: run one phase only and print a short line")
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate"], default=None,
+                    help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
+                         "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
+                         "tcgen05.mma for one to four issuing threads")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")
@@ -513,6 +613,8 @@ def main() -> int:
     ap.add_argument("--no-other-shapes", action="store_true",
                     help="skip the 7B and 14B points of the default run (shorter run while developing)")
     args = ap.parse_args()
+    if args.only == "timeline":
+        os.environ["DISPEC_B200_STAMPS"] = "1"  # before the package builds or loads its libraries
     globals()["PAGE_SIZE"] = args.page_size
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

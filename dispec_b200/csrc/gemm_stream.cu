@@ -45,12 +45,16 @@ template <int NB> struct Cfg {
   // about 100 KB of ring per CTA, so that two CTAs fit an SM: the next kernel's CTA (programmatic
   // dependent launch) fills its ring with W while this kernel's CTA is still streaming
   static constexpr int STAGES = NB == 16 ? 5 : NB == 32 ? 5 : 4;
-  // One thread issues a tcgen05.mma about every 131 cycles, whatever its shape (measured with the
-  // operands resident: 131 cycles at N 16 as at N 256; two issuing threads of different warps get
-  // two per 131 cycles, four get one per 39 at N 16).  A product of 128 x 16 x 16 consumes 4 KB of W,
-  // so a single issuer caps an SM at 55 GB/s, which is what W arrives at.  The four k steps of a
-  // k block therefore belong to ISSUERS threads, each with a partial accumulator of its own, which
-  // the epilogue adds up in a fixed order.  Two CTAs share the SM's 512 columns of tensor memory.
+  // One thread's turn of the ring (wait for the stage, fence, four products, commit) takes about
+  // 0.3 us, of which the tensor pipe is busy a third (a product of 128 x 16 x 16 every 55 cycles from
+  // one issuing thread, every 39 from two: `bench.py --only mma-rate`); a W tile of 16 KB per 0.3 us is
+  // 55 GB/s, which is what an SM's share of the memory bandwidth delivers.  The four k steps of a k
+  // block therefore belong to ISSUERS threads of different warps, each with a partial accumulator of
+  // its own, so that their turns overlap; the epilogue adds the partial accumulators up in a fixed
+  // order.  Measured on the captured decode step at 8 rows: first stage to last product 0.96 -> 0.7 us
+  // on the small products, 8.1 -> 7.6 us on gate/up, 5.75 -> 4.7 us on down.  (Whole k blocks dealt
+  // to five issuers that own a stage of the ring each measured 1 % slower on the whole step.)  Two
+  // CTAs share the SM's 512 columns of tensor memory.
   static constexpr int PARTS = NB == 16 ? 4 : 2;
   static constexpr int ISSUERS = PARTS;
   static constexpr int FIRST_EPI_WARP = 1 + ISSUERS;

@@ -31,3 +31,73 @@ extern "C" int dsp_selftest_wait_limit(int tries, int* ran_out, cudaStream_t str
   DSP_CHECK_LAUNCH("dsp_selftest_wait_limit");
   return 0;
 }
+
+// ---- how often one thread can issue tcgen05.mma --------------------------------------------------
+// A measurement, kept with the library because the weight-streaming product is laid out by its result: `issuers` threads
+// of different warps each issue `iters` products of 128 x n x 16 (bfloat16, operands resident in
+// shared memory, an accumulator of its own each) and report the cycles per product of the first.
+namespace {
+__global__ void __launch_bounds__(128, 1) mma_issue_rate_kernel(int n, int iters, int issuers, long long* out) {
+  using namespace tc;
+  extern __shared__ unsigned char rate_smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rate_smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 48 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, issuers);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if ((threadIdx.x & 31) == 0 && warp < issuers) {
+    const uint32_t idesc = umma_idesc(128, n);
+    const uint32_t a_addr = smem_u32(smem), b_addr = smem_u32(smem + 16384);
+    const long long t0 = clock64();
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma(tmem_base + (uint32_t)(warp * 128), umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, i > 0 || k > 0);
+    }
+    const long long t1 = clock64();
+    umma_commit(&bar);
+    const bool ok = mbar_wait(&bar, 0);  // bounded
+    const long long t2 = clock64();
+    if (warp == 0) {
+      out[0] = t1 - t0;
+      out[1] = t2 - t0;
+      out[2] = ok ? 1 : 0;
+    }
+  }
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+}  // namespace
+
+// out: three device integers (64-bit): cycles until the first issuer's last product was issued, cycles
+// until all products had completed, and 1 if the bounded wait for them returned in time.
+// n: 16..128 in steps of 16; issuers: 1..4; iters: k blocks of four products each, at most 4096.
+extern "C" int dsp_selftest_mma_issue_rate(int n, int issuers, int iters, long long* out, cudaStream_t stream) {
+  DSP_REQUIRE(n >= 16 && n <= 128 && n % 16 == 0, "dsp_selftest_mma_issue_rate: n=%d outside 16..128 in steps of 16", n);
+  DSP_REQUIRE(issuers >= 1 && issuers <= 4 && iters >= 1 && iters <= 4096 && out != nullptr,
+              "dsp_selftest_mma_issue_rate: issuers=%d or iters=%d out of range", issuers, iters);
+  static bool configured = false;
+  if (!configured) {
+    DSP_CUDA(cudaFuncSetAttribute(mma_issue_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    configured = true;
+  }
+  mma_issue_rate_kernel<<<1, 128, 64 * 1024, stream>>>(n, iters, issuers, out);
+  DSP_CHECK_LAUNCH("dsp_selftest_mma_issue_rate");
+  return 0;
+}
