@@ -45,8 +45,24 @@ def make_rng(params: SamplingParams, generator=None) -> random.Random:
 class Sampler:
     """Samples one token per logits row, each row with its own parameters and generator."""
 
-    def __init__(self, device):
+    def __init__(self, device, capacity: int = 256):
         self.device = device
+        # temperature, top_k (as int32 bits), top_p and the uniform number of every row: pinned host
+        # buffers used in turn (a copy may still be on its way when the next step is prepared) and one
+        # device buffer; nothing is allocated per step
+        self._capacity = 0
+        self._host: list = []
+        self._events: list = []
+        self._dev = None
+        self._turn = 0
+        self._grow(capacity)
+
+    def _grow(self, n: int) -> None:
+        cap = max(n, 2 * self._capacity)
+        self._host = [torch.empty((4, cap), dtype=torch.float32, pin_memory=True) for _ in range(3)]
+        self._events = [None, None, None]
+        self._dev = torch.empty((4, cap), dtype=torch.float32, device=self.device)
+        self._capacity = cap
 
     def sample(self, logits: torch.Tensor, params: list, rngs: list) -> list[int]:
         if logits.shape[0] == 0:
@@ -62,15 +78,25 @@ class Sampler:
             return torch.empty((0,), dtype=torch.int32, device=logits.device)
         if all(p.greedy for p in params):
             return ops.argmax(logits)
-        host = torch.empty((4, n), dtype=torch.float32, pin_memory=True)
+        if n > self._capacity:
+            self._grow(n)
+        self._turn = (self._turn + 1) % len(self._host)
+        if self._events[self._turn] is not None:
+            self._events[self._turn].synchronize()
+        host = self._host[self._turn]
+        rows = host.numpy()
+        top_k = rows[1].view("int32")
         for i, (p, rng) in enumerate(zip(params, rngs)):
-            host[0, i] = p.temperature
-            host[1, i] = float(p.top_k)
-            host[2, i] = p.top_p
-            host[3, i] = 0.0 if p.greedy else min(rng.random(), _BELOW_ONE)
-        dev = host.to(self.device, non_blocking=True)
-        top_k = dev[1].to(torch.int32)
-        return ops.sample(logits, dev[0].contiguous(), top_k, dev[2].contiguous(), dev[3].contiguous())
+            rows[0, i] = p.temperature
+            top_k[i] = p.top_k
+            rows[2, i] = p.top_p
+            rows[3, i] = 0.0 if p.greedy else min(rng.random(), _BELOW_ONE)
+        dev = self._dev
+        dev[:, :n].copy_(host[:, :n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._events[self._turn] = event
+        return ops.sample(logits, dev[0, :n], dev[1, :n].view(torch.int32), dev[2, :n], dev[3, :n])
 
 
 def sample(logits: torch.Tensor, params: SamplingParams, generator=None) -> torch.Tensor:
