@@ -413,10 +413,11 @@ def decode_timeline(args) -> dict:
     attention = []
     for base, ctas in a_launches[-layers:][1:]:
         s = a[base:base + ctas * 12].reshape(ctas, 12)
+        # the cluster merges by sending rows to their owners (the shape of this run takes that path)
         attention.append({"ctas": int(ctas), "wait_to_q_ready": phase(s, 2, 3), "q_ready_to_warp0_done": phase(s, 3, 4),
-                          "warp0_done_to_cta_done": phase(s, 4, 5), "cta_done_to_partial": phase(s, 5, 6),
-                          "partial_to_cluster": phase(s, 6, 7), "cluster_to_stored": phase(s, 7, 8),
-                          "stored_to_end": phase(s, 8, 9), "wait_to_end": phase(s, 2, 9)})
+                          "warp0_done_to_cta_done": phase(s, 4, 5), "cta_done_to_rows_merged": phase(s, 5, 8),
+                          "rows_merged_to_sent": phase(s, 8, 6), "sent_to_all_arrived": phase(s, 6, 7),
+                          "all_arrived_to_end": phase(s, 7, 9), "wait_to_end": phase(s, 2, 9)})
     return {"only": "timeline", "batch": batch, "layers": layers, "unit": "us, [mean over CTAs, slowest CTA]",
             "products": {k: v[-1] for k, v in products.items()}, "attention": attention[-1] if attention else None}
 

@@ -18,7 +18,7 @@
 // on pages that were given back, are zero-filled, never read.
 #include <cooperative_groups.h>
 
-#include "common.cuh"
+#include "tcgen05_common.cuh"  // bounded mbarrier waits, cluster addresses, counted remote stores
 
 namespace cg = cooperative_groups;
 
@@ -89,6 +89,13 @@ __device__ __forceinline__ uint32_t sw(int row, int chunk) {
 __device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem, bool valid) {
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "r"(bytes));
+}
+// the same for data that is read once per step (the cache's keys and values in decoding): its
+// lines are the first to leave the L2
+__device__ __forceinline__ void cp_async16_once(uint32_t smem, const void* gmem, bool valid, uint64_t policy) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(smem), "l"(gmem), "r"(bytes),
+               "l"(policy));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -426,6 +433,16 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* c, co
   }
 }
 
+// four scaled outputs as bfloat16 in one 8-byte store
+__device__ __forceinline__ void store_bf16x4(bf16* dst, const float4 v, const float scale) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale, v.y * scale);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale, v.w * scale);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
+}
+
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   if (threadIdx.x == 0) ASTAMP(0);  // entry
@@ -476,7 +493,20 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   const bool cached = n_pages <= DEC_MAXP;
   if (cached)
     for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = table[first_page + i];
+  // The cluster's merge in one level (when the rows fit the inbox): every CTA sends the rows of its
+  // partial to the CTA that finishes them (row r to rank r % nsplit) by remote stores that count
+  // their bytes on a barrier of the receiver; a CTA waits for the bytes due in its own inbox and
+  // leaves.  No CTA reads another's memory and there is no cluster barrier after the keys.
+  __shared__ __align__(8) uint64_t inbox_bar;
+  const int rows_own_max = (G + nsplit - 1) / nsplit;
+  const bool push_merge = nsplit > 1 && nsplit * rows_own_max <= 16;
+  if (push_merge && tid == 0) {
+    tc::mbar_init(&inbox_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   __syncthreads();
+  // first half of a start barrier: by the time rows are sent, every CTA of the cluster is running
+  if (push_merge) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   // a tile lies within one page when the page size is a multiple of the tile (the usual case): one
   // page lookup per tile, and a lane's pieces differ by a constant row stride
@@ -485,6 +515,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   // recorded when the tile is requested, and the whole tile of 16 keys is hidden from the softmax
   // (its rows were zero-filled, not loaded).  Nothing of this is in the loops over keys.
   uint32_t bad_tiles = 0u;
+  const uint64_t once = tc::l2_policy_evict_first();
   auto load_tile = [&](int kt, int stage) {  // by one warp: consecutive lanes take consecutive 16-byte pieces of a row
     const uint32_t k_s = ring + stage * 2 * DEC_TILE_BYTES, v_s = k_s + DEC_TILE_BYTES;
     const int nth = (kt - (my_begin + warp)) >> 2;
@@ -506,8 +537,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
           const int b = b0 + r;
           const bool valid = page_ok && b <= last_cached && b >= lo;
           const size_t off = base + (size_t)r * D + chunk * 8;
-          cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
-          cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
+          cp_async16_once(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid, once);
+          cp_async16_once(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid, once);
         }
       } else {
 #pragma unroll 4
@@ -516,8 +547,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
           const int b = b0 + r;
           const bool valid = page_ok && b <= last_cached && b >= lo;
           const size_t off = base + (size_t)r * D + chunk * 8;
-          cp_async16(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid);
-          cp_async16(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid);
+          cp_async16_once(k_s + sw(r, chunk), p.k_pool + (valid ? off : 0), valid, once);
+          cp_async16_once(v_s + sw(r, chunk), p.v_pool + (valid ? off : 0), valid, once);
         }
       }
       return;
@@ -541,8 +572,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
           off = (((size_t)page * p.KVH + kvh) * p.page_size + within) * D + chunk * 8;
         }
       }
-      cp_async16(k_s + sw(r, chunk), p.k_pool + off, valid);
-      cp_async16(v_s + sw(r, chunk), p.v_pool + off, valid);
+      cp_async16_once(k_s + sw(r, chunk), p.k_pool + off, valid, once);
+      cp_async16_once(v_s + sw(r, chunk), p.v_pool + off, valid, once);
     }
     if (__any_sync(0xffffffffu, met_bad) && nth < 32) bad_tiles |= 1u << nth;
   };
@@ -786,56 +817,82 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
   __syncthreads();
   if (tid == 0) ASTAMP(5);  // every warp of the CTA is through
+  if (push_merge) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // second half
+  if (tid == 0) ASTAMP(10);  // the cluster's CTAs are all running
   const bool last_level = nsplit == 1;
+  // The merges run once per CTA and their cost is latency: instructions fetched for the first time
+  // and transactions between CTAs.  So they are short: lane c holds partial c's (max, sum), a warp
+  // reduction gives the common max and the total, a rolled loop adds the weighted output rows,
+  // and a lane owns four consecutive outputs so that a row leaves in one 16-byte store per lane.
+  constexpr int C4 = D / 4;            // 16-byte pieces of an output row
+  constexpr int NJ = (C4 + 31) / 32;   // pieces per lane
   for (int row = warp; row < G; row += 4) {
-    float m_w[4], l_w[4];
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float* ml = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + 16 * D;
-      m_w[w] = ml[row * 2];
-      l_w[w] = ml[row * 2 + 1];
-      M = fmaxf(M, m_w[w]);
+    float m_l = -INFINITY, l_l = 0.f;
+    if (lane < 4) {
+      const float* ml = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + lane * DEC_WARP_BYTES) + 16 * D;
+      m_l = ml[row * 2];
+      l_l = ml[row * 2 + 1];
     }
-    float L = 0.f;
-    float acc[(D + 31) / 32];
+    float M = m_l;
 #pragma unroll
-    for (int j = 0; j < (D + 31) / 32; ++j) acc[j] = 0.f;
+    for (int s = 1; s < 4; s <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
+    M = __shfl_sync(0xffffffffu, M, 0);
+    const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);
+    float L = w_l * l_l;
 #pragma unroll
+    for (int s = 1; s < 4; s <<= 1) L += __shfl_xor_sync(0xffffffffu, L, s);
+    L = __shfl_sync(0xffffffffu, L, 0);
+    float4 acc[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
     for (int w = 0; w < 4; ++w) {
-      const float wgt = m_w[w] == -INFINITY ? 0.f : exp2f(m_w[w] - M);
-      L += wgt * l_w[w];
-      const float* po = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + row * D;
+      const float wgt = __shfl_sync(0xffffffffu, w_l, w);
+      const float4* po = reinterpret_cast<const float4*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + row * C4;
 #pragma unroll
-      for (int j = 0; j < (D + 31) / 32; ++j) {
-        const int d = lane + 32 * j;
-        if (d < D) acc[j] += wgt * po[d];
+      for (int j = 0; j < NJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < C4) {
+          const float4 v = po[c];
+          acc[j].x += wgt * v.x, acc[j].y += wgt * v.y, acc[j].z += wgt * v.z, acc[j].w += wgt * v.w;
+        }
       }
     }
+    if (tid == 0) ASTAMP(8);  // a row of the CTA's partial is merged (the last one stays)
     if (last_level && to_partials) {
       const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
 #pragma unroll
-      for (int j = 0; j < (D + 31) / 32; ++j) {
-        const int d = lane + 32 * j;
-        if (d < D) p.part_o[idx * D + d] = acc[j];
+      for (int j = 0; j < NJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < C4) reinterpret_cast<float4*>(p.part_o + idx * D)[c] = acc[j];
       }
-      if (lane == 0) {
-        p.part_ml[idx * 2] = M;
-        p.part_ml[idx * 2 + 1] = L;
-      }
+      if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
     } else if (last_level) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
       bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
 #pragma unroll
-      for (int j = 0; j < (D + 31) / 32; ++j) {
-        const int d = lane + 32 * j;
-        if (d < D) dst[d] = __float2bfloat16(acc[j] * inv);
+      for (int j = 0; j < NJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < C4) store_bf16x4(dst + 4 * c, acc[j], inv);
       }
+    } else if (push_merge) {
+      // slot (this rank, the row's place among its owner's rows) of the owner's inbox
+      const uint32_t owner = (uint32_t)(row % nsplit);
+      const int q = split * rows_own_max + row / nsplit;
+      const uint32_t bar = tc::mapa_u32(tc::smem_u32(&inbox_bar), owner);
+      const uint32_t dst = tc::mapa_u32(tc::smem_u32(cta_part + q * D), owner);
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < C4) tc::st_async_v4(dst + (uint32_t)c * 16u, acc[j], bar);
+      }
+      if (lane == 0)
+        tc::st_async_v2(tc::mapa_u32(tc::smem_u32(cta_part + 16 * D + q * 2), owner), make_float2(M, L), bar);
     } else {
 #pragma unroll
-      for (int j = 0; j < (D + 31) / 32; ++j) {
-        const int d = lane + 32 * j;
-        if (d < D) cta_part[row * D + d] = acc[j];
+      for (int j = 0; j < NJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < C4) reinterpret_cast<float4*>(cta_part + row * D)[c] = acc[j];
       }
       if (lane == 0) {
         cta_part[16 * D + row * 2] = M;
@@ -844,6 +901,68 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
     }
   }
   if (last_level) return;
+  if (push_merge) {
+    // the rows this CTA finishes: split, split + nsplit, ...; every rank sends D + 2 floats of each
+    if (tid == 0) ASTAMP(6);  // this CTA's rows are on their way
+    const int rows_own = split < G ? (G - split + nsplit - 1) / nsplit : 0;
+    if (tid == 0) tc::mbar_expect_tx(&inbox_bar, (uint32_t)(nsplit * rows_own * (D + 2) * 4));
+    if (!tc::mbar_wait(&inbox_bar, 0)) {
+      if (tid == 0) atomicOr(p.err, DSP_ERR_WAIT_LIMIT);
+      return;
+    }
+    if (tid == 0) ASTAMP(7);  // every rank's rows have arrived
+    for (int slot = warp; slot < rows_own; slot += 4) {
+      const int row = split + slot * nsplit;
+      float m_l = -INFINITY, l_l = 0.f;
+      if (lane < nsplit) {
+        const int q = lane * rows_own_max + slot;
+        m_l = cta_part[16 * D + q * 2];
+        l_l = cta_part[16 * D + q * 2 + 1];
+      }
+      float M = m_l;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
+      const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);
+      float L = w_l * l_l;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) L += __shfl_xor_sync(0xffffffffu, L, s);
+      float4 acc[NJ];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+      for (int c = 0; c < nsplit; ++c) {
+        const float wgt = __shfl_sync(0xffffffffu, w_l, c);
+        const float4* po = reinterpret_cast<const float4*>(cta_part + (c * rows_own_max + slot) * D);
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          const int k = lane + 32 * j;
+          if (k < C4) {
+            const float4 v = po[k];
+            acc[j].x += wgt * v.x, acc[j].y += wgt * v.y, acc[j].z += wgt * v.z, acc[j].w += wgt * v.w;
+          }
+        }
+      }
+      if (to_partials) {
+        const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          const int k = lane + 32 * j;
+          if (k < C4) reinterpret_cast<float4*>(p.part_o + idx * D)[k] = acc[j];
+        }
+        if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
+      } else {
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          const int k = lane + 32 * j;
+          if (k < C4) store_bf16x4(dst + 4 * k, acc[j], inv);
+        }
+      }
+    }
+    if (tid == 0) ASTAMP(9);  // end
+    return;
+  }
   // ---- level 2: the CTAs of the cluster; the rows are dealt to its warps
   if (tid == 0) ASTAMP(6);  // the CTA's partial is in its shared memory
   cg::cluster_group cluster = cg::this_cluster();

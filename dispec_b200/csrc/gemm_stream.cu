@@ -205,9 +205,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       auto k_of = [&](int it) { return (kb_begin + it % num_kb) * BK; };
       // W does not depend on the kernel before this one: the ring is filled with W tiles first,
       // then the kernel waits for its predecessor and sends the matching slices of A after them
+      // W is read once per call and is far larger than the L2 over a step: its lines leave first
+      const uint64_t once = l2_policy_evict_first();
       for (int it = 0; it < first; ++it) {
         mbar_expect_tx(&full_bar[it], C::STAGE_BYTES);
-        tma_load_2d(smem + it * C::STAGE_BYTES, &map_w, &full_bar[it], k_of(it), w_row(it));
+        tma_load_2d_hint(smem + it * C::STAGE_BYTES, &map_w, &full_bar[it], k_of(it), w_row(it), once);
       }
       STAMP(10);  // the ring's first tiles of W are requested
       pdl_wait();
@@ -223,7 +225,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
         unsigned char* dst = smem + s * C::STAGE_BYTES;
-        tma_load_2d(dst, &map_w, &full_bar[s], k_of(it), w_row(it));
+        tma_load_2d_hint(dst, &map_w, &full_bar[s], k_of(it), w_row(it), once);
         tma_load_2d(dst + W_BYTES, &map_x, &full_bar[s], k_of(it), 0);
       }
       STAMP(7);  // the last tile of W is requested

@@ -614,6 +614,49 @@ def test_attention_tcgen05_far_key_stands_out(plant):
     torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("H,KVH,D,splits", [(16, 1, 128, 8), (16, 1, 64, 3), (12, 1, 80, 5), (9, 1, 128, 2),
+                                            (32, 2, 64, 8), (7, 1, 96, 7), (3, 3, 128, 8)])
+def test_decode_attention_cluster_merge_paths(H, KVH, D, splits):
+    """The ways the cluster's CTAs put their partial rows together, by group size and split count:
+    rows sent to their owners (one or several rows per owner, owners without a row, more rows
+    than warps) and, where the owners' inboxes would not hold them, partials read from the other
+    CTAs.  Two rows: a long one with a far key that stands out, and one of three keys."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import attention as A
+    page, ctx_lens, plant = 16, [1500, 3], [77, 1]
+    B = len(ctx_lens)
+    g = torch.Generator().manual_seed(1000 * H + splits)
+    pages_per = [(c + page - 1) // page for c in ctx_lens]
+    num_pages = sum(pages_per) + 2
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=torch.bfloat16)
+    vp = kp.clone()
+    q = torch.randn(B, H, D, generator=g).bfloat16()
+    refs = []
+    for s, c in enumerate(ctx_lens):
+        k = torch.randn(c, KVH, D, generator=g).bfloat16()
+        v = torch.randn(c, KVH, D, generator=g).bfloat16()
+        k[plant[s]] = (q[s, ::H // KVH] * 4.0).bfloat16()
+        for j in range(pages_per[s]):
+            table[s, j] = perm.pop()
+        for b in range(c):
+            kp[table[s, b // page], :, b % page] = k[b]
+            vp[table[s, b // page], :, b % page] = v[b]
+        refs.append(_attention_reference(q[s:s + 1].double(), k.double(), v.double(), torch.tensor([c - 1]),
+                                         0, D ** -0.5)[0])
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    out = torch.full((B, H * D), float("nan"), dtype=torch.bfloat16, device=dev())
+    A.paged_attention_tiles(q.reshape(B, H * D).to(dev()), H * D, kp.to(dev()), vp.to(dev()), table.to(dev()),
+                            i32(list(range(B + 1))), i32(ctx_lens), i32(list(range(B))), i32([0] * B), B, B, out,
+                            H, KVH, D, 0, D ** -0.5, splits)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error("decode attention, cluster merge")
+    got = out.float().cpu().view(B, H, D)
+    for s, ref in enumerate(refs):
+        torch.testing.assert_close(got[s].double(), ref, atol=2e-2, rtol=2e-2, msg=lambda m: f"row {s}: {m}")
+
+
 @pytest.mark.parametrize("offset", [-1, 0, 1])
 @pytest.mark.parametrize("q_len", [2, 40])
 def test_attention_tcgen05_window_edge(offset, q_len):
