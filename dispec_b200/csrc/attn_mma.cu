@@ -579,16 +579,30 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   };
 
   // this warp's tiles: my_begin + warp, + 4, ...; the tile that holds the newest position (always the
-  // last tile of the sequence) is requested after the wait, every other one may go at once
+  // last tile of the sequence) is requested after the wait when an earlier kernel of this step stored
+  // that position, every other one may go at once
   const int first = my_begin + warp;
   const int newest = pos / DK;
   int issued = 0;  // tiles of this warp requested so far (one commit group each, in order)
+  // (when this kernel stores the newest key and value itself, the tile's other rows are old as well)
   for (int j = 0; j < DSTAGES; ++j) {
     const int kt = first + 4 * j;
-    if (kt >= my_end || kt == newest) break;
+    if (kt >= my_end || (kt == newest && !own_new)) break;
     load_tile(kt, j);
     cp_async_commit();
     ++issued;
+  }
+  const int half = p.rotary_dim / 2;
+  if (p.fused_rope) {
+    // cos and sin of this position's angles, once for q and for the new key: they depend on the
+    // position alone, so they are ready before the predecessor is
+    for (int i = tid; i < half; i += THREADS) {
+      float sn, c;
+      sincosf((float)pos * p.inv_freq[i], &sn, &c);
+      cs[i] = c;
+      cs[half + i] = sn;
+    }
+    __syncthreads();
   }
 
   if (tid == 0) ASTAMP(1);  // page ids and the first tiles are requested
@@ -597,16 +611,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   // the next kernel (the output projection) may start now and not earlier: its weight ring would
   // compete with the key tiles requested above (measured: 1.314 ms -> 1.294 ms per decode step)
   pdl_launch_dependents();
-  const int half = p.rotary_dim / 2;
   if (p.fused_rope) {
-    // cos and sin of this position's angles, once for q and for the new key
-    for (int i = tid; i < half; i += THREADS) {
-      float sn, c;
-      sincosf((float)pos * p.inv_freq[i], &sn, &c);
-      cs[i] = c;
-      cs[half + i] = sn;
-    }
-    __syncthreads();
     // Q: the G heads of this KV head, rotated on the way into shared memory (16-byte pieces; piece j
     // of the low half rotates with piece j of the high half)
     const int hv = half / 8, tail = (D - p.rotary_dim) / 8;
