@@ -412,8 +412,12 @@ constexpr int DEC_MAXP = 256;  // page ids of the CTA's range kept in shared mem
 constexpr int DEC_Q_BYTES = 16 * ROW_BYTES;
 constexpr int DEC_TILE_BYTES = DK * ROW_BYTES;
 constexpr int DEC_PART_BYTES = (16 * D + 32) * 4;  // a partial: [16][D] outputs and [16][2] (m, l)
+// a warp's partial after its key loop: rows 8 floats further apart than D, so that the eight rows a
+// warp stores at once fall into different banks
+constexpr int DEC_WPART_STRIDE = D + 8;
+constexpr int DEC_WPART_BYTES = (16 * DEC_WPART_STRIDE + 32) * 4;
 constexpr int DEC_RING_BYTES = DSTAGES * 2 * DEC_TILE_BYTES;
-constexpr int DEC_WARP_BYTES = DEC_RING_BYTES > DEC_PART_BYTES ? DEC_RING_BYTES : DEC_PART_BYTES;
+constexpr int DEC_WARP_BYTES = DEC_RING_BYTES > DEC_WPART_BYTES ? DEC_RING_BYTES : DEC_WPART_BYTES;
 constexpr int DEC_CS_BYTES = D * 4;  // cos and sin of the token's angles (fused rotation)
 constexpr int DEC_SMEM = DEC_Q_BYTES + 4 * DEC_WARP_BYTES + DEC_PART_BYTES + DEC_MAXP * 4 + DEC_CS_BYTES;
 
@@ -443,7 +447,12 @@ __device__ __forceinline__ void store_bf16x4(bf16* dst, const float4 v, const fl
   *reinterpret_cast<uint2*>(dst) = u;
 }
 
-__global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
+// Registers are held down where the head size allows it: a CTA of this kernel shares its SM with
+// the early CTAs of the product after it (and with the last ones of the product before), and that
+// overlap is worth more than the registers (measured at batch 8 and 16: 238 registers, 7 % and
+// 10 % slower steps than 167).
+constexpr int DEC_MIN_CTAS = D <= 128 ? 3 : 1;
+__global__ void __launch_bounds__(THREADS, DEC_MIN_CTAS) attn_decode_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   if (threadIdx.x == 0) ASTAMP(0);  // entry
   const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(smem);
@@ -807,13 +816,15 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   __syncwarp();
   {
     float* part_o = reinterpret_cast<float*>(warp_mem);
-    float* part_ml = part_o + 16 * D;
+    float* part_ml = part_o + 16 * DEC_WPART_STRIDE;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = g4 + 8 * r;
+      if (row >= G) continue;  // rows beyond the group are never read
 #pragma unroll
       for (int i = 0; i < D / 8; ++i)
-        *reinterpret_cast<float2*>(part_o + row * D + i * 8 + 2 * c4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+        *reinterpret_cast<float2*>(part_o + row * DEC_WPART_STRIDE + i * 8 + 2 * c4) =
+            make_float2(o[i][2 * r], o[i][2 * r + 1]);
       if (c4 == 0) {
         part_ml[row * 2] = m_run[r];
         part_ml[row * 2 + 1] = l_run[r];
@@ -825,86 +836,54 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   if (push_merge) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // second half
   if (tid == 0) ASTAMP(10);  // the cluster's CTAs are all running
   const bool last_level = nsplit == 1;
-  // The merges run once per CTA and their cost is latency: instructions fetched for the first time
-  // and transactions between CTAs.  So they are short: lane c holds partial c's (max, sum), a warp
-  // reduction gives the common max and the total, a rolled loop adds the weighted output rows,
-  // and a lane owns four consecutive outputs so that a row leaves in one 16-byte store per lane.
-  constexpr int C4 = D / 4;            // 16-byte pieces of an output row
-  constexpr int NJ = (C4 + 31) / 32;   // pieces per lane
-  for (int row = warp; row < G; row += 4) {
-    float m_l = -INFINITY, l_l = 0.f;
-    if (lane < 4) {
-      const float* ml = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + lane * DEC_WARP_BYTES) + 16 * D;
-      m_l = ml[row * 2];
-      l_l = ml[row * 2 + 1];
-    }
-    float M = m_l;
+  // The merges run once per CTA and their cost is latency: dependent instructions, and transactions
+  // between CTAs.  So a thread owns four consecutive outputs of one row, asks for all partials of
+  // them at once and weighs them itself (every thread of a row repeats the few exponentials: no
+  // exchange between lanes), and a row leaves in one 16-byte store per thread.
+  constexpr int C4 = D / 4;  // 16-byte pieces of an output row
+  for (int item = tid; item < G * C4; item += THREADS) {
+    const int row = item / C4, c = item - row * C4;
+    float2 ml[4];
+    float4 v[4];
 #pragma unroll
-    for (int s = 1; s < 4; s <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
-    M = __shfl_sync(0xffffffffu, M, 0);
-    const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);
-    float L = w_l * l_l;
-#pragma unroll
-    for (int s = 1; s < 4; s <<= 1) L += __shfl_xor_sync(0xffffffffu, L, s);
-    L = __shfl_sync(0xffffffffu, L, 0);
-    float4 acc[NJ];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
     for (int w = 0; w < 4; ++w) {
-      const float wgt = __shfl_sync(0xffffffffu, w_l, w);
-      const float4* po = reinterpret_cast<const float4*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES) + row * C4;
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < C4) {
-          const float4 v = po[c];
-          acc[j].x += wgt * v.x, acc[j].y += wgt * v.y, acc[j].z += wgt * v.z, acc[j].w += wgt * v.w;
-        }
-      }
+      const float* part = reinterpret_cast<const float*>(smem + DEC_Q_BYTES + w * DEC_WARP_BYTES);
+      ml[w] = *reinterpret_cast<const float2*>(part + 16 * DEC_WPART_STRIDE + row * 2);
+      v[w] = *reinterpret_cast<const float4*>(part + row * DEC_WPART_STRIDE + c * 4);
     }
-    if (tid == 0) ASTAMP(8);  // a row of the CTA's partial is merged (the last one stays)
+    const float M = fmaxf(fmaxf(ml[0].x, ml[1].x), fmaxf(ml[2].x, ml[3].x));
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = ml[w].x == -INFINITY ? 0.f : exp2f(ml[w].x - M);
+      L += wgt * ml[w].y;
+      acc.x += wgt * v[w].x, acc.y += wgt * v[w].y, acc.z += wgt * v[w].z, acc.w += wgt * v[w].w;
+    }
     if (last_level && to_partials) {
       const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < C4) reinterpret_cast<float4*>(p.part_o + idx * D)[c] = acc[j];
-      }
-      if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
+      reinterpret_cast<float4*>(p.part_o + idx * D)[c] = acc;
+      if (c == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
     } else if (last_level) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
-      bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < C4) store_bf16x4(dst + 4 * c, acc[j], inv);
-      }
+      store_bf16x4(p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D + 4 * c, acc, inv);
     } else if (push_merge) {
       // slot (this rank, the row's place among its owner's rows) of the owner's inbox
       const uint32_t owner = (uint32_t)(row % nsplit);
       const int q = split * rows_own_max + row / nsplit;
       const uint32_t bar = tc::mapa_u32(tc::smem_u32(&inbox_bar), owner);
-      const uint32_t dst = tc::mapa_u32(tc::smem_u32(cta_part + q * D), owner);
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < C4) tc::st_async_v4(dst + (uint32_t)c * 16u, acc[j], bar);
-      }
-      if (lane == 0)
+      tc::st_async_v4(tc::mapa_u32(tc::smem_u32(cta_part + q * D + c * 4), owner), acc, bar);
+      if (c == 0)
         tc::st_async_v2(tc::mapa_u32(tc::smem_u32(cta_part + 16 * D + q * 2), owner), make_float2(M, L), bar);
     } else {
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < C4) reinterpret_cast<float4*>(cta_part + row * D)[c] = acc[j];
-      }
-      if (lane == 0) {
+      reinterpret_cast<float4*>(cta_part + row * D)[c] = acc;
+      if (c == 0) {
         cta_part[16 * D + row * 2] = M;
         cta_part[16 * D + row * 2 + 1] = L;
       }
     }
   }
+  if (tid == 0) ASTAMP(8);  // this CTA's rows are merged
   if (last_level) return;
   if (push_merge) {
     // the rows this CTA finishes: split, split + nsplit, ...; every rank sends D + 2 floats of each
@@ -916,53 +895,35 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
       return;
     }
     if (tid == 0) ASTAMP(7);  // every rank's rows have arrived
-    for (int slot = warp; slot < rows_own; slot += 4) {
+    for (int item = tid; item < rows_own * C4; item += THREADS) {
+      const int slot = item / C4, c = item - slot * C4;
       const int row = split + slot * nsplit;
-      float m_l = -INFINITY, l_l = 0.f;
-      if (lane < nsplit) {
-        const int q = lane * rows_own_max + slot;
-        m_l = cta_part[16 * D + q * 2];
-        l_l = cta_part[16 * D + q * 2 + 1];
+      float2 ml[8];
+      float4 v[8];
+      float M = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {  // the decode kernel runs with at most 8 splits
+        const int q = (r < nsplit ? r : 0) * rows_own_max + slot;
+        ml[r] = *reinterpret_cast<const float2*>(cta_part + 16 * D + q * 2);
+        v[r] = *reinterpret_cast<const float4*>(cta_part + q * D + c * 4);
+        if (r >= nsplit) ml[r].x = -INFINITY;
+        M = fmaxf(M, ml[r].x);
       }
-      float M = m_l;
+      float L = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int s = 1; s < 32; s <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
-      const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);
-      float L = w_l * l_l;
-#pragma unroll
-      for (int s = 1; s < 32; s <<= 1) L += __shfl_xor_sync(0xffffffffu, L, s);
-      float4 acc[NJ];
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-      for (int c = 0; c < nsplit; ++c) {
-        const float wgt = __shfl_sync(0xffffffffu, w_l, c);
-        const float4* po = reinterpret_cast<const float4*>(cta_part + (c * rows_own_max + slot) * D);
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          const int k = lane + 32 * j;
-          if (k < C4) {
-            const float4 v = po[k];
-            acc[j].x += wgt * v.x, acc[j].y += wgt * v.y, acc[j].z += wgt * v.z, acc[j].w += wgt * v.w;
-          }
-        }
+      for (int r = 0; r < 8; ++r) {
+        const float wgt = ml[r].x == -INFINITY ? 0.f : exp2f(ml[r].x - M);
+        L += wgt * ml[r].y;
+        acc.x += wgt * v[r].x, acc.y += wgt * v[r].y, acc.z += wgt * v[r].z, acc.w += wgt * v[r].w;
       }
       if (to_partials) {
         const size_t idx = ((size_t)qs * p.H + kvh * G + row) * p.num_outer + outer;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          const int k = lane + 32 * j;
-          if (k < C4) reinterpret_cast<float4*>(p.part_o + idx * D)[k] = acc[j];
-        }
-        if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
+        reinterpret_cast<float4*>(p.part_o + idx * D)[c] = acc;
+        if (c == 0) *reinterpret_cast<float2*>(p.part_ml + idx * 2) = make_float2(M, L);
       } else {
         const float inv = L > 0.f ? 1.f / L : 0.f;
-        bf16* dst = p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          const int k = lane + 32 * j;
-          if (k < C4) store_bf16x4(dst + 4 * k, acc[j], inv);
-        }
+        store_bf16x4(p.out + (size_t)qs * p.out_stride + (size_t)(kvh * G + row) * D + 4 * c, acc, inv);
       }
     }
     if (tid == 0) ASTAMP(9);  // end
