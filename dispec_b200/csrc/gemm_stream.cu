@@ -97,13 +97,26 @@ struct Args {
   // when the next kernel may start (programmatic dependent launch): 0 at once, 1 when this CTA has
   // requested its last tile of W
   int late_trigger;
+  // A norm around the product, split over two kernels (both null: none).  norm_src: the rows whose
+  // mean square scales this product's rows, C = (A W^T) * rsqrt(mean(norm_src[m]^2) + norm_eps) + ...,
+  // A being those rows times the norm's gain.  gain2, C2: a second output, the rounded result times
+  // gain2[n], which is such an A for the product after this one.
+  const bf16* norm_src;
+  long ld_src;
+  float norm_eps;
+  const bf16* gain2;
+  void* C2;
+  long ldc2;
 };
 
 template <typename TOut>
 __device__ __forceinline__ void finish(const Args& a, float v, int m, int n) {
   if (a.bias) v += __bfloat162float(a.bias[n]);
   if (a.residual) v += to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]);
-  reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>(v);
+  const TOut out = from_f32<TOut>(v);
+  reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = out;
+  if (a.C2)
+    reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * __bfloat162float(a.gain2[n]));
 }
 
 // The accumulator of this thread's W row: the partial accumulators added in a fixed order.
@@ -276,9 +289,62 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int quarter = warp & 3;
   const int row = quarter * 32 + lane;
   const bool swiglu = a.epilogue == EPI_SWIGLU;
+  // The scales of a norm whose gain is already in A: rsqrt(mean square + eps) of the rows of
+  // norm_src, by the four epilogue warps (rows in turn, 16-byte loads, 32-bit sums) while the
+  // products run.  Called after the wait on the predecessor, which wrote those rows.
+  __shared__ float row_scale[NB];
+  // rows first, first + step, ... below M: the epilogue warps take them in turn, two rows of a warp
+  // in flight at a time; a row's sum is formed the same way whoever asks (lanes stride over its
+  // 16-byte pieces, then a tree over the lanes)
+  auto compute_row_scales = [&](int first, int step) {
+    if (a.norm_src == nullptr) return;
+    const int pieces = a.K / 8;
+    auto square_sum = [](const uint4 u) {
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
+        ss += lo * lo;
+        ss += hi * hi;
+      }
+      return ss;
+    };
+    for (int m0 = first + (warp - C::FIRST_EPI_WARP) * step; m0 < a.M; m0 += 8 * step) {
+      const int m1 = m0 + 4 * step;
+      const uint4* src0 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)m0 * a.ld_src);
+      const uint4* src1 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)(m1 < a.M ? m1 : m0) * a.ld_src);
+      float ss0 = 0.f, ss1 = 0.f;
+      for (int g0 = lane; g0 < pieces; g0 += 32 * 4) {
+        uint4 u0[4], u1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int g = g0 + 32 * i;
+          u0[i] = g < pieces ? src0[g] : make_uint4(0, 0, 0, 0);
+          u1[i] = (g < pieces && m1 < a.M) ? src1[g] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          ss0 += square_sum(u0[i]);
+          ss1 += square_sum(u1[i]);
+        }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        ss0 += __shfl_xor_sync(0xffffffffu, ss0, sft);
+        ss1 += __shfl_xor_sync(0xffffffffu, ss1, sft);
+      }
+      if (lane == 0) {
+        row_scale[m0] = rsqrtf(ss0 / (float)a.K + a.norm_eps);
+        if (m1 < a.M) row_scale[m1] = rsqrtf(ss1 / (float)a.K + a.norm_eps);
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+  };
   if (splits == 1) {
     if (warp >= C::FIRST_EPI_WARP) {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+      compute_row_scales(0, 1);
       int local = 0;
       for (int nb = blockIdx.x; nb < n_blocks; nb += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -293,6 +359,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
+        if (a.norm_src) {
+#pragma unroll
+          for (int m = 0; m < NB; ++m)
+            if (m < a.M) v[m] = __float_as_uint(__uint_as_float(v[m]) * row_scale[m]);
+        }
         const int n = nb * ROWS_W + row;
         if (swiglu) {
           // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs.  Two rows
@@ -331,9 +402,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // bias and residual of the rows this CTA finishes are fetched while the products still run
     constexpr int MAX_OWN = 8;  // rows per CTA: at most 16 rows over at least 2 ranks
     float own_res[MAX_OWN];
-    float own_bias = 0.f;
+    float own_bias = 0.f, own_gain2 = 0.f;
     auto fetch_own = [&]() {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+      compute_row_scales(rank, splits);  // of the rows this CTA finishes
       const int n = blockIdx.x * ROWS_W + row;
 #pragma unroll
       for (int slot = 0; slot < MAX_OWN; ++slot) {
@@ -342,6 +414,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f;
       }
       if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
+      if (!swiglu && a.C2 && n < a.N) own_gain2 = __bfloat162float(a.gain2[n]);
     };
     if (warp >= C::FIRST_EPI_WARP) {
       fetch_own();
@@ -398,13 +471,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             total_up += part_up[sp];
           }
         }
+        if (a.norm_src) {
+          const float scale = row_scale[m];
+          total *= scale;
+          total_up *= scale;
+        }
         if (swiglu) {
           if (lane < 16 && n + 16 < a.N)
             reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
                 from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
         } else if (n < a.N) {
           // the same order of sums as finish(): bias, then residual
-          reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = from_f32<TOut>((total + own_bias) + res);
+          const TOut out = from_f32<TOut>((total + own_bias) + res);
+          reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = out;
+          if (a.C2) reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * own_gain2);
         }
       };
       finish_row(0, own_res[0]);
@@ -573,10 +653,22 @@ extern "C" int dsp_gemm_stream_stamps_read(unsigned long long* out, long n) {
 // of W lets the next kernel start only when its own last tile is on its way (what the next kernels
 // request before their wait would otherwise compete with a long stream); shorter products let it
 // start at once; 0 or less: always at once.
+// norm_src (bfloat16 rows of K values, row stride ld_src) and norm_eps: the rows of the product are
+// multiplied by rsqrt(mean(norm_src[m]^2) + norm_eps) before bias and residual (A holds those rows
+// times a norm's gain: together that is the norm in front of the product).  gain2 (bfloat16 [N])
+// and C2 (the output's type, row stride ldc2): also stores the rounded output times gain2.  Both
+// for up to 16 rows of A and the plain epilogue (norm_src: the SwiGLU epilogue as well).
 extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const void* bias, const void* residual,
                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int target_ctas,
-                               int epilogue, long late_trigger_bytes, cudaStream_t stream) {
+                               int epilogue, long late_trigger_bytes, const void* norm_src, long ld_src,
+                               float norm_eps, const void* gain2, void* C2, long ldc2, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  DSP_REQUIRE((norm_src == nullptr && C2 == nullptr) || M <= 16,
+              "dsp_gemm_stream: a norm split over two products takes at most 16 rows, got %d", M);
+  DSP_REQUIRE(norm_src == nullptr || (ld_src % 8 == 0 && ((uintptr_t)norm_src % 16) == 0),
+              "dsp_gemm_stream: the rows under the norm must be 16-byte aligned (row stride %ld)", ld_src);
+  DSP_REQUIRE(C2 == nullptr || (gain2 != nullptr && epilogue == EPI_PLAIN),
+              "dsp_gemm_stream: the scaled second output needs a gain and the plain epilogue");
   DSP_REQUIRE(M <= 64, "dsp_gemm_stream: M=%d above 64 rows", M);
   DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_stream: K=%d and the row stride must be multiples of 8", K);
   DSP_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "dsp_gemm_stream: operands must be 16-byte aligned");
@@ -620,6 +712,12 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   a.kb_per_split = kb_per_split;
   a.epilogue = epilogue;
   a.late_trigger = (late_trigger_bytes > 0 && (long)N * K * 2 >= late_trigger_bytes) ? 1 : 0;
+  a.norm_src = (const bf16*)norm_src;
+  a.ld_src = ld_src;
+  a.norm_eps = norm_eps;
+  a.gain2 = (const bf16*)gain2;
+  a.C2 = C2;
+  a.ldc2 = ldc2;
   if (out_dtype == DSP_BF16) {
     if (nb_rows == 16) return launch<16, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
     if (nb_rows == 32) return launch<32, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);

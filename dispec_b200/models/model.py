@@ -140,7 +140,14 @@ class DecoderModel:
             cache = ctx.cache_view(self.placement[label], call.write) if label is not None else None
             sidx = self.call_state[idx]
             state = ctx.state_view(sidx) if sidx is not None else None
-            x, pending = self.layers[call.layer].forward(ctx, x, pending, cache, state)
+            # a block may take its first norm from the product that wrote x (see PreNormBlock)
+            nxt = self.layers[self.schedule[idx + 1].layer] if idx + 1 < len(self.schedule) else None
+            offer = getattr(nxt, "first_norm_after_product", None)
+            then_norm = offer() if offer is not None else None
+            if then_norm is not None and hasattr(self.layers[call.layer], "first_norm_after_product"):
+                x, pending = self.layers[call.layer].forward(ctx, x, pending, cache, state, then_norm=then_norm)
+            else:
+                x, pending = self.layers[call.layer].forward(ctx, x, pending, cache, state)
         return x, pending
 
     def logits(self, ctx, x, pending, rows: torch.Tensor) -> torch.Tensor:

@@ -73,10 +73,12 @@ class GQAAttention(Mixer):
         return small
 
     adds_residual = True
+    takes_deferred_norm = True
 
-    def forward(self, ctx, x, cache, state, residual=None):
+    def forward(self, ctx, x, cache, state, residual=None, then_norm=None):
         """``residual``: added by the last product (32-bit sum, rounded once), so that the sum
-        comes back."""
+        comes back.  ``x`` may be a norm still to be applied (``NormedRows``), and ``then_norm``
+        the (weight, eps) of the norm that reads the result: then (result, NormedRows) comes back."""
         H, KVH, D = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         rot = self.position_encoding.rotation()
@@ -94,7 +96,7 @@ class GQAAttention(Mixer):
                               cache.key_pool if cache.write else None,
                               cache.value_pool if cache.write else None,
                               inv_freq, H, KVH, D, rotary_dim, write_kv=cache.write)
-        out = torch.empty((x.shape[0], H * D), dtype=x.dtype, device=x.device)
+        out = torch.empty((qkv.shape[0], H * D), dtype=qkv.dtype, device=qkv.device)
         attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
                                  scale, fused_rope=fused)
-        return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual)
+        return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual, then_norm=then_norm)

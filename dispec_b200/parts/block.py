@@ -8,6 +8,7 @@ feed-forward output on as ``pending`` so that the next block's first norm (or th
 adds it."""
 from __future__ import annotations
 
+from dispec_b200.ops.gemm import NormedRows
 from dispec_b200.parts.base import Block
 from dispec_b200.registry import register_part
 
@@ -24,7 +25,33 @@ class PreNormBlock(Block):
         return (getattr(self.mixer, "adds_residual", False)
                 and getattr(self.feed_forward, "adds_residual", False))
 
-    def forward(self, ctx, x, pending, cache, state):
+    def _defers_norms(self) -> bool:
+        return (self._takes_residual() and hasattr(self.mixer_norm, "deferred")
+                and hasattr(self.ffn_norm, "after_product")
+                and getattr(self.mixer, "takes_deferred_norm", False)
+                and getattr(self.feed_forward, "takes_deferred_norm", False))
+
+    def first_norm_after_product(self):
+        """(weight, eps) of this block's first norm if the block takes that norm as ``pending``
+        (a ``NormedRows`` of its ``x``) from whoever wrote ``x``; else None."""
+        if self._defers_norms() and hasattr(self.mixer_norm, "after_product"):
+            return self.mixer_norm.after_product()
+        return None
+
+    def forward(self, ctx, x, pending, cache, state, then_norm=None):
+        """``then_norm``: (weight, eps) of the norm that reads this block's result first (the next
+        block's, offered by its ``first_norm_after_product``); a block that can hands back that
+        norm, still to be applied, as ``pending``."""
+        if self._defers_norms() and (pending is None or isinstance(pending, NormedRows)):
+            # each norm is handed to the product after it, which takes it apart where it can: the
+            # product before stores the rows times the gain beside its result, the product after
+            # scales its own result rows (see ops.gemm.NormedRows); else the norm kernel runs there
+            h = pending if pending is not None else self.mixer_norm.deferred(x)
+            x, h = self.mixer.forward(ctx, h, cache, state, residual=x,
+                                      then_norm=self.ffn_norm.after_product())
+            if then_norm is None:
+                return self.feed_forward.forward(ctx, h, residual=x), None
+            return self.feed_forward.forward(ctx, h, residual=x, then_norm=then_norm)
         if pending is None and self._takes_residual():
             # the sums into the residual stream happen in the epilogue of the last product of the
             # mixer and of the feed-forward (32-bit sum, rounded once)

@@ -5,6 +5,7 @@ dispec/engine/model_runner.py:215,218,220)."""
 from __future__ import annotations
 
 from dispec_b200 import ops
+from dispec_b200.ops import gemm as gemm_ops
 from dispec_b200.parts.base import Norm, TensorSpec
 from dispec_b200.registry import register_part
 
@@ -24,6 +25,15 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, rows=None):
         return ops.rms_norm(x, self.weight, self.eps, rows=rows)
+
+    def deferred(self, x):
+        """This norm of ``x`` as an input that its consumer applies (a product takes it apart
+        where it can, see ``ops.gemm.NormedRows``; otherwise the norm kernel runs there)."""
+        return gemm_ops.NormedRows(x, self.weight, self.eps)
+
+    def after_product(self):
+        """(weight, eps) for a product that writes the rows this norm reads (``linear(then_norm=)``)."""
+        return self.weight, self.eps
 
     def forward_add(self, ctx, residual, delta, rows=None):
         """Norm of residual + delta (32-bit sum).  Without ``rows`` the sum replaces ``residual``."""

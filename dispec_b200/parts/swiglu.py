@@ -37,12 +37,14 @@ class SwiGLUFeedForward(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     adds_residual = True
+    takes_deferred_norm = True
 
-    def forward(self, ctx, x, residual=None):
+    def forward(self, ctx, x, residual=None, then_norm=None):
         """``residual``: added by the last product (32-bit sum, rounded once), so that the sum
-        comes back."""
+        comes back.  ``x`` may be a norm still to be applied (``NormedRows``), and ``then_norm``
+        the (weight, eps) of the norm that reads the result: then (result, NormedRows) comes back."""
         if self.block and gemm_ops.gate_up_swiglu_supported(x, self.w_gate_up):
             act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up)
         else:
             act = ops.swiglu(ops.linear(x, self.w_gate_up), block=self.block)
-        return ops.linear(act, self.w_down, residual=residual, out=residual)
+        return ops.linear(act, self.w_down, residual=residual, out=residual, then_norm=then_norm)

@@ -533,6 +533,98 @@ def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
     torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("M,N,K,bias,resid,target", [
+    (8, 2048, 1536, True, False, 0),      # K split over a cluster: the owners of the rows scale them
+    (16, 1536, 1536, False, True, 0),     # two rows per owner
+    (1, 256, 1536, True, True, 0),
+    (5, 1000, 200, True, False, 0),       # ragged rows of W, K of 3 blocks and a tail
+    (13, 40000, 96, False, False, 0),     # more blocks than CTAs: no split, every CTA scales all rows
+    (3, 384, 3584, False, True, 148),
+])
+def test_gemm_stream_norm_taken_apart(M, N, K, bias, resid, target):
+    """The few-row product with a norm split around it: rows times the gain as the operand, the
+    rsqrt factors formed by the kernel from the rows themselves; against the norm's formula in
+    float64, and against the norm kernel followed by the plain product."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm, library
+    eps = 3e-5
+    h = rnd((M, K), torch.bfloat16, 161, 3.0)
+    h[0] *= 40.0  # rows of very different size: a factor of the wrong row would show
+    gain = (1.0 + rnd((K,), torch.float32, 162, 0.3)).bfloat16()
+    w = rnd((N, K), torch.bfloat16, 163, 0.1)
+    b = rnd((N,), torch.bfloat16, 164) if bias else None
+    r = rnd((M, N), torch.bfloat16, 165) if resid else None
+    scaled = (h.float() * gain.float()).bfloat16()
+    normed = gemm.NormedRows(h, gain, eps, scaled)
+    assert normed.splittable(w)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    gemm._stream(scaled, w, b, r, out, target_ctas=target, norm=normed)
+    assert library.device_error() == 0
+    hd = h.double()
+    y = hd * torch.rsqrt((hd * hd).mean(dim=1, keepdim=True) + eps) * gain.double()
+    ref = y @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if resid:
+        ref = ref + r.double()
+    torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
+    # no further from the truth than the norm kernel followed by the plain product (which rounds
+    # the normalised rows twice, this path once)
+    two = gemm.linear(ops.rms_norm(h, gain, eps), w, b, residual=r)
+    assert (out.double() - ref).abs().max() <= 1.25 * (two.double() - ref).abs().max() + 1e-3
+    # through linear(): the same kernel, the same bits
+    assert torch.equal(gemm.linear(normed, w, b, residual=r), out) or target != 0
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 8960, 1536), (16, 224, 96), (3, 512, 776)])
+def test_gemm_stream_norm_taken_apart_with_swiglu(M, I, K):
+    from dispec_b200.ops import gemm, library
+    eps = 1e-6
+    h = rnd((M, K), torch.bfloat16, 171, 2.0)
+    gain = (1.0 + rnd((K,), torch.float32, 172, 0.3)).bfloat16()
+    wg, wu = rnd((I, K), torch.bfloat16, 173, 0.15), rnd((I, K), torch.bfloat16, 174, 0.15)
+    blk = gemm.SWIGLU_BLOCK
+    w = torch.stack([wg.view(I // blk, blk, K), wu.view(I // blk, blk, K)], dim=1).reshape(2 * I, K).contiguous()
+    scaled = (h.float() * gain.float()).bfloat16()
+    normed = gemm.NormedRows(h, gain, eps, scaled)
+    out = gemm.linear_gate_up_swiglu(normed, w)
+    assert library.device_error() == 0
+    hd = h.double()
+    rstd = torch.rsqrt((hd * hd).mean(dim=1, keepdim=True) + eps)
+    # the kernel's own arithmetic: the operand it is given (rows times gain, rounded), the factors
+    # of the rows, the activation
+    g, u = scaled.double() @ wg.double().T * rstd, scaled.double() @ wu.double().T * rstd
+    torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+    # and against the norm's formula: no further off than the norm kernel followed by the product
+    y = hd * rstd * gain.double()
+    g, u = y @ wg.double().T, y @ wu.double().T
+    ref = g * torch.sigmoid(g) * u
+    from dispec_b200 import ops
+    two = gemm.linear_gate_up_swiglu(ops.rms_norm(h, gain, eps), w)
+    assert (out.double() - ref).abs().max() <= 1.25 * (two.double() - ref).abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("M,N,K,target", [(8, 1536, 8960, 0), (16, 300, 96, 0), (2, 40000, 64, 0), (33, 512, 96, 0)])
+def test_gemm_stream_scaled_second_output(M, N, K, target):
+    """linear(then_norm=): beside its result the product stores the rounded result times the next
+    norm's gain (up to 16 rows); with more rows it stores nothing and the norm kernel runs."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm, library
+    x = rnd((M, K), torch.bfloat16, 181)
+    w = rnd((N, K), torch.bfloat16, 182, 0.1)
+    r = rnd((M, N), torch.bfloat16, 183)
+    gain = (1.0 + rnd((N,), torch.float32, 184, 0.3)).bfloat16()
+    plain = gemm.linear(x, w, residual=r)
+    out, nxt = gemm.linear(x, w, residual=r, then_norm=(gain, 1e-6))
+    assert library.device_error() == 0
+    assert torch.equal(out, plain) and nxt.source is out
+    if M <= gemm.NORM_SPLIT_MAX_ROWS:
+        assert torch.equal(nxt.scaled, (out.float() * gain.float()).bfloat16())
+    else:
+        assert nxt.scaled is None
+    torch.testing.assert_close(nxt.materialize().float(), ops.rms_norm(out, gain, 1e-6).float())
+
+
 @pytest.mark.parametrize("decode_kernel", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 8, 12])
 def test_attention_tensor_core_single_token_splits(splits, decode_kernel):
