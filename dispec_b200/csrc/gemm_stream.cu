@@ -501,7 +501,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // one block per CTA; the cluster adds the partial tiles
     float* red = reinterpret_cast<float*>(smem);  // [NB][128], reuses the ring once it has drained
     bool ok = true;
+    cg::cluster_group cluster = cg::this_cluster();
     if (warp >= C::FIRST_EPI_WARP) {
+      if (a.norm_src) {  // the factors of the rows this CTA finishes, while the products run
+        pdl_wait();
+        compute_row_scales((int)cluster.block_rank(), splits);
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
       tc_fence_after();
@@ -514,7 +519,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
     if (warp >= C::FIRST_EPI_WARP && !failed) {
       pdl_wait();
@@ -550,6 +554,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
               total += part[j][sp];
               total_up += part_up[j][sp];
             }
+          }
+          if (a.norm_src) {
+            total *= row_scale[m];
+            total_up *= row_scale[m];
           }
           if (swiglu) {
             if (lane < 16 && n + 16 < a.N)
@@ -656,15 +664,13 @@ extern "C" int dsp_gemm_stream_stamps_read(unsigned long long* out, long n) {
 // norm_src (bfloat16 rows of K values, row stride ld_src) and norm_eps: the rows of the product are
 // multiplied by rsqrt(mean(norm_src[m]^2) + norm_eps) before bias and residual (A holds those rows
 // times a norm's gain: together that is the norm in front of the product).  gain2 (bfloat16 [N])
-// and C2 (the output's type, row stride ldc2): also stores the rounded output times gain2.  Both
-// for up to 16 rows of A and the plain epilogue (norm_src: the SwiGLU epilogue as well).
+// and C2 (the output's type, row stride ldc2): also stores the rounded output times gain2, with
+// the plain epilogue.
 extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const void* bias, const void* residual,
                                long ldr, void* C, long ldc, int M, int N, int K, int out_dtype, int target_ctas,
                                int epilogue, long late_trigger_bytes, const void* norm_src, long ld_src,
                                float norm_eps, const void* gain2, void* C2, long ldc2, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  DSP_REQUIRE((norm_src == nullptr && C2 == nullptr) || M <= 16,
-              "dsp_gemm_stream: a norm split over two products takes at most 16 rows, got %d", M);
   DSP_REQUIRE(norm_src == nullptr || (ld_src % 8 == 0 && ((uintptr_t)norm_src % 16) == 0),
               "dsp_gemm_stream: the rows under the norm must be 16-byte aligned (row stride %ld)", ld_src);
   DSP_REQUIRE(C2 == nullptr || (gain2 != nullptr && epilogue == EPI_PLAIN),

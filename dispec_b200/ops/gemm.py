@@ -21,7 +21,7 @@ from dispec_b200.ops import library as L
 from dispec_b200.ops import tuning
 
 STREAM_MAX_ROWS = 64  # rows the weight-streaming kernel takes
-NORM_SPLIT_MAX_ROWS = 16  # rows up to which that kernel takes a norm split over two products
+NORM_SPLIT_MAX_ROWS = STREAM_MAX_ROWS  # rows up to which a norm is split over two products
 
 
 @dataclass

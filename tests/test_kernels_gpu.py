@@ -540,6 +540,9 @@ def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
     (5, 1000, 200, True, False, 0),       # ragged rows of W, K of 3 blocks and a tail
     (13, 40000, 96, False, False, 0),     # more blocks than CTAs: no split, every CTA scales all rows
     (3, 384, 3584, False, True, 148),
+    (33, 2048, 1536, True, True, 0),      # more than 16 rows: the cluster reads its partial tiles
+    (64, 1536, 1536, False, True, 0),
+    (40, 40000, 96, True, False, 0),
 ])
 def test_gemm_stream_norm_taken_apart(M, N, K, bias, resid, target):
     """The few-row product with a norm split around it: rows times the gain as the operand, the
@@ -576,7 +579,7 @@ def test_gemm_stream_norm_taken_apart(M, N, K, bias, resid, target):
     assert torch.equal(gemm.linear(normed, w, b, residual=r), out) or target != 0
 
 
-@pytest.mark.parametrize("M,I,K", [(8, 8960, 1536), (16, 224, 96), (3, 512, 776)])
+@pytest.mark.parametrize("M,I,K", [(8, 8960, 1536), (16, 224, 96), (3, 512, 776), (64, 8960, 1536), (17, 224, 96)])
 def test_gemm_stream_norm_taken_apart_with_swiglu(M, I, K):
     from dispec_b200.ops import gemm, library
     eps = 1e-6
@@ -604,10 +607,11 @@ def test_gemm_stream_norm_taken_apart_with_swiglu(M, I, K):
     assert (out.double() - ref).abs().max() <= 1.25 * (two.double() - ref).abs().max() + 1e-3
 
 
-@pytest.mark.parametrize("M,N,K,target", [(8, 1536, 8960, 0), (16, 300, 96, 0), (2, 40000, 64, 0), (33, 512, 96, 0)])
+@pytest.mark.parametrize("M,N,K,target", [(8, 1536, 8960, 0), (16, 300, 96, 0), (2, 40000, 64, 0), (33, 512, 96, 0),
+                                          (64, 1536, 8960, 0), (70, 512, 96, 0)])
 def test_gemm_stream_scaled_second_output(M, N, K, target):
     """linear(then_norm=): beside its result the product stores the rounded result times the next
-    norm's gain (up to 16 rows); with more rows it stores nothing and the norm kernel runs."""
+    norm's gain; with more rows it stores nothing and the norm kernel runs."""
     from dispec_b200 import ops
     from dispec_b200.ops import gemm, library
     x = rnd((M, K), torch.bfloat16, 181)
