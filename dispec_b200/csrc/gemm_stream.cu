@@ -119,6 +119,19 @@ __device__ __forceinline__ void finish(const Args& a, float v, int m, int n) {
     reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * __bfloat162float(a.gain2[n]));
 }
 
+// sum of the squares of eight bfloat16 values
+__device__ __forceinline__ float square_sum8(const uint4 u) {
+  const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
+    ss += lo * lo;
+    ss += hi * hi;
+  }
+  return ss;
+}
+
 // The accumulator of this thread's W row: the partial accumulators added in a fixed order.
 template <int NB, int PARTS>
 __device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[NB]) {
@@ -299,17 +312,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   auto compute_row_scales = [&](int first, int step) {
     if (a.norm_src == nullptr) return;
     const int pieces = a.K / 8;
-    auto square_sum = [](const uint4 u) {
-      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-      float ss = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
-        ss += lo * lo;
-        ss += hi * hi;
-      }
-      return ss;
-    };
     for (int m0 = first + (warp - C::FIRST_EPI_WARP) * step; m0 < a.M; m0 += 8 * step) {
       const int m1 = m0 + 4 * step;
       const uint4* src0 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)m0 * a.ld_src);
@@ -325,8 +327,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          ss0 += square_sum(u0[i]);
-          ss1 += square_sum(u1[i]);
+          ss0 += square_sum8(u0[i]);
+          ss1 += square_sum8(u1[i]);
         }
       }
 #pragma unroll
@@ -340,6 +342,51 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+  };
+  // The same for the few rows a CTA of a cluster finishes (rank, rank + splits, ...): here the
+  // factors are wanted soon after the wait, so all 128 threads share each row and every piece of
+  // it is asked for at once (one trip to the L2 for K up to 4096); two rows at a time.
+  __shared__ float row_part[4][2];
+  auto compute_own_row_scales = [&](int first, int step) {
+    if (a.norm_src == nullptr) return;
+    const int pieces = a.K / 8;
+    const int t = (int)threadIdx.x - 32 * C::FIRST_EPI_WARP, w = t >> 5;
+    for (int m0 = first; m0 < a.M; m0 += 2 * step) {
+      const int m1 = m0 + step;
+      const uint4* src0 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)m0 * a.ld_src);
+      const uint4* src1 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)(m1 < a.M ? m1 : m0) * a.ld_src);
+      float ss0 = 0.f, ss1 = 0.f;
+      for (int g0 = t; g0 < pieces; g0 += 128 * 4) {
+        uint4 u0[4], u1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int g = g0 + 128 * i;
+          u0[i] = g < pieces ? src0[g] : make_uint4(0, 0, 0, 0);
+          u1[i] = (g < pieces && m1 < a.M) ? src1[g] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          ss0 += square_sum8(u0[i]);
+          ss1 += square_sum8(u1[i]);
+        }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        ss0 += __shfl_xor_sync(0xffffffffu, ss0, sft);
+        ss1 += __shfl_xor_sync(0xffffffffu, ss1, sft);
+      }
+      if (lane == 0) {
+        row_part[w][0] = ss0;
+        row_part[w][1] = ss1;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (t < 2) {
+        const int m = t == 0 ? m0 : m1;
+        const float ss = ((row_part[0][t] + row_part[1][t]) + row_part[2][t]) + row_part[3][t];
+        if (m < a.M) row_scale[m] = rsqrtf(ss / (float)a.K + a.norm_eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the factors are visible, the partial sums free again
+    }
   };
   if (splits == 1) {
     if (warp >= C::FIRST_EPI_WARP) {
@@ -405,7 +452,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float own_bias = 0.f, own_gain2 = 0.f;
     auto fetch_own = [&]() {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
-      compute_row_scales(rank, splits);  // of the rows this CTA finishes
       const int n = blockIdx.x * ROWS_W + row;
 #pragma unroll
       for (int slot = 0; slot < MAX_OWN; ++slot) {
@@ -415,6 +461,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
       if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
       if (!swiglu && a.C2 && n < a.N) own_gain2 = __bfloat162float(a.gain2[n]);
+      compute_own_row_scales(rank, splits);  // behind the loads above
     };
     if (warp >= C::FIRST_EPI_WARP) {
       fetch_own();
@@ -505,7 +552,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (warp >= C::FIRST_EPI_WARP) {
       if (a.norm_src) {  // the factors of the rows this CTA finishes, while the products run
         pdl_wait();
-        compute_row_scales((int)cluster.block_rank(), splits);
+        compute_own_row_scales((int)cluster.block_rank(), splits);
       }
       ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
