@@ -343,47 +343,48 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
   };
-  // The same for the few rows a CTA of a cluster finishes (rank, rank + splits, ...): here the
-  // factors are wanted soon after the wait, so all 128 threads share each row and every piece of
-  // it is asked for at once (one trip to the L2 for K up to 4096); two rows at a time.
-  __shared__ float row_part[4][2];
+  // The same for the rows a CTA of a cluster finishes (rank, rank + splits, ...): here the factors
+  // are wanted soon after the wait, so all 128 threads share each row and eight to sixteen loads of
+  // a thread are in flight: a CTA's whole share over 8 ranks at once (2, 4 or 8 rows), four pieces
+  // of a row per thread (K up to 4096 in one trip to the L2), two at 64 rows of A.
+  constexpr int OWN = NB == 16 ? 2 : NB == 32 ? 4 : 8, PIECES = NB == 64 ? 2 : 4;
+  __shared__ float row_part[4][OWN];
   auto compute_own_row_scales = [&](int first, int step) {
     if (a.norm_src == nullptr) return;
     const int pieces = a.K / 8;
     const int t = (int)threadIdx.x - 32 * C::FIRST_EPI_WARP, w = t >> 5;
-    for (int m0 = first; m0 < a.M; m0 += 2 * step) {
-      const int m1 = m0 + step;
-      const uint4* src0 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)m0 * a.ld_src);
-      const uint4* src1 = reinterpret_cast<const uint4*>(a.norm_src + (size_t)(m1 < a.M ? m1 : m0) * a.ld_src);
-      float ss0 = 0.f, ss1 = 0.f;
-      for (int g0 = t; g0 < pieces; g0 += 128 * 4) {
-        uint4 u0[4], u1[4];
+    for (int base = first; base < a.M; base += OWN * step) {
+      float ss[OWN];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int g = g0 + 128 * i;
-          u0[i] = g < pieces ? src0[g] : make_uint4(0, 0, 0, 0);
-          u1[i] = (g < pieces && m1 < a.M) ? src1[g] : make_uint4(0, 0, 0, 0);
+      for (int r = 0; r < OWN; ++r) ss[r] = 0.f;
+      for (int g0 = t; g0 < pieces; g0 += 128 * PIECES) {
+        uint4 u[OWN][PIECES];
+#pragma unroll
+        for (int r = 0; r < OWN; ++r) {
+          const int m = base + r * step;
+          const uint4* src = reinterpret_cast<const uint4*>(a.norm_src + (size_t)(m < a.M ? m : base) * a.ld_src);
+#pragma unroll
+          for (int i = 0; i < PIECES; ++i) {
+            const int g = g0 + 128 * i;
+            u[r][i] = (g < pieces && m < a.M) ? src[g] : make_uint4(0, 0, 0, 0);
+          }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          ss0 += square_sum8(u0[i]);
-          ss1 += square_sum8(u1[i]);
-        }
+        for (int r = 0; r < OWN; ++r)
+#pragma unroll
+          for (int i = 0; i < PIECES; ++i) ss[r] += square_sum8(u[r][i]);
       }
 #pragma unroll
-      for (int sft = 16; sft > 0; sft >>= 1) {
-        ss0 += __shfl_xor_sync(0xffffffffu, ss0, sft);
-        ss1 += __shfl_xor_sync(0xffffffffu, ss1, sft);
-      }
-      if (lane == 0) {
-        row_part[w][0] = ss0;
-        row_part[w][1] = ss1;
+      for (int r = 0; r < OWN; ++r) {
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], sft);
+        if (lane == 0) row_part[w][r] = ss[r];
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (t < 2) {
-        const int m = t == 0 ? m0 : m1;
-        const float ss = ((row_part[0][t] + row_part[1][t]) + row_part[2][t]) + row_part[3][t];
-        if (m < a.M) row_scale[m] = rsqrtf(ss / (float)a.K + a.norm_eps);
+      if (t < OWN) {
+        const int m = base + t * step;
+        const float sum = ((row_part[0][t] + row_part[1][t]) + row_part[2][t]) + row_part[3][t];
+        if (m < a.M) row_scale[m] = rsqrtf(sum / (float)a.K + a.norm_eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the factors are visible, the partial sums free again
     }
@@ -391,7 +392,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (splits == 1) {
     if (warp >= C::FIRST_EPI_WARP) {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
-      compute_row_scales(0, 1);
+      if constexpr (NB <= 32) compute_row_scales(0, 1);
+      else compute_own_row_scales(0, 1);  // many rows: more loads in flight
       int local = 0;
       for (int nb = blockIdx.x; nb < n_blocks; nb += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -549,11 +551,25 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float* red = reinterpret_cast<float*>(smem);  // [NB][128], reuses the ring once it has drained
     bool ok = true;
     cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int n = blockIdx.x * ROWS_W + row;
+    // eight rows of this CTA's share at a time: their bias, residual and norm factors are asked for
+    // while the products still run, their partial sums from every CTA of the cluster at once
+    // (remote reads take a few hundred cycles each), then added in rank order
+    constexpr int AT_ONCE = 8;
+    float own_res[AT_ONCE];
+    float own_bias = 0.f, own_gain2 = 0.f;
     if (warp >= C::FIRST_EPI_WARP) {
-      if (a.norm_src) {  // the factors of the rows this CTA finishes, while the products run
-        pdl_wait();
-        compute_own_row_scales((int)cluster.block_rank(), splits);
+      pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+#pragma unroll
+      for (int j = 0; j < AT_ONCE; ++j) {
+        const int m = rank + j * splits;
+        own_res[j] = (!swiglu && a.residual && m < a.M && n < a.N)
+                         ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f;
       }
+      if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
+      if (!swiglu && a.C2 && n < a.N) own_gain2 = __bfloat162float(a.gain2[n]);
+      compute_own_row_scales(rank, splits);
       ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
       if (!ok) failed = 1;
       tc_fence_after();
@@ -568,50 +584,41 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     cluster.sync();
     if (warp >= C::FIRST_EPI_WARP && !failed) {
-      pdl_wait();
-      const int rank = (int)cluster.block_rank();
-      const int n = blockIdx.x * ROWS_W + row;
-      // the partial sums of four rows are requested from every CTA of the cluster at once (remote
-      // reads take a few hundred cycles each), then added in rank order
-      constexpr int ROWS_AT_ONCE = 4;
       const float* remote[MAX_SPLITS];
 #pragma unroll
       for (int sp = 0; sp < MAX_SPLITS; ++sp) remote[sp] = cluster.map_shared_rank(red, sp < splits ? sp : 0);
-      const bool up_lane = swiglu && lane < 16;
-      for (int m0 = rank; m0 < a.M; m0 += splits * ROWS_AT_ONCE) {
-        float part[ROWS_AT_ONCE][MAX_SPLITS], part_up[ROWS_AT_ONCE][MAX_SPLITS];
+      bool first = true;
+      for (int m0 = rank; m0 < a.M; m0 += splits * AT_ONCE, first = false) {
+        float part[AT_ONCE][MAX_SPLITS];
 #pragma unroll
-        for (int j = 0; j < ROWS_AT_ONCE; ++j) {
+        for (int j = 0; j < AT_ONCE; ++j) {
           const int m = m0 + j * splits;
 #pragma unroll
-          for (int sp = 0; sp < MAX_SPLITS; ++sp) {
-            const bool on = sp < splits && m < a.M;
-            part[j][sp] = on ? remote[sp][m * ROWS_W + row] : 0.f;
-            part_up[j][sp] = (on && up_lane) ? remote[sp][m * ROWS_W + row + 16] : 0.f;
-          }
+          for (int sp = 0; sp < MAX_SPLITS; ++sp)
+            part[j][sp] = (sp < splits && m < a.M) ? remote[sp][m * ROWS_W + row] : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < ROWS_AT_ONCE; ++j) {
+        for (int j = 0; j < AT_ONCE; ++j) {
           const int m = m0 + j * splits;
           if (m >= a.M) break;
-          float total = 0.f, total_up = 0.f;
+          float total = 0.f;
 #pragma unroll
-          for (int sp = 0; sp < MAX_SPLITS; ++sp) {
-            if (sp < splits) {
-              total += part[j][sp];
-              total_up += part_up[j][sp];
-            }
-          }
-          if (a.norm_src) {
-            total *= row_scale[m];
-            total_up *= row_scale[m];
-          }
+          for (int sp = 0; sp < MAX_SPLITS; ++sp)
+            if (sp < splits) total += part[j][sp];
+          if (a.norm_src) total *= row_scale[m];
           if (swiglu) {
+            // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs
+            const float up = __shfl_down_sync(0xffffffffu, total, 16);
             if (lane < 16 && n + 16 < a.N)
               reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                  from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+                  from_f32<TOut>(total / (1.f + expf(-total)) * up);
           } else if (n < a.N) {
-            finish<TOut>(a, total, m, n);
+            const float res = first ? own_res[j]
+                                    : (a.residual ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f);
+            // the same order of sums as finish(): bias, then residual
+            const TOut out = from_f32<TOut>((total + own_bias) + res);
+            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = out;
+            if (a.C2) reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * own_gain2);
           }
         }
       }

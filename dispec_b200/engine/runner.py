@@ -48,7 +48,9 @@ class ModelRunner:
                            and all(getattr(p, "graph_safe", True) for p in model._parts))
         # captured decode steps, one per padded batch size; the page tables of a captured step
         # have room for the longest sequence the pools or the model allow
-        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_num_seqs]
+        # (powers of two, and the largest batch itself so that every batch has a bucket)
+        self.graph_buckets = [1 << i for i in range(13) if (1 << i) < max_num_seqs]
+        self.graph_buckets.append(max_num_seqs)
         # the longest request: the configuration's max_position_embeddings unless the caller says
         # otherwise (angles are computed from the position, so no table stands in the way of more)
         limit = max_model_len or model.spec.max_position or (1 << 30)
