@@ -406,8 +406,10 @@ def decode_timeline(args) -> dict:
         row = {"ctas": int(ctas),
                "end_of_previous_product_to_wait": round(float(s[:, 1].min() - prev_end) / 1000.0, 2) if prev_end else None,
                "wait_to_first_stage": phase(s, 1, 2), "first_stage_to_last_product_issued": phase(s, 2, 3),
-               "last_w_requested_to_last_product": phase(s, 7, 3), "accumulator_to_partials_arrived": phase(s, 4, 5),
-               "partials_arrived_to_rows_stored": phase(s, 5, 9), "wait_to_end": phase(s, 1, 6)}
+               "last_w_requested_to_last_product": phase(s, 7, 3), "last_product_issued_to_accumulator": phase(s, 3, 4),
+               "accumulator_to_cluster_barrier": phase(s, 4, 11),
+               "accumulator_to_partials_arrived": phase(s, 4, 5), "partials_arrived_to_rows_stored": phase(s, 5, 9),
+               "accumulator_to_end": phase(s, 4, 6), "wait_to_end": phase(s, 1, 6)}
         prev_end = s[:, 6].max()
         products.setdefault(name, []).append(row)
     attention = []

@@ -12,14 +12,14 @@
 //
 // K is split across a thread-block cluster (up to 8 CTAs) when there are too few 128-row blocks
 // of W to fill the SMs, and the partial tiles are added through distributed shared memory in rank
-// order (deterministic, no global scratch).  Up to 16 rows of A: every CTA sends each row of its
-// partial tile to the CTA that finishes that row (remote stores into an inbox beside the ring,
-// nobody waits for them), one cluster barrier, and every CTA adds what arrived in its own memory:
-// no remote read, and no CTA waits for the others before it leaves (0.5 to 0.9 us per launch
-// less than the other form).  More rows: each CTA leaves its partial tile in its shared memory
-// and, after a cluster barrier, reads its share from every rank; a second barrier keeps the CTAs
-// until all have read.  Without a split a CTA walks over several blocks of W and
-// the accumulator is double-buffered, so the epilogue of one block overlaps the next.
+// order (deterministic, no global scratch): every CTA sends each row of its partial tile to the
+// CTA that finishes that row (remote stores that count their bytes on a barrier of the receiver)
+// and adds what arrived in its own memory; no remote read, and no CTA waits for the others
+// before it leaves.  Up to 16 rows of A the inbox lies beside the ring and nobody waits for the
+// cluster at all; with more rows the inbox is part of the drained ring, which costs one cluster
+// barrier, and whole rows travel 16 bytes a lane.  Without a split a CTA walks over several
+// blocks of W and the accumulator is double-buffered, so the epilogue of one block overlaps the
+// next.
 //
 // Epilogues: bias[n], residual[m, n] (32-bit sum, rounded once), or SwiGLU over W rows that
 // alternate in blocks of 16 (16 gate rows, the 16 up rows of the same outputs): C is [M, N/2].
@@ -119,6 +119,35 @@ __device__ __forceinline__ void finish(const Args& a, float v, int m, int n) {
     reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * __bfloat162float(a.gain2[n]));
 }
 
+// silu(gate) * up for the bfloat16 model.  One warp per scheduler runs the epilogue, so its length
+// in instructions is its time: the hardware's exponential and reciprocal (a few units in the last
+// place of 32 bits, far below the output's rounding) instead of the library's sequences, which at
+// 64 rows of A made the epilogue of the gate/up product 3.9 us long.
+__device__ __forceinline__ float silu_times(float gate, float up) {
+  return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
+
+// four consecutive values of a row, as 32-bit floats
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+// what a store of the output type leaves of four 32-bit values
+template <typename T> __device__ __forceinline__ float4 rounded4(float4 v) {
+  return make_float4(to_f32(from_f32<T>(v.x)), to_f32(from_f32<T>(v.y)), to_f32(from_f32<T>(v.z)),
+                     to_f32(from_f32<T>(v.w)));
+}
+
 // sum of the squares of eight bfloat16 values
 __device__ __forceinline__ float square_sum8(const uint4 u) {
   const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
@@ -154,16 +183,17 @@ __device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[N
       v[c] = __float_as_uint(sum);
     }
   } else {
+    // 32 columns of every partial accumulator per trip to the tensor memory (a load and its wait
+    // take a few hundred nanoseconds: they are not taken one after the other)
+    static_assert(PARTS == 2, "two partial accumulators");
 #pragma unroll
     for (int c0 = 0; c0 < NB; c0 += 32) {
       uint32_t part[32];
-      tmem_ld32(taddr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+      tmem_ld32_nowait(taddr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+      tmem_ld32_nowait(taddr + (uint32_t)(NB + c0), part);
+      tmem_ld_wait();
 #pragma unroll
-      for (int p = 1; p < PARTS; ++p) {
-        tmem_ld32(taddr + (uint32_t)(p * NB + c0), part);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) v[c0 + c] = __float_as_uint(__uint_as_float(v[c0 + c]) + __uint_as_float(part[c]));
-      }
+      for (int c = 0; c < 32; ++c) v[c0 + c] = __float_as_uint(__uint_as_float(v[c0 + c]) + __uint_as_float(part[c]));
     }
   }
 }
@@ -408,6 +438,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
+        if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // the accumulator is in registers
         if (a.norm_src) {
 #pragma unroll
           for (int m = 0; m < NB; ++m)
@@ -428,13 +459,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const float gate = low ? x0 : other, up = low ? other : x1;
             const int m = low ? m0 : m0 + 1;
             if (m < a.M && n_ok)
-              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + col] = from_f32<TOut>(silu_times(gate, up));
           }
         } else {
 #pragma unroll
           for (int m = 0; m < NB; ++m)
             if (m < a.M && n < a.N) finish<TOut>(a, __uint_as_float(v[m]), m, n);
         }
+        if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // the block's stores are issued
       }
     }
     __syncthreads();
@@ -528,7 +560,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (swiglu) {
           if (lane < 16 && n + 16 < a.N)
             reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                from_f32<TOut>(total / (1.f + expf(-total)) * total_up);
+                from_f32<TOut>(silu_times(total, total_up));
         } else if (n < a.N) {
           // the same order of sums as finish(): bias, then residual
           const TOut out = from_f32<TOut>((total + own_bias) + res);
@@ -547,83 +579,118 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // this CTA's rows are stored
     }
   } else {
-    // one block per CTA; the cluster adds the partial tiles
-    float* red = reinterpret_cast<float*>(smem);  // [NB][128], reuses the ring once it has drained
-    bool ok = true;
+    // One block per CTA and more than 16 rows of A; the cluster adds the partial tiles.  This part
+    // runs once per CTA, so what it costs is the instructions it fetches and the trips it waits
+    // for, and it is written for few of both.  Every thread puts its accumulators (one W row, all
+    // rows of A) into the drained ring, [row of A][128]; after one cluster barrier (every CTA is
+    // through with its ring) a warp sends whole rows of A, 16 bytes a lane, to the CTA that
+    // finishes them (row m to rank m % splits) by remote stores that count their bytes on the
+    // receiver's barrier; a CTA waits for the bytes due in its inbox (a second part of the ring)
+    // and a warp finishes whole rows, four outputs a lane.  The loops over rows are rolled.
+    // (Measured at 64 rows, whole decode step of the 1.5B shape: partial tiles read from every rank
+    // between two cluster barriers 1.89 ms; this form 1.79 ms; the same with one bulk copy per row
+    // and a second barrier that keeps the tiles in place 1.80 ms; with one bulk copy per rank from
+    // a tile ordered by rank 2.00 ms, its unrolled stores with computed addresses being the cost.)
+    const int rows_per = (a.M + splits - 1) / splits;
+    float* tile = reinterpret_cast<float*>(smem);                    // [row of A][128]
+    float* inbox = tile + NB * ROWS_W;                               // [source rank][rows per CTA][128]
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
-    const int n = blockIdx.x * ROWS_W + row;
-    // eight rows of this CTA's share at a time: their bias, residual and norm factors are asked for
-    // while the products still run, their partial sums from every CTA of the cluster at once
-    // (remote reads take a few hundred cycles each), then added in rank order
-    constexpr int AT_ONCE = 8;
-    float own_res[AT_ONCE];
-    float own_bias = 0.f, own_gain2 = 0.f;
+    const int rows_own = rank < a.M ? (a.M - rank + splits - 1) / splits : 0;
+    const int ew = warp - C::FIRST_EPI_WARP;                          // 0..3 in the epilogue warps
+    const int n4 = blockIdx.x * ROWS_W + 4 * lane;                    // this lane's four outputs of a row
+    const bool n_ok = n4 < a.N;                                       // N is a multiple of 4 here
+    // bias, and the residual of the first two rows this warp finishes (its share at 64 rows over 8
+    // ranks), are asked for while the products still run
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gain4 = bias4, res4[2] = {bias4, bias4};
     if (warp >= C::FIRST_EPI_WARP) {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
+      if (!swiglu && n_ok) {
+        if (a.bias) bias4 = load4(a.bias + n4);
+        if (a.C2) gain4 = load4(a.gain2 + n4);
 #pragma unroll
-      for (int j = 0; j < AT_ONCE; ++j) {
-        const int m = rank + j * splits;
-        own_res[j] = (!swiglu && a.residual && m < a.M && n < a.N)
-                         ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f;
+        for (int i = 0; i < 2; ++i) {
+          const int m = rank + (ew + 4 * i) * splits;
+          if (a.residual && m < a.M) res4[i] = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
+        }
       }
-      if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
-      if (!swiglu && a.C2 && n < a.N) own_gain2 = __bfloat162float(a.gain2[n]);
       compute_own_row_scales(rank, splits);
-      ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
-      if (!ok) failed = 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0))) failed = 1;
       tc_fence_after();
-      if (ok) {
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // the accumulator is complete
+      {
         uint32_t v[NB];
         load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16), v);
 #pragma unroll
-        for (int m = 0; m < NB; ++m) red[m * ROWS_W + row] = __uint_as_float(v[m]);
+        for (int m = 0; m < NB; ++m) tile[m * ROWS_W + row] = __uint_as_float(v[m]);
       }
     }
     tc_fence_before();
     __syncthreads();
-    cluster.sync();
-    if (warp >= C::FIRST_EPI_WARP && !failed) {
-      const float* remote[MAX_SPLITS];
-#pragma unroll
-      for (int sp = 0; sp < MAX_SPLITS; ++sp) remote[sp] = cluster.map_shared_rank(red, sp < splits ? sp : 0);
-      bool first = true;
-      for (int m0 = rank; m0 < a.M; m0 += splits * AT_ONCE, first = false) {
-        float part[AT_ONCE][MAX_SPLITS];
-#pragma unroll
-        for (int j = 0; j < AT_ONCE; ++j) {
-          const int m = m0 + j * splits;
-#pragma unroll
-          for (int sp = 0; sp < MAX_SPLITS; ++sp)
-            part[j][sp] = (sp < splits && m < a.M) ? remote[sp][m * ROWS_W + row] : 0.f;
+    cluster.sync();  // every CTA's products are done: the rings are free, the tiles in place
+    if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(11);
+    if (warp >= C::FIRST_EPI_WARP) {
+      if (!failed) {
+        // a warp sends whole rows of A, 16 bytes a lane: row m to rank m % splits, slot m / splits
+#pragma unroll 1
+        for (int m = ew; m < a.M; m += 4) {
+          const uint32_t owner = (uint32_t)(m % splits);
+          const int slot = m / splits;
+          const float4 val = reinterpret_cast<const float4*>(tile + m * ROWS_W)[lane];
+          const uint32_t dst = mapa_u32(smem_u32(inbox + (rank * rows_per + slot) * ROWS_W + 4 * lane), owner);
+          st_async_v4(dst, val, mapa_u32(smem_u32(&inbox_bar), owner));
         }
+      }
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) mbar_expect_tx(&inbox_bar, (uint32_t)(splits * rows_own * ROWS_W * 4));
+      if (!__all_sync(0xffffffffu, mbar_wait(&inbox_bar, 0))) failed = 1;
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // every rank's rows have arrived
+      if (!failed) {
+#pragma unroll 1
+        for (int slot = ew, i = 0; slot < rows_own; slot += 4, ++i) {
+          const int m = rank + slot * splits;
+          float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < AT_ONCE; ++j) {
-          const int m = m0 + j * splits;
-          if (m >= a.M) break;
-          float total = 0.f;
-#pragma unroll
-          for (int sp = 0; sp < MAX_SPLITS; ++sp)
-            if (sp < splits) total += part[j][sp];
-          if (a.norm_src) total *= row_scale[m];
+          for (int sp = 0; sp < MAX_SPLITS; ++sp) {  // in rank order
+            if (sp < splits) {
+              const float4 part = reinterpret_cast<const float4*>(inbox + (sp * rows_per + slot) * ROWS_W)[lane];
+              total.x += part.x, total.y += part.y, total.z += part.z, total.w += part.w;
+            }
+          }
+          if (a.norm_src) {
+            const float scale = row_scale[m];
+            total.x *= scale, total.y *= scale, total.z *= scale, total.w *= scale;
+          }
           if (swiglu) {
-            // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 outputs
-            const float up = __shfl_down_sync(0xffffffffu, total, 16);
-            if (lane < 16 && n + 16 < a.N)
-              reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                  from_f32<TOut>(total / (1.f + expf(-total)) * up);
-          } else if (n < a.N) {
-            const float res = first ? own_res[j]
-                                    : (a.residual ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f);
+            // a lane holds four W rows; of every 32 rows the first 16 are gates, the other 16 the up
+            // rows of the same outputs: lanes 0..3 of eight pair with lanes 4..7
+            float4 up;
+            up.x = __shfl_down_sync(0xffffffffu, total.x, 4);
+            up.y = __shfl_down_sync(0xffffffffu, total.y, 4);
+            up.z = __shfl_down_sync(0xffffffffu, total.z, 4);
+            up.w = __shfl_down_sync(0xffffffffu, total.w, 4);
+            if ((lane & 4) == 0 && n4 + 16 < a.N) {
+              const int col = ((blockIdx.x * ROWS_W + (lane >> 3) * 32) >> 1) + 4 * (lane & 3);
+              store4(reinterpret_cast<TOut*>(a.C) + (size_t)m * a.ldc + col,
+                     make_float4(silu_times(total.x, up.x), silu_times(total.y, up.y), silu_times(total.z, up.z),
+                                 silu_times(total.w, up.w)));
+            }
+          } else if (n_ok) {
+            float4 res = i == 0 ? res4[0] : res4[1];
+            if (i >= 2 && a.residual) res = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
             // the same order of sums as finish(): bias, then residual
-            const TOut out = from_f32<TOut>((total + own_bias) + res);
-            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = out;
-            if (a.C2) reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * own_gain2);
+            total.x = (total.x + bias4.x) + res.x, total.y = (total.y + bias4.y) + res.y;
+            total.z = (total.z + bias4.z) + res.z, total.w = (total.w + bias4.w) + res.w;
+            store4(reinterpret_cast<TOut*>(a.C) + (size_t)m * a.ldc + n4, total);
+            if (a.C2) {
+              const float4 out = rounded4<TOut>(total);
+              store4(reinterpret_cast<TOut*>(a.C2) + (size_t)m * a.ldc2 + n4,
+                     make_float4(out.x * gain4.x, out.y * gain4.y, out.z * gain4.z, out.w * gain4.w));
+            }
           }
         }
       }
+      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // this CTA's rows are stored
     }
-    cluster.sync();  // nobody leaves while its shared memory may still be read
   }
 
   // every warp is through with the tensor memory before it is given back
@@ -754,6 +821,16 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   if (splits < 1) splits = 1;
   if (splits > MAX_SPLITS) splits = MAX_SPLITS;
   if (splits > kb_total) splits = kb_total;
+  if (nb_rows > 16 && splits > 1) {
+    // with more than 16 rows the cluster's sum moves four outputs at a time: rows and pointers
+    // must allow 16-byte (32-bit output) or 8-byte accesses, else K is not split
+    const uintptr_t mask = out_dtype == DSP_F32 ? 15 : 7;
+    const bool vec_ok = N % 4 == 0 && ldc % 4 == 0 && ((uintptr_t)C & mask) == 0 &&
+                        (residual == nullptr || (ldr % 4 == 0 && ((uintptr_t)residual & mask) == 0)) &&
+                        (bias == nullptr || ((uintptr_t)bias & 7) == 0) &&
+                        (C2 == nullptr || (ldc2 % 4 == 0 && ((uintptr_t)C2 & mask) == 0 && ((uintptr_t)gain2 & 7) == 0));
+    if (!vec_ok) splits = 1;
+  }
   const int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;
   Args a;
