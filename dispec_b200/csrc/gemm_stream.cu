@@ -15,9 +15,9 @@
 // order (deterministic, no global scratch): every CTA sends each row of its partial tile to the
 // CTA that finishes that row (remote stores that count their bytes on a barrier of the receiver)
 // and adds what arrived in its own memory; no remote read, and no CTA waits for the others
-// before it leaves.  Up to 16 rows of A the inbox lies beside the ring and nobody waits for the
-// cluster at all; with more rows the inbox is part of the drained ring, which costs one cluster
-// barrier, and whole rows travel 16 bytes a lane.  Without a split a CTA walks over several
+// before it leaves: whole rows travel 16 bytes a lane.  Up to 16 rows of A the inbox lies behind
+// the ring and nobody waits for the cluster at all; with more rows the inbox is part of the
+// drained ring, which costs one cluster barrier.  Without a split a CTA walks over several
 // blocks of W and the accumulator is double-buffered, so the epilogue of one block overlaps the
 // next.
 //
@@ -61,11 +61,13 @@ template <int NB> struct Cfg {
   static constexpr int THREADS = 32 * (1 + ISSUERS + 4);
   static constexpr int ACC_COLS = PARTS * NB;  // one accumulator buffer
   static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
-  // K split over a cluster, up to 16 rows of A: every CTA sends the rows of its partial tile to the
-  // CTA that finishes them (row m to rank m % splits), into an inbox beside the ring:
-  // [source rank][rows per CTA][128] floats, at most (16 + 8) rows
+  // K split over a cluster: every CTA sends the rows of its partial tile to the CTA that finishes
+  // them (row m to rank m % splits), into an inbox of [source rank][rows per CTA][128] floats.  Up
+  // to 16 rows of A (at most 16 + 8 rows of inbox) it has room of its own behind the ring
   static constexpr bool PUSH = NB == 16;
-  static constexpr int INBOX_BYTES = PUSH ? (16 + MAX_SPLITS) * ROWS_W * 4 : 0;
+  // behind the ring: that inbox, or 8 KB in which, without a split of K, an epilogue warp turns 16
+  // columns of its accumulator around, so that a lane stores four outputs of one row
+  static constexpr int INBOX_BYTES = PUSH ? (16 + MAX_SPLITS) * ROWS_W * 4 : 4 * 16 * 32 * 4;
 };
 
 // Timestamps for measurements, compiled in only with -DDSP_STAMPS (DISPEC_B200_STAMPS=1 at build
@@ -97,6 +99,7 @@ struct Args {
   // when the next kernel may start (programmatic dependent launch): 0 at once, 1 when this CTA has
   // requested its last tile of W
   int late_trigger;
+  int vec4;  // rows and pointers allow stores of four outputs (N, row strides: multiples of 4; 16-byte pointers)
   // A norm around the product, split over two kernels (both null: none).  norm_src: the rows whose
   // mean square scales this product's rows, C = (A W^T) * rsqrt(mean(norm_src[m]^2) + norm_eps) + ...,
   // A being those rows times the norm's gain.  gain2, C2: a second output, the rounded result times
@@ -439,6 +442,50 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
         if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // the accumulator is in registers
+        if (a.vec4 && !swiglu && a.residual == nullptr) {
+          // Sixteen columns (rows of A) at a time go through shared memory and come back turned
+          // around: a lane then holds four W rows of one row of A, the loop over the rows is rolled
+          // (its instructions are fetched once) and a store carries four outputs.  (The output head
+          // at 64 rows: 5.9 -> 1.9 us from the last accumulator to the last store.  The SwiGLU
+          // epilogue written this way measured no faster than the form below, which pairs rows.)
+          float* stage = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES) + (warp - C::FIRST_EPI_WARP) * 512;
+          const int sub = lane >> 3, l8 = lane & 7;
+          const int n4 = nb * ROWS_W + quarter * 32 + 4 * l8;
+          float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gain4 = bias4;
+          if (n4 < a.N) {
+            if (a.bias) bias4 = load4(a.bias + n4);
+            if (a.C2) gain4 = load4(a.gain2 + n4);
+          }
+#pragma unroll
+          for (int c0 = 0; c0 < NB; c0 += 16) {
+            if (c0 >= a.M) break;
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stage[j * 32 + lane] = __uint_as_float(v[c0 + j]);
+            __syncwarp();
+#pragma unroll 1
+            for (int it = 0; it < 4; ++it) {
+              const int m = c0 + 4 * it + sub;
+              float4 val = *reinterpret_cast<const float4*>(stage + (4 * it + sub) * 32 + 4 * l8);
+              if (a.norm_src) {
+                const float scale = row_scale[m];
+                val.x *= scale, val.y *= scale, val.z *= scale, val.w *= scale;
+              }
+              if (m < a.M && n4 < a.N) {
+                val.x += bias4.x, val.y += bias4.y, val.z += bias4.z, val.w += bias4.w;
+                store4(reinterpret_cast<TOut*>(a.C) + (size_t)m * a.ldc + n4, val);
+                if (a.C2) {
+                  const float4 out = rounded4<TOut>(val);
+                  store4(reinterpret_cast<TOut*>(a.C2) + (size_t)m * a.ldc2 + n4,
+                         make_float4(out.x * gain4.x, out.y * gain4.y, out.z * gain4.z, out.w * gain4.w));
+                }
+              }
+            }
+          }
+          if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // the block's stores are issued
+          continue;
+        }
+        // (SwiGLU, a residual, or rows or pointers that do not allow that: one output per thread and row)
         if (a.norm_src) {
 #pragma unroll
           for (int m = 0; m < NB; ++m)
@@ -470,130 +517,28 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
     __syncthreads();
-  } else if constexpr (C::PUSH) {
-    // one block per CTA; every CTA sends each row of its partial tile to the CTA that finishes that
-    // row: remote stores that count their bytes on a barrier of the receiving CTA.  A CTA waits only
-    // for the bytes that are due in its own inbox (never for the whole cluster), adds them in rank
-    // order and leaves; nobody reads another's memory.
-    cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank();
-    const int rows_per = (a.M + splits - 1) / splits;
-    float* inbox = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // second half of the start barrier
-    // bias and residual of the rows this CTA finishes are fetched while the products still run
-    constexpr int MAX_OWN = 8;  // rows per CTA: at most 16 rows over at least 2 ranks
-    float own_res[MAX_OWN];
-    float own_bias = 0.f, own_gain2 = 0.f;
-    auto fetch_own = [&]() {
-      pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
-      const int n = blockIdx.x * ROWS_W + row;
-#pragma unroll
-      for (int slot = 0; slot < MAX_OWN; ++slot) {
-        const int m = rank + slot * splits;
-        own_res[slot] = (!swiglu && a.residual && m < a.M && n < a.N)
-                            ? to_f32(reinterpret_cast<const TOut*>(a.residual)[(size_t)m * a.ldr + n]) : 0.f;
-      }
-      if (!swiglu && a.bias && n < a.N) own_bias = __bfloat162float(a.bias[n]);
-      if (!swiglu && a.C2 && n < a.N) own_gain2 = __bfloat162float(a.gain2[n]);
-      compute_own_row_scales(rank, splits);  // behind the loads above
-    };
-    if (warp >= C::FIRST_EPI_WARP) {
-      fetch_own();
-#ifdef DSP_STAMPS
-      asm volatile("" ::"f"(own_res[0]), "f"(own_bias));  // bias and residual have arrived
-#endif
-      const bool ok = __all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0));
-      if (!ok) failed = 1;
-      tc_fence_after();
-      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // the accumulator is complete
-      if (ok) {
-        uint32_t v[NB];
-        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16), v);
-        int owner = 0, slot = 0;
-#pragma unroll
-        for (int m = 0; m < NB; ++m) {
-          if (m < a.M) {
-            const uint32_t dst = mapa_u32(smem_u32(inbox + ((rank * rows_per + slot) * ROWS_W + row)), (uint32_t)owner);
-            st_async_b32(dst, v[m], mapa_u32(smem_u32(&inbox_bar), (uint32_t)owner));
-          }
-          if (++owner == splits) {
-            owner = 0;
-            ++slot;
-          }
-        }
-      }
-    }
-    // the rows this CTA finishes: rank, rank + splits, ...; every rank sends 128 floats of each
-    const int rows_own = rank < a.M ? (a.M - rank + splits - 1) / splits : 0;
-    if (threadIdx.x == 32 * C::FIRST_EPI_WARP) mbar_expect_tx(&inbox_bar, (uint32_t)(splits * rows_own * ROWS_W * 4));
-    if (warp >= C::FIRST_EPI_WARP && !__all_sync(0xffffffffu, mbar_wait(&inbox_bar, 0))) failed = 1;
-    if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // every rank's partial rows have arrived
-    if (warp >= C::FIRST_EPI_WARP && !failed) {
-      const int n = blockIdx.x * ROWS_W + row;
-      // Sums one row's partial values (all ranks' loads at once, added in rank order) and stores it.
-      // This is the last link before the next kernel may go on, and its instructions run once per
-      // CTA, cold: the usual case, one row per CTA, is straight code; further rows (more rows of A
-      // than ranks) take the loop behind a branch that the usual case never fetches.
-      auto finish_row = [&](int slot, float res) {
-        const int m = rank + slot * splits;
-        if (m >= a.M) return;
-        float part[MAX_SPLITS], part_up[MAX_SPLITS];
-#pragma unroll
-        for (int sp = 0; sp < MAX_SPLITS; ++sp) {
-          const float* src = inbox + ((sp < splits ? sp : 0) * rows_per + slot) * ROWS_W + row;
-          part[sp] = src[0];
-          part_up[sp] = (swiglu && lane < 16) ? src[16] : 0.f;
-        }
-        float total = 0.f, total_up = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < MAX_SPLITS; ++sp) {
-          if (sp < splits) {
-            total += part[sp];
-            total_up += part_up[sp];
-          }
-        }
-        if (a.norm_src) {
-          const float scale = row_scale[m];
-          total *= scale;
-          total_up *= scale;
-        }
-        if (swiglu) {
-          if (lane < 16 && n + 16 < a.N)
-            reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + ((n - lane) >> 1) + lane] =
-                from_f32<TOut>(silu_times(total, total_up));
-        } else if (n < a.N) {
-          // the same order of sums as finish(): bias, then residual
-          const TOut out = from_f32<TOut>((total + own_bias) + res);
-          reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + n] = out;
-          if (a.C2) reinterpret_cast<TOut*>(a.C2)[(size_t)m * a.ldc2 + n] = from_f32<TOut>(to_f32(out) * own_gain2);
-        }
-      };
-      finish_row(0, own_res[0]);
-      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(8);  // the first row is stored
-      if (rows_per > 1) finish_row(1, own_res[1]);  // up to 16 rows over 8 ranks
-      if (rows_per > 2) {
-#pragma unroll
-        for (int slot = 2; slot < MAX_OWN; ++slot)
-          if (slot < rows_per) finish_row(slot, own_res[slot]);
-      }
-      if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // this CTA's rows are stored
-    }
   } else {
-    // One block per CTA and more than 16 rows of A; the cluster adds the partial tiles.  This part
-    // runs once per CTA, so what it costs is the instructions it fetches and the trips it waits
-    // for, and it is written for few of both.  Every thread puts its accumulators (one W row, all
-    // rows of A) into the drained ring, [row of A][128]; after one cluster barrier (every CTA is
-    // through with its ring) a warp sends whole rows of A, 16 bytes a lane, to the CTA that
+    // One block per CTA; the cluster adds the partial tiles.  This part runs once per CTA, so what
+    // it costs is the instructions it fetches and the trips it waits for, and it is written for
+    // few of both.  Every thread puts its accumulators (one W row, all rows of A) into the drained
+    // ring, [row of A][128]; a warp sends whole rows of A, 16 bytes a lane, to the CTA that
     // finishes them (row m to rank m % splits) by remote stores that count their bytes on the
-    // receiver's barrier; a CTA waits for the bytes due in its inbox (a second part of the ring)
-    // and a warp finishes whole rows, four outputs a lane.  The loops over rows are rolled.
-    // (Measured at 64 rows, whole decode step of the 1.5B shape: partial tiles read from every rank
-    // between two cluster barriers 1.89 ms; this form 1.79 ms; the same with one bulk copy per row
-    // and a second barrier that keeps the tiles in place 1.80 ms; with one bulk copy per rank from
-    // a tile ordered by rank 2.00 ms, its unrolled stores with computed addresses being the cost.)
+    // receiver's barrier; a CTA waits for the bytes due in its inbox and a warp finishes whole
+    // rows, four outputs a lane.  The loops over rows are rolled.  Up to 16 rows of A the inbox
+    // has room of its own behind the ring, so nobody waits for the cluster (the barrier whose first
+    // half was passed at the start only says that every CTA is running); with more rows it is a
+    // second part of the ring, and one cluster barrier says that every CTA is through with its ring.
+    // (Measured on the whole decode step of the 1.5B shape.  64 rows: partial tiles read from every
+    // rank between two cluster barriers 1.89 ms; this form 1.79 ms; the same with one bulk copy per
+    // row and a second barrier that keeps the tiles in place 1.80 ms; with one bulk copy per rank
+    // from a tile ordered by rank 2.00 ms, its unrolled stores with computed addresses being the
+    // cost.  8 rows: every thread sending its own 4-byte values, unrolled, 1.000 ms; this form
+    // 0.988 ms; 1 row 0.989 -> 0.949 ms.)
     const int rows_per = (a.M + splits - 1) / splits;
     float* tile = reinterpret_cast<float*>(smem);                    // [row of A][128]
-    float* inbox = tile + NB * ROWS_W;                               // [source rank][rows per CTA][128]
+    // [source rank][rows per CTA][128]: behind the ring where there is room for it (up to 16 rows)
+    float* inbox = C::PUSH ? reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES) : tile + NB * ROWS_W;
+    if constexpr (C::PUSH) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // second half of the start barrier
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int rows_own = rank < a.M ? (a.M - rank + splits - 1) / splits : 0;
@@ -625,9 +570,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int m = 0; m < NB; ++m) tile[m * ROWS_W + row] = __uint_as_float(v[m]);
       }
     }
-    tc_fence_before();
-    __syncthreads();
-    cluster.sync();  // every CTA's products are done: the rings are free, the tiles in place
+    if constexpr (C::PUSH) {
+      // the inbox is nobody's ring: only this CTA's epilogue warps meet, over the tile
+      if (warp >= C::FIRST_EPI_WARP) asm volatile("bar.sync 1, 128;" ::: "memory");
+    } else {
+      tc_fence_before();
+      __syncthreads();
+      cluster.sync();  // every CTA's products are done: the rings are free, the tiles in place
+    }
     if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(11);
     if (warp >= C::FIRST_EPI_WARP) {
       if (!failed) {
@@ -821,16 +771,14 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   if (splits < 1) splits = 1;
   if (splits > MAX_SPLITS) splits = MAX_SPLITS;
   if (splits > kb_total) splits = kb_total;
-  if (nb_rows > 16 && splits > 1) {
-    // with more than 16 rows the cluster's sum moves four outputs at a time: rows and pointers
-    // must allow 16-byte (32-bit output) or 8-byte accesses, else K is not split
-    const uintptr_t mask = out_dtype == DSP_F32 ? 15 : 7;
-    const bool vec_ok = N % 4 == 0 && ldc % 4 == 0 && ((uintptr_t)C & mask) == 0 &&
-                        (residual == nullptr || (ldr % 4 == 0 && ((uintptr_t)residual & mask) == 0)) &&
-                        (bias == nullptr || ((uintptr_t)bias & 7) == 0) &&
-                        (C2 == nullptr || (ldc2 % 4 == 0 && ((uintptr_t)C2 & mask) == 0 && ((uintptr_t)gain2 & 7) == 0));
-    if (!vec_ok) splits = 1;
-  }
+  // the epilogues move four outputs at a time where rows and pointers allow 16-byte (32-bit output)
+  // or 8-byte accesses; where they do not, K is not split and every thread stores single outputs
+  const uintptr_t mask = out_dtype == DSP_F32 ? 15 : 7;
+  const bool vec_ok = N % 4 == 0 && ldc % 4 == 0 && ((uintptr_t)C & mask) == 0 &&
+                      (residual == nullptr || (ldr % 4 == 0 && ((uintptr_t)residual & mask) == 0)) &&
+                      (bias == nullptr || ((uintptr_t)bias & 7) == 0) &&
+                      (C2 == nullptr || (ldc2 % 4 == 0 && ((uintptr_t)C2 & mask) == 0 && ((uintptr_t)gain2 & 7) == 0));
+  if (!vec_ok) splits = 1;
   const int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;
   Args a;
@@ -849,6 +797,7 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   a.kb_per_split = kb_per_split;
   a.epilogue = epilogue;
   a.late_trigger = (late_trigger_bytes > 0 && (long)N * K * 2 >= late_trigger_bytes) ? 1 : 0;
+  a.vec4 = vec_ok ? 1 : 0;
   a.norm_src = (const bf16*)norm_src;
   a.ld_src = ld_src;
   a.norm_eps = norm_eps;

@@ -492,6 +492,10 @@ def test_gemm_tcgen05_rows_do_not_depend_on_the_batch_and_repeat_exactly():
     (40, 384, 776, False, False, torch.bfloat16, 0),     # 32 < M <= 64 columns
     (64, 1000, 1536, True, False, torch.bfloat16, 0),
     (5, 40000, 1536, False, False, torch.float32, 0),    # more blocks than CTAs: double-buffered accumulator
+    (9, 301, 200, True, True, torch.bfloat16, 0),        # a width that rules out four outputs per store
+    (37, 1001, 200, True, False, torch.float32, 0),
+    (64, 151936, 64, False, False, torch.float32, 0),    # the output head's width, every row count's epilogue
+    (20, 4096, 1536, True, True, torch.bfloat16, 0),     # 32 blocks: K split over 4 CTAs, 5 rows each
 ])
 def test_gemm_stream_tcgen05(M, N, K, bias, resid, out_dtype, target):
     from dispec_b200.ops import gemm, library
@@ -543,6 +547,7 @@ def test_gemm_stream_tcgen05_swiglu_epilogue(M, I, K, target):
     (33, 2048, 1536, True, True, 0),      # more than 16 rows: the cluster reads its partial tiles
     (64, 1536, 1536, False, True, 0),
     (40, 40000, 96, True, False, 0),
+    (6, 302, 96, True, False, 0),         # a width that rules out four outputs per store
 ])
 def test_gemm_stream_norm_taken_apart(M, N, K, bias, resid, target):
     """The few-row product with a norm split around it: rows times the gain as the operand, the
