@@ -20,7 +20,12 @@ using namespace tc;
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 columns
-constexpr int THREADS = 192;    // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
+// warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue (a warp reaches the 32
+// lanes of tensor memory that its index modulo 4 names).  Eight epilogue warps, two per quarter taking
+// the chunks of columns in turn, left every product alone as fast as four (gate/up 92 us either way:
+// the products, not the epilogue, bound it) and made the prefill step 18 % slower.
+constexpr int EPI_WARPS = 4;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
@@ -33,6 +38,13 @@ struct Epilogue {
   long ldc;
   int M, N, K;
 };
+
+// silu(gate) * up of the bfloat16 model on the hardware's exponential and reciprocal (a few units in
+// the last place of 32 bits, far below the output's rounding): four epilogue warps, one per
+// scheduler, run 128 of these per thread and tile, and their length in instructions is their time
+__device__ __forceinline__ float silu_times(float gate, float up) {
+  return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
 
 template <typename TOut>
 __device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_t (&v)[32], int row, int col) {
@@ -49,14 +61,14 @@ __device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
           const float g = __uint_as_float(v[j * 8 + t]), u = __uint_as_float(v[16 + j * 8 + t]);
-          ob[t] = __float2bfloat16(g / (1.f + expf(-g)) * u);
+          ob[t] = __float2bfloat16(silu_times(g, u));
         }
         reinterpret_cast<uint4*>(dst)[j] = oraw;
       }
     } else {
       for (int t = 0; t < 16; ++t) {
         const float g = __uint_as_float(v[t]), u = __uint_as_float(v[16 + t]);
-        dst[t] = from_f32<TOut>(g / (1.f + expf(-g)) * u);
+        dst[t] = from_f32<TOut>(silu_times(g, u));
       }
     }
     return;
@@ -118,7 +130,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&accum_full[b], 1);
-      mbar_init(&accum_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&accum_empty[b], EPI_WARPS);  // one arrival per epilogue warp
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -215,7 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 32 * ((warp - 2) >> 2); c0 < BN; c0 += 32 * (EPI_WARPS / 4)) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
         store_row_chunk<TOut>(e, v, row, n0 + c0);
@@ -249,7 +261,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // with multicast frees the stage in both CTAs and announces the finished accumulator to both;
 // both CTAs' epilogue warps arrive on the leader's "accumulator empty" barrier.  No TMA load is
 // multicast.
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 3;   // ring slots of the pair kernel, SUB k blocks each
+constexpr int SUB = 2;       // k blocks per ring slot: one barrier round trip of the issuing thread per 128 of k
 constexpr int HALF_B_BYTES = (BN / 2) * BK * 2;
 constexpr int STAGE2_BYTES = A_BYTES + HALF_B_BYTES;  // 32 KB per CTA
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
@@ -305,7 +318,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   __shared__ __align__(8) uint64_t full_bar[STAGES2];   // used in the leader: both CTAs' loads land here
   __shared__ __align__(8) uint64_t empty_bar[STAGES2];  // one per CTA, freed by the multicast commit
   __shared__ __align__(8) uint64_t accum_full[2];       // one per CTA
-  __shared__ __align__(8) uint64_t accum_empty[2];      // used in the leader: 8 epilogue warps arrive
+  __shared__ __align__(8) uint64_t accum_empty[2];      // used in the leader: both CTAs' epilogue warps arrive
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -325,7 +338,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&accum_full[b], 1);
-      mbar_init(&accum_empty[b], 8);
+      mbar_init(&accum_empty[b], 2 * EPI_WARPS);
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -345,30 +358,35 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 0) {
     if (lane == 0) {
       // as in the one-CTA kernel: the first ring of W tiles is asked for before the wait
-      const int ahead = num_kb < STAGES2 ? num_kb : STAGES2;
-      for (int kb = 0; kb < ahead; ++kb) {
-        if (rank == 0) mbar_expect_tx(&full_bar[kb], 2 * STAGE_P);
-        tma_load_2d_pair(smem + kb * STAGE_P + A_BYTES, &map_w, &full_bar[kb], kb * BK,
-                         (pair % n_tiles) * BNP + (int)rank * (BNP / 2));
+      const int num_steps = (num_kb + SUB - 1) / SUB;  // ring slots per tile
+      const int ahead = num_steps < STAGES2 ? num_steps : STAGES2;
+      for (int st = 0; st < ahead; ++st) {
+        const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
+        if (rank == 0) mbar_expect_tx(&full_bar[st], 2 * STAGE_P * subs);
+        for (int u = 0; u < subs; ++u)
+          tma_load_2d_pair(smem + (st * SUB + u) * STAGE_P + A_BYTES, &map_w, &full_bar[st], (st * SUB + u) * BK,
+                           (pair % n_tiles) * BNP + (int)rank * (BNP / 2));
       }
       pdl_wait();
       int it = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
         const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
         const int w0 = (tile % n_tiles) * BNP + (int)rank * (BNP / 2);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int st = 0; st < num_steps; ++st, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
-          unsigned char* a_dst = smem + s * STAGE_P;
+          const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
+          unsigned char* slot = smem + s * SUB * STAGE_P;
           if (it >= ahead) {
             if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
               failed = 1;
               break;
             }
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P);
-            tma_load_2d_pair(a_dst + A_BYTES, &map_w, &full_bar[s], kb * BK, w0);
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P * subs);
+            for (int u = 0; u < subs; ++u)
+              tma_load_2d_pair(slot + u * STAGE_P + A_BYTES, &map_w, &full_bar[s], (st * SUB + u) * BK, w0);
           }
-          tma_load_2d_pair(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+          for (int u = 0; u < subs; ++u) tma_load_2d_pair(slot + u * STAGE_P, &map_a, &full_bar[s], (st * SUB + u) * BK, m0);
         }
       }
     }
@@ -384,7 +402,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int num_steps = (num_kb + SUB - 1) / SUB;
+        for (int st = 0; st < num_steps; ++st, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
           if (!mbar_wait(&full_bar[s], phase)) {
@@ -392,11 +411,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_P);
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
+          for (int u = 0; u < subs; ++u) {
+            const uint32_t a_addr = smem_u32(smem + (s * SUB + u) * STAGE_P);
+            const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (st | u | k) != 0);
+          }
           umma_commit_pair(&empty_bar[s]);
         }
         if (failed) break;
@@ -416,7 +438,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      for (int c0 = 0; c0 < BNP; c0 += 32) {
+      for (int c0 = 32 * ((warp - 2) >> 2); c0 < BNP; c0 += 32 * (EPI_WARPS / 4)) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 256 + c0), v);
         store_row_chunk<TOut>(e, v, row, n0 + c0);
@@ -487,7 +509,7 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
     };
     const int bnp = cost(192) < cost(256) ? 192 : 256;
     DSP_REQUIRE(make_map(&map_w, W, N, K, K, bnp / 2), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
-    const int smem2 = STAGES2 * (A_BYTES + (bnp / 2) * BK * 2) + 1024;
+    const int smem2 = STAGES2 * SUB * (A_BYTES + (bnp / 2) * BK * 2) + 1024;
     const long tiles2 = (long)((N + bnp - 1) / bnp) * m_tiles2;
     const long pairs = tiles2 < pairs_avail ? tiles2 : pairs_avail;
     dim3 grid2((unsigned)(2 * pairs));
