@@ -365,13 +365,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (rank == 0) mbar_expect_tx(&full_bar[st], 2 * STAGE_P * subs);
         for (int u = 0; u < subs; ++u)
           tma_load_2d_pair(smem + (st * SUB + u) * STAGE_P + A_BYTES, &map_w, &full_bar[st], (st * SUB + u) * BK,
-                           (pair % n_tiles) * BNP + (int)rank * (BNP / 2));
+                           (pair / m_tiles) * BNP + (int)rank * (BNP / 2));
       }
       pdl_wait();
       int it = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
-        const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM;
-        const int w0 = (tile % n_tiles) * BNP + (int)rank * (BNP / 2);
+        const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
+        const int w0 = (tile / m_tiles) * BNP + (int)rank * (BNP / 2);
         for (int st = 0; st < num_steps; ++st, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
@@ -431,7 +431,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     int local = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
       const int buf = local & 1;
-      const int m0 = (tile / n_tiles) * 2 * BM + (int)rank * BM, n0 = (tile % n_tiles) * BNP;
+      const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * BNP;
       if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[buf], (local >> 1) & 1))) {
         failed = 1;
         break;
