@@ -147,29 +147,27 @@ def test_attention_part_in_two_portions(dtype, window):
     torch.testing.assert_close(got, ref, atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_pre_norm_block_alone(dtype):
-    """The arrangement of a layer (two norms, mixer, feed-forward, residual sums) against the
-    plain layer function, a sequence in two portions."""
-    from dispec_b200.cache import CacheGroupSpec
-    from dispec_b200.engine import SeqEntry
-    from dispec_b200.models.model import CachePlacement
+BLOCK_SIZES = dict(H=4, KVH=2, D=32, hidden=96, inter=208, eps=1e-5, theta=30000.0)
+
+
+def _make_block(dtype, seed, prefix, weights):
+    """A pre-norm block of the package's own parts with random weights (also put into ``weights``
+    under the plain implementation's names)."""
     from dispec_b200.parts.attention import GQAAttention
     from dispec_b200.parts.block import PreNormBlock
     from dispec_b200.parts.norms import RMSNorm
     from dispec_b200.parts.rotary import RotaryEncoding
     from dispec_b200.parts.swiglu import SwiGLUFeedForward
-    H, KVH, D, hidden, inter, eps, theta = 4, 2, 32, 96, 208, 1e-5, 30000.0
-    pe = RotaryEncoding(D, theta)
+    z = BLOCK_SIZES
+    pe = RotaryEncoding(z["D"], z["theta"])
     pe.prepare(DEV)
-    parts = dict(n1=RMSNorm(hidden, eps), n2=RMSNorm(hidden, eps),
-                 mixer=GQAAttention(hidden, H, KVH, D, True, pe), ffn=SwiGLUFeedForward(hidden, inter))
+    parts = dict(n1=RMSNorm(z["hidden"], z["eps"]), n2=RMSNorm(z["hidden"], z["eps"]),
+                 mixer=GQAAttention(z["hidden"], z["H"], z["KVH"], z["D"], True, pe),
+                 ffn=SwiGLUFeedForward(z["hidden"], z["inter"]))
     names = {"n1": {"weight": "input_layernorm.weight"}, "n2": {"weight": "post_attention_layernorm.weight"},
              "mixer": {f"{n}_proj.{k}": f"self_attn.{n}_proj.{k}" for n in "qkv" for k in ("weight", "bias")}
              | {"o_proj.weight": "self_attn.o_proj.weight"},
              "ffn": {f"{n}_proj.weight": f"mlp.{n}_proj.weight" for n in ("gate", "up", "down")}}
-    weights = {}
-    seed = 200
     for key, part in parts.items():
         local = {}
         for n, spec in part.tensor_specs().items():
@@ -178,13 +176,25 @@ def test_pre_norm_block_alone(dtype):
             if spec.init == "one_plus_normal":
                 t = t + 1.0
             t = t.to(dtype)
-            weights["L." + names[key][n]] = t.float()
+            weights[prefix + names[key][n]] = t.float()
             local[n] = t.to(DEV)
         part.load(local)
-    block = PreNormBlock(parts["n1"], parts["mixer"], parts["n2"], parts["ffn"])
+    return PreNormBlock(parts["n1"], parts["mixer"], parts["n2"], parts["ffn"]), parts
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pre_norm_block_alone(dtype):
+    """The arrangement of a layer (two norms, mixer, feed-forward, residual sums) against the
+    plain layer function, a sequence in two portions."""
+    from dispec_b200.cache import CacheGroupSpec
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.models.model import CachePlacement
+    z = BLOCK_SIZES
+    weights = {}
+    block, parts = _make_block(dtype, 200, "L.", weights)
     T = 23
-    x = rnd((T, hidden), 300).to(dtype)
-    groups = [CacheGroupSpec.key_value(KVH, D, 0, 1)]
+    x = rnd((T, z["hidden"]), 300).to(dtype)
+    groups = [CacheGroupSpec.key_value(z["KVH"], z["D"], 0, 1)]
     out, harness, pos = [], None, 0
     for n in (9, 14):
         e = [SeqEntry("s", list(range(n)), pos, [])]
@@ -194,11 +204,47 @@ def test_pre_norm_block_alone(dtype):
         commit(harness, e)
         pos += n
     got = torch.cat(out).float().cpu()
-    c = dict(eps=eps, heads=H, kv_heads=KVH, head_dim=D)
-    cos, sin = plain.rope_tables(torch.arange(T), D, theta)
+    c = dict(eps=z["eps"], heads=z["H"], kv_heads=z["KVH"], head_dim=z["D"])
+    cos, sin = plain.rope_tables(torch.arange(T), z["D"], z["theta"])
     ref = plain.decoder_layer(x.float(), weights, "L.", c, cos, sin, 0)
     tol = 3e-5 if dtype == torch.float32 else 6e-2
     torch.testing.assert_close(got, ref, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype,rows", [(torch.bfloat16, 11), (torch.bfloat16, 70), (torch.float32, 11)])
+def test_pre_norm_blocks_hand_their_norms_to_the_products(dtype, rows):
+    """Two blocks in a row, the first told which norm reads its result: it hands that norm on,
+    still to be applied; with few rows in bfloat16 the scaled copy is there and the norms run
+    inside the products, otherwise the second block runs the norm kernel.  Either way the result
+    is the plain two layers."""
+    from dispec_b200.cache import CacheGroupSpec
+    from dispec_b200.engine import SeqEntry
+    from dispec_b200.models.model import CachePlacement
+    from dispec_b200.ops.gemm import NORM_SPLIT_MAX_ROWS, NormedRows
+    z = BLOCK_SIZES
+    weights = {}
+    first, parts1 = _make_block(dtype, 400, "A.", weights)
+    second, parts2 = _make_block(dtype, 500, "B.", weights)
+    x = rnd((rows, z["hidden"]), 600).to(dtype)
+    groups = [CacheGroupSpec.key_value(z["KVH"], z["D"], 0, 2)]
+    e = [SeqEntry("s", list(range(rows)), 0, [])]
+    ctx, harness = make_ctx(e, groups, 8, 2 * (rows // 8 + 2), dtype, _tile_sizes(parts1["mixer"]))
+    offer = second.first_norm_after_product()
+    assert offer is not None and offer[0] is parts2["n1"].weight
+    h, pending = first.forward(ctx, x.to(DEV).clone(), None, ctx.cache_view(CachePlacement(0, 0), True), None,
+                               then_norm=offer)
+    assert isinstance(pending, NormedRows) and pending.source is h and pending.weight is parts2["n1"].weight
+    if dtype == torch.bfloat16 and rows <= NORM_SPLIT_MAX_ROWS:
+        assert torch.equal(pending.scaled, (h.float() * parts2["n1"].weight.float()).to(dtype))
+    else:
+        assert pending.scaled is None
+    out, last = second.forward(ctx, h, pending, ctx.cache_view(CachePlacement(0, 1), True), None)
+    assert last is None
+    c = dict(eps=z["eps"], heads=z["H"], kv_heads=z["KVH"], head_dim=z["D"])
+    cos, sin = plain.rope_tables(torch.arange(rows), z["D"], z["theta"])
+    ref = plain.decoder_layer(plain.decoder_layer(x.float(), weights, "A.", c, cos, sin, 0), weights, "B.", c, cos, sin, 0)
+    tol = 6e-5 if dtype == torch.float32 else 1e-1
+    torch.testing.assert_close(out.float().cpu(), ref, atol=tol, rtol=tol)
 
 
 # ------------------------------------------------------------------- toy parts and models
