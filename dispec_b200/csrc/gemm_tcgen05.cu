@@ -37,6 +37,7 @@ struct Epilogue {
   void* C;
   long ldc;
   int M, N, K;
+  int k_boxes;  // the tensor maps are the three-dimensional ones: one request brings SUB k blocks (pair kernel)
 };
 
 // silu(gate) * up of the bfloat16 model on the hardware's exponential and reciprocal (a few units in
@@ -282,6 +283,13 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint64_t* leader_bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(c0), "r"(c1),
+        "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
@@ -326,7 +334,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const int num_kb = (e.K + BK - 1) / BK;
-  constexpr int STAGE_P = A_BYTES + (BNP / 2) * BK * 2;  // A tile and this CTA's half of the W tile
+  constexpr int B_HALF = (BNP / 2) * BK * 2;   // this CTA's half of the W tile, one k block
+  constexpr int STAGE_P = A_BYTES + B_HALF;    // one k block of both operands
   const int n_tiles = (e.N + BNP - 1) / BNP, m_tiles = (e.M + 2 * BM - 1) / (2 * BM);
   const int num_tiles = n_tiles * m_tiles;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -357,15 +366,36 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (warp == 0) {
     if (lane == 0) {
-      // as in the one-CTA kernel: the first ring of W tiles is asked for before the wait
+      // as in the one-CTA kernel: the first ring of W tiles is asked for before the wait.  A ring
+      // slot holds SUB k blocks of A, then SUB k blocks of this CTA's half of W; with the
+      // three-dimensional maps one request brings all SUB blocks of an operand (and counts the
+      // bytes of all SUB, zero-filled beyond K), else one request per k block
       const int num_steps = (num_kb + SUB - 1) / SUB;  // ring slots per tile
       const int ahead = num_steps < STAGES2 ? num_steps : STAGES2;
-      for (int st = 0; st < ahead; ++st) {
+      auto slot_bytes = [&](int st) {
         const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
-        if (rank == 0) mbar_expect_tx(&full_bar[st], 2 * STAGE_P * subs);
-        for (int u = 0; u < subs; ++u)
-          tma_load_2d_pair(smem + (st * SUB + u) * STAGE_P + A_BYTES, &map_w, &full_bar[st], (st * SUB + u) * BK,
-                           (pair / m_tiles) * BNP + (int)rank * (BNP / 2));
+        return 2 * STAGE_P * (e.k_boxes ? SUB : subs);
+      };
+      auto load_w = [&](unsigned char* slot, uint64_t* bar, int st, int w0) {
+        unsigned char* dst = slot + SUB * A_BYTES;
+        if (e.k_boxes) {
+          tma_load_3d_pair(dst, &map_w, bar, 0, w0, st * SUB);
+        } else {
+          for (int u = 0; u < SUB && st * SUB + u < num_kb; ++u)
+            tma_load_2d_pair(dst + u * B_HALF, &map_w, bar, (st * SUB + u) * BK, w0);
+        }
+      };
+      auto load_a = [&](unsigned char* slot, uint64_t* bar, int st, int m0) {
+        if (e.k_boxes) {
+          tma_load_3d_pair(slot, &map_a, bar, 0, m0, st * SUB);
+        } else {
+          for (int u = 0; u < SUB && st * SUB + u < num_kb; ++u)
+            tma_load_2d_pair(slot + u * A_BYTES, &map_a, bar, (st * SUB + u) * BK, m0);
+        }
+      };
+      for (int st = 0; st < ahead; ++st) {
+        if (rank == 0) mbar_expect_tx(&full_bar[st], slot_bytes(st));
+        load_w(smem + st * SUB * STAGE_P, &full_bar[st], st, ((pair / m_tiles) % n_tiles) * BNP + (int)rank * (BNP / 2));
       }
       pdl_wait();
       int it = 0;
@@ -375,18 +405,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int st = 0; st < num_steps; ++st, ++it) {
           const int s = it % STAGES2;
           const uint32_t phase = (it / STAGES2) & 1;
-          const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
           unsigned char* slot = smem + s * SUB * STAGE_P;
           if (it >= ahead) {
             if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
               failed = 1;
               break;
             }
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_P * subs);
-            for (int u = 0; u < subs; ++u)
-              tma_load_2d_pair(slot + u * STAGE_P + A_BYTES, &map_w, &full_bar[s], (st * SUB + u) * BK, w0);
+            if (rank == 0) mbar_expect_tx(&full_bar[s], slot_bytes(st));
+            load_w(slot, &full_bar[s], st, w0);
           }
-          for (int u = 0; u < subs; ++u) tma_load_2d_pair(slot + u * STAGE_P, &map_a, &full_bar[s], (st * SUB + u) * BK, m0);
+          load_a(slot, &full_bar[s], st, m0);
         }
       }
     }
@@ -413,8 +441,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           tc_fence_after();
           const int subs = num_kb - st * SUB < SUB ? num_kb - st * SUB : SUB;
           for (int u = 0; u < subs; ++u) {
-            const uint32_t a_addr = smem_u32(smem + (s * SUB + u) * STAGE_P);
-            const uint32_t b_addr = a_addr + A_BYTES;
+            const uint32_t a_addr = smem_u32(smem + s * SUB * STAGE_P + u * A_BYTES);
+            const uint32_t b_addr = smem_u32(smem + s * SUB * STAGE_P + SUB * A_BYTES + u * B_HALF);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
               umma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (st | u | k) != 0);
@@ -491,6 +519,7 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
   e.M = M;
   e.N = N;
   e.K = K;
+  e.k_boxes = 0;
   const int smem = STAGES * STAGE_BYTES + 1024;
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -508,7 +537,11 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
       return ((tiles2 + pairs_avail - 1) / pairs_avail) * bn;
     };
     const int bnp = cost(192) < cost(256) ? 192 : 256;
-    DSP_REQUIRE(make_map(&map_w, W, N, K, K, bnp / 2), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+    e.k_boxes = (make_map_k_blocks(&map_a, A, M, K, lda, BM, SUB) && make_map_k_blocks(&map_w, W, N, K, K, bnp / 2, SUB)) ? 1 : 0;
+    if (!e.k_boxes) {
+      DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
+      DSP_REQUIRE(make_map(&map_w, W, N, K, K, bnp / 2), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+    }
     const int smem2 = STAGES2 * SUB * (A_BYTES + (bnp / 2) * BK * 2) + 1024;
     const long tiles2 = (long)((N + bnp - 1) / bnp) * m_tiles2;
     const long pairs = tiles2 < pairs_avail ? tiles2 : pairs_avail;

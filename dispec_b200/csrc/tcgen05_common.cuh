@@ -194,4 +194,20 @@ inline bool make_map(CUtensorMap* map, const void* base, long rows, long K, long
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// The same matrix seen as (64 of k, rows, K / 64 blocks of k): one box of (64, box_rows, k_blocks)
+// brings several k blocks of a row tile with a single request, laid out as consecutive tiles of
+// [box_rows][64] (a request costs the TMA unit about 200 cycles whatever its size: measured 41 bytes
+// a clock and SM with boxes of 16 KB, 73 with boxes of 32 KB).  K must be a multiple of 64 (a
+// partial last block would read on into the next row).
+inline bool make_map_k_blocks(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows, int k_blocks) {
+  EncodeTiled fn = encode_fn();
+  if (fn == nullptr || K % 64 != 0) return false;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)k_blocks};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 }  // namespace tc
