@@ -345,6 +345,32 @@ def mma_issue_rate() -> dict:
     return {"only": "mma-rate", "shape_of_one_product": "128 x N x 16, bfloat16, operands in shared memory", "table": table}
 
 
+def tma_ingest_rate() -> dict:
+    """Bytes a clock that one SM takes in from the L2 by TMA, by the size of a request: boxes of
+    64 of k x 128 rows x 1, 2 or 3 blocks of k (16, 32, 48 KB), one to four requests per ring slot."""
+    import ctypes
+    import torch
+    from dispec_b200.ops import library as L
+    from dispec_b200.ops import tuning
+    ctas = tuning.sm_count(torch.device("cuda:0"))
+    rows, iters = 20480, 2000
+    matrix = torch.zeros((rows, 1536), dtype=torch.bfloat16, device="cuda:0")
+    cycles = torch.zeros(ctas, dtype=torch.int64, device="cuda:0")
+    ok = torch.ones(1, dtype=torch.int32, device="cuda:0")
+    table = {}
+    for stages, boxes, k_blocks in ((6, 1, 1), (6, 2, 1), (3, 4, 1), (3, 1, 2), (3, 2, 2), (2, 2, 3)):
+        for _ in range(2):  # the second run is warm
+            L.check(L.core().dsp_selftest_tma_rate(L.ptr(matrix), rows, stages, boxes, k_blocks, ctas, iters,
+                                                   L.ptr(cycles), L.ptr(ok), L.stream_handle()))
+        torch.cuda.synchronize()
+        per_slot = float(cycles.double().mean()) / iters
+        table[f"{boxes}_requests_of_{16 * k_blocks}KB_ring_of_{stages}"] = {
+            "cycles_per_slot": round(per_slot), "bytes_per_clock_and_sm": round(boxes * k_blocks * 16384 / per_slot, 1),
+            "ok": bool(int(ok.item()))}
+    return {"only": "tma-rate", "ctas": ctas, "source": "a 20,480 x 1,536 bfloat16 matrix in the L2, row tiles in turn",
+            "table": table}
+
+
 def decode_timeline(args) -> dict:
     """Where the time of a decode step's kernels goes: the weight-streaming products and the
     single-token attention of a captured step (few layers of the recorded shape) record the global
@@ -432,6 +458,8 @@ def run_ours(args) -> dict:
 
     if args.only == "mma-rate":
         return mma_issue_rate()
+    if args.only == "tma-rate":
+        return tma_ingest_rate()
     if args.only == "timeline":
         return decode_timeline(args)
     cfg_dict = dict(BENCH_CONFIG)
@@ -603,10 +631,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate"], default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
-                         "tcgen05.mma for one to four issuing threads")
+                         "tcgen05.mma for one to four issuing threads; tma-rate: bytes a clock an SM takes in from "
+                         "the L2 by TMA, by the size of a request")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

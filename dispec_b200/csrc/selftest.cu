@@ -101,3 +101,83 @@ extern "C" int dsp_selftest_mma_issue_rate(int n, int issuers, int iters, long l
   DSP_CHECK_LAUNCH("dsp_selftest_mma_issue_rate");
   return 0;
 }
+
+// ---- how fast one SM takes tiles in by TMA --------------------------------------------------------
+// A measurement, kept with the library because the many-row product's ring is laid out by its
+// result: every CTA (one per SM) runs a ring of `stages` slots; one thread requests `boxes` boxes
+// per slot from a matrix of `rows` x 1536 bfloat16 that lies in the L2 (each box 64 of k by 128
+// rows by `k_blocks` blocks of k, through the three-dimensional map of make_map_k_blocks), another
+// waits for them and frees the slot; nothing is computed.  out[0]: cycles per slot (mean over the
+// CTAs), out[1]: 1 if no wait ran out.
+namespace {
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(tc::smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+constexpr int TMA_RATE_MAX_STAGES = 8, TMA_RATE_K = 1536;
+__global__ void __launch_bounds__(64, 1) tma_rate_kernel(const __grid_constant__ CUtensorMap map, int rows, int stages,
+                                                          int boxes, int k_blocks, int iters, long long* cycles, int* ok) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[TMA_RATE_MAX_STAGES], empty_bar[TMA_RATE_MAX_STAGES];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int box_bytes = 128 * 128 * k_blocks;
+  const int steps_per_row_tile = TMA_RATE_K / 64 / k_blocks, row_tiles = rows / 128;
+  const long long t0 = clock64();
+  if (threadIdx.x == 0) {
+    int s = 0, phase = 0;
+    for (int it = 0; it < iters; ++it) {
+      if (it >= stages && !tc::mbar_wait(&empty_bar[s], (uint32_t)(phase ^ 1))) {
+        *ok = 0;
+        break;
+      }
+      tc::mbar_expect_tx(&full_bar[s], (uint32_t)(boxes * box_bytes));
+      for (int b = 0; b < boxes; ++b) {
+        const int tile = ((int)blockIdx.x * 7 + it / steps_per_row_tile * 3 + b * 5) % row_tiles;
+        tma_load_3d(smem + (s * boxes + b) * box_bytes, &map, &full_bar[s], 0, tile * 128, (it % steps_per_row_tile) * k_blocks);
+      }
+      if (++s == stages) s = 0, phase ^= 1;
+    }
+  } else if (threadIdx.x == 32) {
+    int s = 0, phase = 0;
+    for (int it = 0; it < iters; ++it) {
+      if (!tc::mbar_wait(&full_bar[s], (uint32_t)phase)) {
+        *ok = 0;
+        break;
+      }
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(&empty_bar[s])) : "memory");
+      if (++s == stages) s = 0, phase ^= 1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) cycles[blockIdx.x] = clock64() - t0;
+}
+}  // namespace
+
+// matrix: rows x 1536 bfloat16 on the device (rows a multiple of 128); cycles: one value per CTA;
+// ok: set to 0 if a wait ran out (the caller sets it to 1 first)
+extern "C" int dsp_selftest_tma_rate(const void* matrix, int rows, int stages, int boxes, int k_blocks, int ctas, int iters,
+                                     long long* cycles, int* ok, cudaStream_t stream) {
+  DSP_REQUIRE(matrix != nullptr && cycles != nullptr && ok != nullptr && rows >= 128 && rows % 128 == 0,
+              "dsp_selftest_tma_rate: a matrix of a multiple of 128 rows and result buffers are needed (rows=%d)", rows);
+  DSP_REQUIRE(stages >= 1 && stages <= TMA_RATE_MAX_STAGES && boxes >= 1 && boxes <= 8 && k_blocks >= 1 && k_blocks <= 8 &&
+                  (TMA_RATE_K / 64) % k_blocks == 0 && ctas >= 1 && ctas <= 1024 && iters >= 1,
+              "dsp_selftest_tma_rate: stages=%d, boxes=%d or k_blocks=%d out of range", stages, boxes, k_blocks);
+  const size_t smem = (size_t)stages * boxes * 128 * 128 * k_blocks + 1024;
+  DSP_REQUIRE(smem <= 227 * 1024, "dsp_selftest_tma_rate: %zu bytes of shared memory asked for", smem);
+  CUtensorMap map;
+  DSP_REQUIRE(tc::make_map_k_blocks(&map, matrix, rows, TMA_RATE_K, TMA_RATE_K, 128, k_blocks),
+              "dsp_selftest_tma_rate: cannot encode the tensor map");
+  DSP_CUDA(cudaFuncSetAttribute(tma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  tma_rate_kernel<<<ctas, 64, smem, stream>>>(map, rows, stages, boxes, k_blocks, iters, cycles, ok);
+  DSP_CHECK_LAUNCH("dsp_selftest_tma_rate");
+  return 0;
+}
