@@ -948,3 +948,27 @@ def test_random_model_filled_on_the_device_equals_the_written_folder(tmp_path, d
     a = open(tmp_path / "model.safetensors", "rb").read()
     b = open(tmp_path / "dev" / "model.safetensors", "rb").read()
     assert a == b
+
+
+def test_measurement_entries_run_and_refuse_bad_arguments():
+    """The two measurement kernels that `bench.py --only mma-rate | tma-rate` call: they run with
+    bounded waits, report that no wait ran out, and refuse arguments outside their ranges."""
+    import ctypes
+    from dispec_b200.ops import library as L
+    core = L.core()
+    out = torch.zeros(3, dtype=torch.int64, device=dev())
+    L.check(core.dsp_selftest_mma_issue_rate(16, 2, 50, ctypes.c_void_p(out.data_ptr()), L.stream_handle()))
+    issue, done, ok = out.tolist()
+    assert ok == 1 and issue > 0 and done >= issue
+    assert core.dsp_selftest_mma_issue_rate(24, 1, 50, ctypes.c_void_p(out.data_ptr()), L.stream_handle()) != 0
+    matrix = torch.zeros((1280, 1536), dtype=torch.bfloat16, device=dev())
+    cycles = torch.zeros(4, dtype=torch.int64, device=dev())
+    flag = torch.ones(1, dtype=torch.int32, device=dev())
+    for stages, boxes, k_blocks in ((3, 2, 2), (6, 1, 1)):
+        L.check(core.dsp_selftest_tma_rate(L.ptr(matrix), 1280, stages, boxes, k_blocks, 4, 50, L.ptr(cycles), L.ptr(flag),
+                                           L.stream_handle()))
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 1 and int(cycles.min()) > 0
+    assert core.dsp_selftest_tma_rate(L.ptr(matrix), 1280, 3, 2, 5, 4, 50, L.ptr(cycles), L.ptr(flag), L.stream_handle()) != 0
+    assert core.dsp_selftest_tma_rate(L.ptr(matrix), 1000, 3, 2, 2, 4, 50, L.ptr(cycles), L.ptr(flag), L.stream_handle()) != 0
+    assert L.device_error() == 0
