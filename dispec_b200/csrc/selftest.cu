@@ -110,11 +110,6 @@ extern "C" int dsp_selftest_mma_issue_rate(int n, int issuers, int iters, long l
 // waits for them and frees the slot; nothing is computed.  out[0]: cycles per slot (mean over the
 // CTAs), out[1]: 1 if no wait ran out.
 namespace {
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(tc::smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
 constexpr int TMA_RATE_MAX_STAGES = 8, TMA_RATE_K = 1536;
 __global__ void __launch_bounds__(64, 1) tma_rate_kernel(const __grid_constant__ CUtensorMap map, int rows, int stages,
                                                           int boxes, int k_blocks, int iters, long long* cycles, int* ok) {
@@ -142,7 +137,7 @@ __global__ void __launch_bounds__(64, 1) tma_rate_kernel(const __grid_constant__
       tc::mbar_expect_tx(&full_bar[s], (uint32_t)(boxes * box_bytes));
       for (int b = 0; b < boxes; ++b) {
         const int tile = ((int)blockIdx.x * 7 + it / steps_per_row_tile * 3 + b * 5) % row_tiles;
-        tma_load_3d(smem + (s * boxes + b) * box_bytes, &map, &full_bar[s], 0, tile * 128, (it % steps_per_row_tile) * k_blocks);
+        tc::tma_load_3d(smem + (s * boxes + b) * box_bytes, &map, &full_bar[s], 0, tile * 128, (it % steps_per_row_tile) * k_blocks);
       }
       if (++s == stages) s = 0, phase ^= 1;
     }
