@@ -256,7 +256,8 @@ def decode_e2e(model, prompts, steps, warmup, num_blocks, max_model_len=None):
                                       max_batch_tokens=8192, max_num_seqs=max(len(prompts), 8),
                                       max_model_len=max_model_len)
     for p in prompts:
-        engine.add_request(p, warmup + steps + 8, SamplingParams(0.0))
+        # (room for the steps in which the other prompts are still being read)
+        engine.add_request(p, warmup + steps + 8 + len(prompts), SamplingParams(0.0))
     while engine.waiting or engine.prefilling:
         engine.step()
     for _ in range(warmup):

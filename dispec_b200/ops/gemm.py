@@ -179,6 +179,11 @@ def linear(x, w: torch.Tensor, bias: torch.Tensor | None = None,
     if isinstance(x, NormedRows):
         if backend in (None, "stream") and x.splittable(w):
             norm, x, backend = x, x.scaled, "stream"
+        elif (backend is None and x.scaled is not None and x.scaled.dtype == torch.bfloat16
+              and x.source.shape[0] > STREAM_MAX_ROWS and x.source.stride(1) == 1 and x.source.stride(0) % 8 == 0
+              and x.source.data_ptr() % 16 == 0 and stream_supported(STREAM_MAX_ROWS, x.source.shape[1], x.scaled, w)
+              and tuning.rows_in_chunks_is_faster(x.source.shape[0], w.shape[0], x.source.shape[1], w.device)):
+            norm, x, backend = x, x.scaled, "stream_chunks"
         else:
             x = x.materialize()
     if not (x.is_cuda and w.is_cuda):
@@ -210,12 +215,27 @@ def linear(x, w: torch.Tensor, bias: torch.Tensor | None = None,
     if backend is None:
         if stream_supported(M, K, x, w):
             backend = "stream"
+        elif (M > STREAM_MAX_ROWS and stream_supported(STREAM_MAX_ROWS, K, x, w)
+              and tuning.rows_in_chunks_is_faster(M, N, K, x.device)):
+            backend = "stream_chunks"
         elif M > STREAM_MAX_ROWS and tcgen05_supported(x, w):
             backend = "tcgen05"
         elif M > STREAM_MAX_ROWS and out_dtype == torch.bfloat16:
             backend = "library"
         else:
             backend = "simt"
+    if backend == "stream_chunks":
+        # a narrow product with a long K at 65 to a few hundred rows: the few-row kernel per 64 rows
+        # (see tuning.rows_in_chunks_is_faster)
+        scaled = None
+        if then_norm is not None and out_dtype == torch.bfloat16 and then_norm[0].dtype == torch.bfloat16:
+            scaled = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        for r in range(0, M, STREAM_MAX_ROWS):
+            rows = slice(r, min(M, r + STREAM_MAX_ROWS))
+            part = None if norm is None else NormedRows(norm.source[rows], norm.weight, norm.eps, norm.scaled[rows])
+            _stream(x[rows], w, bias, None if residual is None else residual[rows], out[rows], norm=part,
+                    scaled_out=(then_norm[0], scaled[rows]) if scaled is not None else None)
+        return result(scaled)
     if backend == "stream":
         scaled = None
         if (then_norm is not None and M <= NORM_SPLIT_MAX_ROWS and out_dtype == torch.bfloat16

@@ -950,6 +950,40 @@ def test_random_model_filled_on_the_device_equals_the_written_folder(tmp_path, d
     assert a == b
 
 
+@pytest.mark.parametrize("M", [65, 130, 200])
+def test_linear_runs_narrow_long_products_in_chunks_of_rows(M):
+    """65 to a few hundred rows, a narrow product with a long K (the down projection's shape): the
+    few-row kernel per 64 rows instead of eight tiles of the many-row kernel; with a norm taken
+    apart on both sides it gives what the single launches give."""
+    from dispec_b200 import ops
+    from dispec_b200.ops import gemm, library, tuning
+    N, K, eps = 1536, 8960, 1e-6
+    assert tuning.rows_in_chunks_is_faster(M, N, K, torch.device(dev()))
+    assert not tuning.rows_in_chunks_is_faster(M, 17920, 1536, torch.device(dev()))
+    x = rnd((M, K), torch.bfloat16, 201)
+    w = rnd((N, K), torch.bfloat16, 202, 0.05)
+    b = rnd((N,), torch.bfloat16, 203)
+    r = rnd((M, N), torch.bfloat16, 204)
+    gain = (1.0 + rnd((N,), torch.float32, 205, 0.3)).bfloat16()
+    out, nxt = gemm.linear(x, w, b, residual=r, then_norm=(gain, eps))
+    assert library.device_error() == 0
+    ref = x.double() @ w.double().T + b.double() + r.double()
+    torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.equal(nxt.scaled, (out.float() * gain.float()).bfloat16())
+    # the norm handed on, into another narrow product
+    w2 = rnd((1024, N), torch.bfloat16, 207, 0.1)
+    got = gemm.linear(nxt, w2)
+    hd = out.double()
+    rstd = torch.rsqrt((hd * hd).mean(dim=1, keepdim=True) + eps)
+    own = nxt.scaled.double() @ w2.double().T * rstd
+    two = gemm.linear(ops.rms_norm(out, gain, eps), w2)
+    torch.testing.assert_close(two.double(), (hd * rstd * gain.double()) @ w2.double().T, atol=6e-2, rtol=3e-2)
+    if tuning.rows_in_chunks_is_faster(M, 1024, N, torch.device(dev())):
+        torch.testing.assert_close(got.double(), own, atol=3e-2, rtol=2e-2)
+    else:  # the many-row kernel took it: the norm kernel ran first
+        assert torch.equal(got, two)
+
+
 def test_measurement_entries_run_and_refuse_bad_arguments():
     """The two measurement kernels that `bench.py --only mma-rate | tma-rate` call: they run with
     bounded waits, report that no wait ran out, and refuse arguments outside their ranges."""
