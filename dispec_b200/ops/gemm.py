@@ -3,7 +3,9 @@
 float32: the FMA kernel (``dsp_gemm_simt``), always; no tensor cores, no reduced-precision
 mode, one FMA chain per output so that a row does not depend on its batch.
 bfloat16: the weight-streaming tcgen05 kernel for up to 64 rows (decoding and the rows whose
-logits are wanted); above that the persistent tcgen05/TMA kernel of this package.  Operands
+logits are wanted); above that the persistent tcgen05/TMA kernel of this package, except that a
+narrow product with a long K at 65 to a few hundred rows runs the weight-streaming kernel once per
+64 rows where ``tuning.rows_in_chunks_is_faster`` says so (the many-row kernel does not split K).  Operands
 those kernels cannot take (a width that is no multiple of 8) go to the FMA kernel when there
 are at most 64 rows or 32-bit logits are wanted, and otherwise to the library matrix product
 (cuBLAS through torch.mm), which is where the reference engine itself calls a library
