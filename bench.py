@@ -15,7 +15,7 @@ goes to standard output:
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   bytes a decode step must read (every weight once + the live requests' cache)
              divided by its time, against the measured copy bandwidth
-  points     decode at batch 1 and 64 (with the fraction of the copy bandwidth), one request at
+  points     decode at batch 1, 64 and 128 (with the fraction of the copy bandwidth), one request at
              32,768 tokens of context, and, for the Qwen2.5-7B and 14B layer sizes with every layer
              of each, decode at batch 1 / 8 / 64 and the 2,048-token prefill with their fractions
 
@@ -522,7 +522,7 @@ def run_ours(args) -> dict:
     torch.cuda.empty_cache()
     e2e_value, e2e_ms, h2d, d2h = decode_e2e(model, prompts, args.steps, args.warmup, BATCH * pages_per_req + 64, over)
     points = {}
-    for b in (1, 64):
+    for b in (1, 64, 128):  # 128: beyond the rows of the few-row product (its chunks and the many-row product)
         r = runner_for(b)
         steps = max(20, min(args.steps, 100))
         bms, _, bctx = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, max(3, args.warmup // 2))
