@@ -182,16 +182,36 @@ def _make_block(dtype, seed, prefix, weights):
     return PreNormBlock(parts["n1"], parts["mixer"], parts["n2"], parts["ffn"]), parts
 
 
+class NormKernelOnly:
+    """A norm that offers the two methods every norm has and nothing else: the block then runs it
+    as a kernel of its own and lets the products add the residual stream."""
+
+    def __init__(self, norm):
+        self._norm = norm
+
+    def forward(self, ctx, x, rows=None):
+        return self._norm.forward(ctx, x, rows=rows)
+
+    def forward_add(self, ctx, residual, delta, rows=None):
+        return self._norm.forward_add(ctx, residual, delta, rows=rows)
+
+
+@pytest.mark.parametrize("norms_in_products", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_pre_norm_block_alone(dtype):
+def test_pre_norm_block_alone(dtype, norms_in_products):
     """The arrangement of a layer (two norms, mixer, feed-forward, residual sums) against the
-    plain layer function, a sequence in two portions."""
+    plain layer function, a sequence in two portions; with norms that can be handed to the
+    products after them and with norms that cannot."""
     from dispec_b200.cache import CacheGroupSpec
     from dispec_b200.engine import SeqEntry
     from dispec_b200.models.model import CachePlacement
+    from dispec_b200.parts.block import PreNormBlock
     z = BLOCK_SIZES
     weights = {}
     block, parts = _make_block(dtype, 200, "L.", weights)
+    if not norms_in_products:
+        block = PreNormBlock(NormKernelOnly(parts["n1"]), parts["mixer"], NormKernelOnly(parts["n2"]), parts["ffn"])
+        assert block.first_norm_after_product() is None
     T = 23
     x = rnd((T, z["hidden"]), 300).to(dtype)
     groups = [CacheGroupSpec.key_value(z["KVH"], z["D"], 0, 1)]
