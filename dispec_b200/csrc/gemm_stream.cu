@@ -1,9 +1,9 @@
-// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for up to 64 rows of A, bfloat16 in, 32-bit
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) for up to 128 rows of A, bfloat16 in, 32-bit
 // accumulation: the matrix product of decoding, bound by streaming W once from HBM, on TMA and
 // the fifth-generation tensor cores.
 //
 // Roles are swapped: 128 rows of W are the M side of tcgen05.mma, the few rows of A (padded to
-// 16, 32 or 64) its N side, so the accumulator in tensor memory is 128 lanes (rows of W) by a
+// 16, 32, 64 or 128) its N side, so the accumulator in tensor memory is 128 lanes (rows of W) by a
 // few columns (rows of A).  One thread streams W tiles of 128 rows x 64 k (16 KB a request)
 // and the matching slice of A by TMA into a ring of 4 to 5 stages (two CTAs per SM, about 180 KB
 // on its way per SM, which plain loads cannot keep in flight); one thread issues the products; four warps read
@@ -44,7 +44,7 @@ template <int NB> struct Cfg {
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   // about 100 KB of ring per CTA, so that two CTAs fit an SM: the next kernel's CTA (programmatic
   // dependent launch) fills its ring with W while this kernel's CTA is still streaming
-  static constexpr int STAGES = NB == 16 ? 5 : NB == 32 ? 5 : 4;
+  static constexpr int STAGES = NB == 16 ? 5 : NB == 32 ? 5 : NB == 64 ? 4 : 5;  // 128 rows of A: one CTA per SM
   // One thread's turn of the ring (wait for the stage, fence, four products, commit) takes about
   // 0.3 us, of which the tensor pipe is busy a third (a product of 128 x 16 x 16 every 55 cycles from
   // one issuing thread, every 39 from two: `bench.py --only mma-rate`); a W tile of 16 KB per 0.3 us is
@@ -55,10 +55,15 @@ template <int NB> struct Cfg {
   // on the small products, 8.1 -> 7.6 us on gate/up, 5.75 -> 4.7 us on down.  (Whole k blocks dealt
   // to five issuers that own a stage of the ring each measured 1 % slower on the whole step.)  Two
   // CTAs share the SM's 512 columns of tensor memory.
-  static constexpr int PARTS = NB == 16 ? 4 : 2;
+  // (at 128 rows of A a product of 128 x 128 x 16 keeps the pipe busy for the 64 cycles one thread
+  // needs to issue it: one issuer, no partial accumulators)
+  static constexpr int PARTS = NB == 16 ? 4 : NB <= 64 ? 2 : 1;
   static constexpr int ISSUERS = PARTS;
   static constexpr int FIRST_EPI_WARP = 1 + ISSUERS;
   static constexpr int THREADS = 32 * (1 + ISSUERS + 4);
+  static constexpr int MIN_CTAS = NB <= 64 ? 2 : 1;  // CTAs per SM the registers are held down for
+  // the epilogue takes the accumulator in windows of at most 64 columns (rows of A): what a thread holds at once
+  static constexpr int WINDOW = NB <= 64 ? NB : 64;
   static constexpr int ACC_COLS = PARTS * NB;  // one accumulator buffer
   static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   // K split over a cluster: every CTA sends the rows of its partial tile to the CTA that finishes
@@ -165,8 +170,9 @@ __device__ __forceinline__ float square_sum8(const uint4 u) {
 }
 
 // The accumulator of this thread's W row: the partial accumulators added in a fixed order.
+// NB columns from taddr on; the PARTS partial accumulators lie part_stride columns apart.
 template <int NB, int PARTS>
-__device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[NB]) {
+__device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t part_stride, uint32_t (&v)[NB]) {
   if constexpr (NB == 16) {
     // the partial accumulators lie side by side: one load of PARTS x 16 columns, one wait
     static_assert(PARTS == 4 || PARTS == 2, "loads of 32 or 64 columns");
@@ -185,6 +191,10 @@ __device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[N
       for (int p = 1; p < PARTS; ++p) sum += __uint_as_float(all[p * 16 + c]);
       v[c] = __float_as_uint(sum);
     }
+  } else if constexpr (PARTS == 1) {
+#pragma unroll
+    for (int c0 = 0; c0 < NB; c0 += 32) tmem_ld32_nowait(taddr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
+    tmem_ld_wait();
   } else {
     // 32 columns of every partial accumulator per trip to the tensor memory (a load and its wait
     // take a few hundred nanoseconds: they are not taken one after the other)
@@ -193,7 +203,7 @@ __device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[N
     for (int c0 = 0; c0 < NB; c0 += 32) {
       uint32_t part[32];
       tmem_ld32_nowait(taddr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(v[c0]));
-      tmem_ld32_nowait(taddr + (uint32_t)(NB + c0), part);
+      tmem_ld32_nowait(taddr + part_stride + (uint32_t)c0, part);
       tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c0 + c] = __float_as_uint(__uint_as_float(v[c0 + c]) + __uint_as_float(part[c]));
@@ -202,7 +212,7 @@ __device__ __forceinline__ void load_accumulator(uint32_t taddr, uint32_t (&v)[N
 }
 
 template <int NB, typename TOut>
-__global__ void __launch_bounds__(Cfg<NB>::THREADS, 2)
+__global__ void __launch_bounds__(Cfg<NB>::THREADS, Cfg<NB>::MIN_CTAS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const Args a, int* err) {
   using C = Cfg<NB>;
@@ -436,12 +446,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         tc_fence_after();
         if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // an accumulator is complete (the last one stays)
-        uint32_t v[NB];
-        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * C::ACC_COLS), v);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
-        if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // the accumulator is in registers
+        // the accumulator in windows of WIN columns (rows h0 .. h0 + WIN - 1 of A); one window up to 64 rows
+        constexpr int WIN = C::WINDOW;
+        for (int h0 = 0; h0 < NB && h0 < a.M; h0 += WIN) {
+        uint32_t v[WIN];
+        load_accumulator<WIN, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * C::ACC_COLS + h0), NB, v);
+        if (h0 + WIN >= NB || h0 + WIN >= a.M) {  // the last window: the accumulator is free again
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[buf])) : "memory");
+          if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(5);  // the accumulator is in registers
+        }
         if (a.vec4 && !swiglu && a.residual == nullptr) {
           // Sixteen columns (rows of A) at a time go through shared memory and come back turned
           // around: a lane then holds four W rows of one row of A, the loop over the rows is rolled
@@ -457,15 +472,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (a.C2) gain4 = load4(a.gain2 + n4);
           }
 #pragma unroll
-          for (int c0 = 0; c0 < NB; c0 += 16) {
-            if (c0 >= a.M) break;
+          for (int c0 = 0; c0 < WIN; c0 += 16) {
+            if (h0 + c0 >= a.M) break;
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 16; ++j) stage[j * 32 + lane] = __uint_as_float(v[c0 + j]);
             __syncwarp();
 #pragma unroll 1
             for (int it = 0; it < 4; ++it) {
-              const int m = c0 + 4 * it + sub;
+              const int m = h0 + c0 + 4 * it + sub;
               float4 val = *reinterpret_cast<const float4*>(stage + (4 * it + sub) * 32 + 4 * l8);
               if (a.norm_src) {
                 const float scale = row_scale[m];
@@ -482,14 +497,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
               }
             }
           }
-          if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // the block's stores are issued
-          continue;
+          continue;  // the next window
         }
         // (SwiGLU, a residual, or rows or pointers that do not allow that: one output per thread and row)
         if (a.norm_src) {
 #pragma unroll
-          for (int m = 0; m < NB; ++m)
-            if (m < a.M) v[m] = __float_as_uint(__uint_as_float(v[m]) * row_scale[m]);
+          for (int m = 0; m < WIN; ++m)
+            if (h0 + m < a.M) v[m] = __float_as_uint(__uint_as_float(v[m]) * row_scale[h0 + m]);
         }
         const int n = nb * ROWS_W + row;
         if (swiglu) {
@@ -500,19 +514,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const int col = ((n - lane) >> 1) + (lane & 15);
           const bool n_ok = n - lane < a.N;  // N is a multiple of 32: the block of 32 rows is whole
 #pragma unroll
-          for (int m0 = 0; m0 < NB; m0 += 2) {
+          for (int m0 = 0; m0 < WIN; m0 += 2) {
             const float x0 = __uint_as_float(v[m0]), x1 = __uint_as_float(v[m0 + 1]);
             const float other = __shfl_xor_sync(0xffffffffu, low ? x1 : x0, 16);
             const float gate = low ? x0 : other, up = low ? other : x1;
-            const int m = low ? m0 : m0 + 1;
+            const int m = h0 + (low ? m0 : m0 + 1);
             if (m < a.M && n_ok)
               reinterpret_cast<TOut*>(a.C)[(size_t)m * a.ldc + col] = from_f32<TOut>(silu_times(gate, up));
           }
         } else {
 #pragma unroll
-          for (int m = 0; m < NB; ++m)
-            if (m < a.M && n < a.N) finish<TOut>(a, __uint_as_float(v[m]), m, n);
+          for (int m = 0; m < WIN; ++m)
+            if (h0 + m < a.M && n < a.N) finish<TOut>(a, __uint_as_float(v[m]), h0 + m, n);
         }
+        }  // windows
         if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(9);  // the block's stores are issued
       }
     }
@@ -545,29 +560,32 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int ew = warp - C::FIRST_EPI_WARP;                          // 0..3 in the epilogue warps
     const int n4 = blockIdx.x * ROWS_W + 4 * lane;                    // this lane's four outputs of a row
     const bool n_ok = n4 < a.N;                                       // N is a multiple of 4 here
-    // bias, and the residual of the first two rows this warp finishes (its share at 64 rows over 8
+    // bias, and the residual of the first rows this warp finishes (its share at 64 or 128 rows over 8
     // ranks), are asked for while the products still run
-    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gain4 = bias4, res4[2] = {bias4, bias4};
+    constexpr int RES = NB <= 64 ? 2 : 4;  // rows of a warp's share whose residual is asked for ahead
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gain4 = bias4, res4[RES];
     if (warp >= C::FIRST_EPI_WARP) {
       pdl_wait();  // the residual comes from earlier kernels, and C may still be read by them
       if (!swiglu && n_ok) {
         if (a.bias) bias4 = load4(a.bias + n4);
         if (a.C2) gain4 = load4(a.gain2 + n4);
+      }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int m = rank + (ew + 4 * i) * splits;
-          if (a.residual && m < a.M) res4[i] = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
-        }
+      for (int i = 0; i < RES; ++i) {
+        const int m = rank + (ew + 4 * i) * splits;
+        res4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!swiglu && n_ok && a.residual && m < a.M)
+          res4[i] = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
       }
       compute_own_row_scales(rank, splits);
       if (!__all_sync(0xffffffffu, mbar_wait(&accum_full[0], 0))) failed = 1;
       tc_fence_after();
       if (threadIdx.x == 32 * C::FIRST_EPI_WARP) STAMP(4);  // the accumulator is complete
-      {
-        uint32_t v[NB];
-        load_accumulator<NB, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16), v);
+      for (int h0 = 0; h0 < NB && h0 < a.M; h0 += C::WINDOW) {
+        uint32_t v[C::WINDOW];
+        load_accumulator<C::WINDOW, C::PARTS>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)h0, NB, v);
 #pragma unroll
-        for (int m = 0; m < NB; ++m) tile[m * ROWS_W + row] = __uint_as_float(v[m]);
+        for (int m = 0; m < C::WINDOW; ++m) tile[(h0 + m) * ROWS_W + row] = __uint_as_float(v[m]);
       }
     }
     if constexpr (C::PUSH) {
@@ -625,8 +643,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                                  silu_times(total.w, up.w)));
             }
           } else if (n_ok) {
-            float4 res = i == 0 ? res4[0] : res4[1];
-            if (i >= 2 && a.residual) res = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
+            float4 res = res4[0];
+#pragma unroll
+            for (int q = 1; q < RES; ++q)
+              if (i == q) res = res4[q];
+            if (i >= RES && a.residual) res = load4(reinterpret_cast<const TOut*>(a.residual) + (size_t)m * a.ldr + n4);
             // the same order of sums as finish(): bias, then residual
             total.x = (total.x + bias4.x) + res.x, total.y = (total.y + bias4.y) + res.y;
             total.z = (total.z + bias4.z) + res.z, total.w = (total.w + bias4.w) + res.w;
@@ -670,7 +691,8 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Args& a, in
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits > 1 ? n_blocks : (n_blocks < 2 * num_sms ? n_blocks : 2 * num_sms), splits, 1);
+  const int resident = C::MIN_CTAS * num_sms;  // without a split the CTAs walk over the blocks of W
+  cfg.gridDim = dim3(splits > 1 ? n_blocks : (n_blocks < resident ? n_blocks : resident), splits, 1);
   cfg.blockDim = dim3(C::THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -746,7 +768,9 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
               "dsp_gemm_stream: the rows under the norm must be 16-byte aligned (row stride %ld)", ld_src);
   DSP_REQUIRE(C2 == nullptr || (gain2 != nullptr && epilogue == EPI_PLAIN),
               "dsp_gemm_stream: the scaled second output needs a gain and the plain epilogue");
-  DSP_REQUIRE(M <= 64, "dsp_gemm_stream: M=%d above 64 rows", M);
+  DSP_REQUIRE(M <= 128, "dsp_gemm_stream: M=%d above 128 rows", M);
+  DSP_REQUIRE(M <= 64 || (norm_src == nullptr && C2 == nullptr),
+              "dsp_gemm_stream: a norm split over two products takes at most 64 rows, got %d", M);
   DSP_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "dsp_gemm_stream: K=%d and the row stride must be multiples of 8", K);
   DSP_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "dsp_gemm_stream: operands must be 16-byte aligned");
   DSP_REQUIRE(out_dtype == DSP_BF16 || out_dtype == DSP_F32, "dsp_gemm_stream: unknown output dtype %d", out_dtype);
@@ -760,7 +784,7 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
     DSP_CUDA(cudaGetDevice(&dev));
     DSP_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  const int nb_rows = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  const int nb_rows = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
   CUtensorMap map_w, map_x;
   DSP_REQUIRE(make_map(&map_w, W, N, K, K, ROWS_W), "dsp_gemm_stream: cannot encode the tensor map of W");
   DSP_REQUIRE(make_map(&map_x, A, M, K, lda, nb_rows), "dsp_gemm_stream: cannot encode the tensor map of A");
@@ -784,7 +808,7 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   Args a;
   a.stamp_base = -1;
 #ifdef DSP_STAMPS
-  a.stamp_base = stamp_next_base(splits > 1 ? (long)n_blocks * splits : (n_blocks < 2 * num_sms ? n_blocks : 2 * num_sms), N, K);
+  a.stamp_base = stamp_next_base(splits > 1 ? (long)n_blocks * splits : (n_blocks < (nb_rows > 64 ? 1 : 2) * num_sms ? n_blocks : (nb_rows > 64 ? 1 : 2) * num_sms), N, K);
 #endif
   a.bias = (const bf16*)bias;
   a.residual = residual;
@@ -807,9 +831,11 @@ extern "C" int dsp_gemm_stream(const void* A, long lda, const void* W, const voi
   if (out_dtype == DSP_BF16) {
     if (nb_rows == 16) return launch<16, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
     if (nb_rows == 32) return launch<32, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
-    return launch<64, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+    if (nb_rows == 64) return launch<64, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+    return launch<128, bf16>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
   }
   if (nb_rows == 16) return launch<16, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
   if (nb_rows == 32) return launch<32, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
-  return launch<64, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+  if (nb_rows == 64) return launch<64, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
+  return launch<128, float>(map_w, map_x, a, n_blocks, splits, num_sms, err, stream);
 }

@@ -2,10 +2,10 @@
 
 float32: the FMA kernel (``dsp_gemm_simt``), always; no tensor cores, no reduced-precision
 mode, one FMA chain per output so that a row does not depend on its batch.
-bfloat16: the weight-streaming tcgen05 kernel for up to 64 rows (decoding and the rows whose
+bfloat16: the weight-streaming tcgen05 kernel for up to 128 rows (decoding and the rows whose
 logits are wanted); above that the persistent tcgen05/TMA kernel of this package, except that a
-narrow product with a long K at 65 to a few hundred rows runs the weight-streaming kernel once per
-64 rows where ``tuning.rows_in_chunks_is_faster`` says so (the many-row kernel does not split K).  Operands
+narrow product with a long K at a few hundred rows runs the weight-streaming kernel once per
+128 rows where ``tuning.rows_in_chunks_is_faster`` says so (the many-row kernel does not split K).  Operands
 those kernels cannot take (a width that is no multiple of 8) go to the FMA kernel when there
 are at most 64 rows or 32-bit logits are wanted, and otherwise to the library matrix product
 (cuBLAS through torch.mm), which is where the reference engine itself calls a library
@@ -22,8 +22,8 @@ import torch
 from dispec_b200.ops import library as L
 from dispec_b200.ops import tuning
 
-STREAM_MAX_ROWS = 64  # rows the weight-streaming kernel takes
-NORM_SPLIT_MAX_ROWS = STREAM_MAX_ROWS  # rows up to which a norm is split over two products
+STREAM_MAX_ROWS = 128  # rows the weight-streaming kernel takes
+NORM_SPLIT_MAX_ROWS = 64  # rows up to which a norm is split over two products
 
 
 @dataclass
@@ -184,7 +184,7 @@ def linear(x, w: torch.Tensor, bias: torch.Tensor | None = None,
         elif (backend is None and x.scaled is not None and x.scaled.dtype == torch.bfloat16
               and x.source.shape[0] > STREAM_MAX_ROWS and x.source.stride(1) == 1 and x.source.stride(0) % 8 == 0
               and x.source.data_ptr() % 16 == 0 and stream_supported(STREAM_MAX_ROWS, x.source.shape[1], x.scaled, w)
-              and tuning.rows_in_chunks_is_faster(x.source.shape[0], w.shape[0], x.source.shape[1], w.device)):
+              and tuning.rows_in_chunks_is_faster(x.source.shape[0], w.shape[0], x.source.shape[1], w.device, STREAM_MAX_ROWS)):
             norm, x, backend = x, x.scaled, "stream_chunks"
         else:
             x = x.materialize()
@@ -218,7 +218,7 @@ def linear(x, w: torch.Tensor, bias: torch.Tensor | None = None,
         if stream_supported(M, K, x, w):
             backend = "stream"
         elif (M > STREAM_MAX_ROWS and stream_supported(STREAM_MAX_ROWS, K, x, w)
-              and tuning.rows_in_chunks_is_faster(M, N, K, x.device)):
+              and tuning.rows_in_chunks_is_faster(M, N, K, x.device, STREAM_MAX_ROWS)):
             backend = "stream_chunks"
         elif M > STREAM_MAX_ROWS and tcgen05_supported(x, w):
             backend = "tcgen05"
@@ -227,17 +227,12 @@ def linear(x, w: torch.Tensor, bias: torch.Tensor | None = None,
         else:
             backend = "simt"
     if backend == "stream_chunks":
-        # a narrow product with a long K at 65 to a few hundred rows: the few-row kernel per 64 rows
-        # (see tuning.rows_in_chunks_is_faster)
-        scaled = None
-        if then_norm is not None and out_dtype == torch.bfloat16 and then_norm[0].dtype == torch.bfloat16:
-            scaled = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        # a narrow product with a long K at a few hundred rows: the few-row kernel per 128 rows
+        # (see tuning.rows_in_chunks_is_faster); norms around it run as kernels
         for r in range(0, M, STREAM_MAX_ROWS):
             rows = slice(r, min(M, r + STREAM_MAX_ROWS))
-            part = None if norm is None else NormedRows(norm.source[rows], norm.weight, norm.eps, norm.scaled[rows])
-            _stream(x[rows], w, bias, None if residual is None else residual[rows], out[rows], norm=part,
-                    scaled_out=(then_norm[0], scaled[rows]) if scaled is not None else None)
-        return result(scaled)
+            _stream(x[rows], w, bias, None if residual is None else residual[rows], out[rows])
+        return result()
     if backend == "stream":
         scaled = None
         if (then_norm is not None and M <= NORM_SPLIT_MAX_ROWS and out_dtype == torch.bfloat16

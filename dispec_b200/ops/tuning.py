@@ -41,26 +41,26 @@ def stream_target_ctas(device=None) -> int:
 # trigger, products of 27 MB and more with the late one (1.334 -> 1.312 ms a step at 28 layers).
 STREAM_LATE_TRIGGER_BYTES = 16 << 20
 
-# A product of 65 to a few hundred rows: the many-row kernel cuts it into tiles of 256 rows x 192 or
-# 256 columns and does not split K, so a narrow product with a long K (down_proj: 8 tiles of 140 k
-# blocks) keeps a tenth of the SMs busy; the few-row kernel run once per 64 rows streams W again for
-# every chunk but fills the SMs.  Estimates in microseconds, fitted on a captured decode step at 128
-# rows (qkv / o_proj / gate_up / down: 13 / 14 / 18 / 45 us as one many-row product, 7 / 6 / 13 / 11 us
-# per chunk of 64 rows): whichever is smaller runs.
+# A product of a few hundred rows: the many-row kernel cuts it into tiles of 256 rows x 192 or 256
+# columns and does not split K, so a narrow product with a long K (down_proj: 8 tiles of 140 k
+# blocks) keeps a tenth of the SMs busy; the few-row kernel run once per 128 rows streams W again for
+# every chunk but fills the SMs.  Estimates in microseconds, fitted on captured decode steps of the
+# 1.5B sizes (qkv / o_proj / gate_up / down: 13 / 14 / 18 / 45 us as one many-row product at 128 to
+# 256 rows; 8.9 / 9.0 / 16.3 / 14.2 us per chunk of 128 rows): whichever is smaller runs.
 MANY_ROW_US_PER_K_BLOCK = 0.31   # one tile's k block of 64 on a CTA pair that streams alone
 MANY_ROW_US_FIXED = 6.0
-CHUNK_US_FIXED = 5.0
-CHUNK_BYTES_PER_US = 5.5e6       # W bytes a microsecond of the few-row kernel at 64 rows
+CHUNK_US_FIXED = 8.0
+CHUNK_BYTES_PER_US = 4.5e6       # W bytes a microsecond of the few-row kernel at 128 rows
 
 
-def rows_in_chunks_is_faster(M: int, N: int, K: int, device=None) -> bool:
-    """Whether ceil(M / 64) launches of the few-row product beat one many-row product."""
+def rows_in_chunks_is_faster(M: int, N: int, K: int, device=None, chunk_rows: int = 128) -> bool:
+    """Whether ceil(M / chunk_rows) launches of the few-row product beat one many-row product."""
     pairs = max(1, sm_count(device) // 2)
     width = 256
     tiles = -(-M // 256) * -(-N // width)
     many = MANY_ROW_US_FIXED + -(-tiles // pairs) * -(-K // 64) * MANY_ROW_US_PER_K_BLOCK
     many = max(many, 2.0 * N * K / 6.5e6)
-    chunks = -(-M // 64)
+    chunks = -(-M // chunk_rows)
     return chunks * (CHUNK_US_FIXED + 2.0 * N * K / CHUNK_BYTES_PER_US) < many
 
 

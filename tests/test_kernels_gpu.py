@@ -950,16 +950,16 @@ def test_random_model_filled_on_the_device_equals_the_written_folder(tmp_path, d
     assert a == b
 
 
-@pytest.mark.parametrize("M", [65, 130, 200])
+@pytest.mark.parametrize("M", [130, 200, 256])
 def test_linear_runs_narrow_long_products_in_chunks_of_rows(M):
-    """65 to a few hundred rows, a narrow product with a long K (the down projection's shape): the
-    few-row kernel per 64 rows instead of eight tiles of the many-row kernel; with a norm taken
-    apart on both sides it gives what the single launches give."""
+    """A few hundred rows, a narrow product with a long K (the down projection's shape): the
+    few-row kernel per 128 rows instead of eight tiles of the many-row kernel; a norm handed on
+    from it runs as a kernel."""
     from dispec_b200 import ops
     from dispec_b200.ops import gemm, library, tuning
     N, K, eps = 1536, 8960, 1e-6
-    assert tuning.rows_in_chunks_is_faster(M, N, K, torch.device(dev()))
-    assert not tuning.rows_in_chunks_is_faster(M, 17920, 1536, torch.device(dev()))
+    assert tuning.rows_in_chunks_is_faster(M, N, K, torch.device(dev()), gemm.STREAM_MAX_ROWS)
+    assert not tuning.rows_in_chunks_is_faster(M, 17920, 1536, torch.device(dev()), gemm.STREAM_MAX_ROWS)
     x = rnd((M, K), torch.bfloat16, 201)
     w = rnd((N, K), torch.bfloat16, 202, 0.05)
     b = rnd((N,), torch.bfloat16, 203)
@@ -969,19 +969,46 @@ def test_linear_runs_narrow_long_products_in_chunks_of_rows(M):
     assert library.device_error() == 0
     ref = x.double() @ w.double().T + b.double() + r.double()
     torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
-    assert torch.equal(nxt.scaled, (out.float() * gain.float()).bfloat16())
-    # the norm handed on, into another narrow product
+    assert nxt.scaled is None and nxt.source is out
     w2 = rnd((1024, N), torch.bfloat16, 207, 0.1)
-    got = gemm.linear(nxt, w2)
-    hd = out.double()
-    rstd = torch.rsqrt((hd * hd).mean(dim=1, keepdim=True) + eps)
-    own = nxt.scaled.double() @ w2.double().T * rstd
-    two = gemm.linear(ops.rms_norm(out, gain, eps), w2)
-    torch.testing.assert_close(two.double(), (hd * rstd * gain.double()) @ w2.double().T, atol=6e-2, rtol=3e-2)
-    if tuning.rows_in_chunks_is_faster(M, 1024, N, torch.device(dev())):
-        torch.testing.assert_close(got.double(), own, atol=3e-2, rtol=2e-2)
-    else:  # the many-row kernel took it: the norm kernel ran first
-        assert torch.equal(got, two)
+    assert torch.equal(gemm.linear(nxt, w2), gemm.linear(ops.rms_norm(out, gain, eps), w2))
+
+
+@pytest.mark.parametrize("M,N,K,bias,resid,swiglu", [(65, 2048, 1536, True, False, False), (128, 1536, 8960, False, True, False),
+                                                     (100, 17920, 1536, False, False, True), (128, 1000, 200, True, True, False),
+                                                     (97, 40000, 96, True, False, False), (128, 4096, 1536, False, False, True)])
+def test_gemm_stream_up_to_128_rows(M, N, K, bias, resid, swiglu):
+    """65 to 128 rows of A in the few-row kernel: the accumulator of 128 columns is taken in two
+    windows of 64 by the epilogues (K split over a cluster, and not)."""
+    from dispec_b200.ops import gemm, library
+    x = rnd((M, K), torch.bfloat16, 211)
+    x[M - 1] *= 3.0  # the last row, in the second window
+    if swiglu:
+        I = N // 2
+        wg, wu = rnd((I, K), torch.bfloat16, 212, 0.15), rnd((I, K), torch.bfloat16, 213, 0.15)
+        blk = gemm.SWIGLU_BLOCK
+        w = torch.stack([wg.view(I // blk, blk, K), wu.view(I // blk, blk, K)], dim=1).reshape(N, K).contiguous()
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=dev())
+        gemm._stream(x, w, None, None, out, epilogue=gemm.EPI_SWIGLU)
+        g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+        assert library.device_error() == 0
+        torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+        return
+    w = rnd((N, K), torch.bfloat16, 214, 0.1)
+    b = rnd((N,), torch.bfloat16, 215) if bias else None
+    r = rnd((M, N), torch.bfloat16, 216) if resid else None
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    gemm._stream(x, w, b, r, out)
+    assert library.device_error() == 0
+    ref = x.double() @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if resid:
+        ref = ref + r.double()
+    torch.testing.assert_close(out.double(), ref, atol=3e-2, rtol=2e-2)
+    again = torch.empty_like(out)
+    gemm._stream(x, w, b, r, again)
+    assert torch.equal(out, again)
 
 
 def test_measurement_entries_run_and_refuse_bad_arguments():
