@@ -237,7 +237,7 @@ class CacheManager:
             return []
         released = []
         for g, table in enumerate(r.tables):
-            for page in table:
+            for page in reversed(table):  # the free stack then hands them out in table order again
                 if page >= 0:
                     self.pools[g].release(page)
                     released.append((g, page))

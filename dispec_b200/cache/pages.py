@@ -3,6 +3,12 @@
 Follows puneethgv/DiSpec dispec/kv/block_manager.py:37-64,89-96 (free list popped from
 the end, a reference count per page that returns the page at zero) and adds reservations:
 pages promised to a request at admission that no other request can take.
+
+The stack is laid so that a fresh pool hands out ascending page ids, and a request's pages go
+back in the reverse of their table order (cache/manager.py), so that the next request gets them
+ascending again: pages that follow each other in a table then follow each other in memory, and
+the attention kernel for portions of prompts fetches such a run with one request.  Nothing is
+wrong when they do not; it only takes more requests.
 """
 from __future__ import annotations
 
@@ -19,7 +25,7 @@ class PagePool:
         if num_pages <= 0:
             raise ValueError(f"a page pool needs at least one page, got {num_pages}")
         self.num_pages = num_pages
-        self._free: list[int] = list(range(num_pages))
+        self._free: list[int] = list(range(num_pages - 1, -1, -1))
         self._ref: list[int] = [0] * num_pages
         self.reserved = 0  # pages promised but not yet handed out
 

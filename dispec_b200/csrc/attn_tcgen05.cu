@@ -63,6 +63,7 @@ struct Params {
   bf16* out;
   long out_stride;
   int H, KVH, G, tokens_per_tile, page_size, num_pages, window;
+  int page_runs;  // the run maps are valid
   float scale_log2;
   int* err;
 };
@@ -122,7 +123,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUtensorMap map_k,
-                    const __grid_constant__ CUtensorMap map_v) {
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap runs_k,
+                    const __grid_constant__ CUtensorMap runs_v) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
@@ -241,7 +243,18 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         else mbar_expect_tx(&kv_full[s], (uint32_t)__popc(live) * page_bytes);
       }
       __syncwarp();
-      if (pg >= 0) {
+      // The tile's pages lie one after the other in the pool (what a pool hands out while it is
+      // not fragmented): one request per operand brings them all, where a page of 16 tokens
+      // otherwise takes 2 * KD requests of 2 KB, and the requests, not the bytes, are what the
+      // TMA unit's time goes to.  Both ways leave the same bytes at the same places.
+      const int pg_first = __shfl_sync(0xffffffffu, pg, 0);
+      const bool in_run = __all_sync(0xffffffffu, lane >= pages_per_tile || (pg >= 0 && pg == pg_first + lane));
+      if (p.page_runs && in_run && pg_first + pages_per_tile <= p.num_pages) {
+        if (lane == 0) {
+          tma_load_4d(k_s + s * KV_BYTES, &runs_k, &kv_full[s], 0, kvh * p.page_size, pg_first, 0);
+          tma_load_4d(v_s + s * KV_BYTES, &runs_v, &kv_full[s], 0, kvh * p.page_size, pg_first, 0);
+        }
+      } else if (pg >= 0) {
         const int row = (pg * p.KVH + kvh) * p.page_size;
         const int dst = s * KV_BYTES + lane * p.page_size * 128;
 #pragma unroll
@@ -505,32 +518,48 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
   }
 }
 
+// DISPEC_B200_PAGE_RUNS=0 in the environment keeps every page on a request of its own (for
+// measurements, and for tests that compare the two ways of loading); read at every call.
+bool page_runs_enabled() {
+  const char* v = getenv("DISPEC_B200_PAGE_RUNS");
+  return !(v != nullptr && v[0] == '0');
+}
+
 struct MapKey {
   const void* base;
-  long rows;
-  int page_size;
-  CUtensorMap map;
+  long num_pages;
+  int heads, page_size;
+  bool has_runs;
+  CUtensorMap map, runs;
 };
-// tensor maps of the pools seen so far (a handful: two per layer cache)
-bool pool_map(const void* base, long rows, int page_size, CUtensorMap* out) {
+// tensor maps of the pools seen so far (a handful: two per layer cache): one whose box is a page of
+// one head, and one whose box is a key tile's worth of consecutive pages (absent for a pool of
+// fewer pages than a tile has)
+bool pool_map(const void* base, long num_pages, int heads, int page_size, CUtensorMap* out, CUtensorMap* runs,
+              bool* has_runs) {
   constexpr int SLOTS = 256;
   static MapKey cache[SLOTS];
   static int used = 0;
   for (int i = 0; i < used; ++i)
-    if (cache[i].base == base && cache[i].rows == rows && cache[i].page_size == page_size) {
+    if (cache[i].base == base && cache[i].num_pages == num_pages && cache[i].heads == heads &&
+        cache[i].page_size == page_size) {
       *out = cache[i].map;
+      *runs = cache[i].runs;
+      *has_runs = cache[i].has_runs;
       return true;
     }
-  CUtensorMap m;
-  if (!make_map(&m, base, rows, D, D, page_size)) return false;
-  if (used < SLOTS) {
-    cache[used].base = base;
-    cache[used].rows = rows;
-    cache[used].page_size = page_size;
-    cache[used].map = m;
-    ++used;
-  }
-  *out = m;
+  MapKey k;
+  k.base = base;
+  k.num_pages = num_pages;
+  k.heads = heads;
+  k.page_size = page_size;
+  if (!make_map(&k.map, base, num_pages * heads * page_size, D, D, page_size)) return false;
+  k.has_runs = make_map_page_runs(&k.runs, base, num_pages, heads, page_size, D, BN / page_size);
+  if (!k.has_runs) k.runs = k.map;
+  if (used < SLOTS) cache[used++] = k;
+  *out = k.map;
+  *runs = k.runs;
+  *has_runs = k.has_runs;
   return true;
 }
 }  // namespace
@@ -571,9 +600,12 @@ extern "C" int DSP_CAT(dsp_attn_tcgen05_d, DSP_HEAD_DIM)(
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = err;
-  CUtensorMap map_k, map_v;
-  const long rows = (long)num_pages * KVH * page_size;
-  if (!pool_map(k_pool, rows, page_size, &map_k) || !pool_map(v_pool, rows, page_size, &map_v)) return 4;
+  CUtensorMap map_k, map_v, runs_k, runs_v;
+  bool has_runs_k = false, has_runs_v = false;
+  if (!pool_map(k_pool, num_pages, KVH, page_size, &map_k, &runs_k, &has_runs_k) ||
+      !pool_map(v_pool, num_pages, KVH, page_size, &map_v, &runs_v, &has_runs_v))
+    return 4;
+  p.page_runs = has_runs_k && has_runs_v && page_runs_enabled();
   static bool configured = false;  // once; not repeated under graph capture
   if (!configured) {
     if (cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
@@ -591,5 +623,5 @@ extern "C" int DSP_CAT(dsp_attn_tcgen05_d, DSP_HEAD_DIM)(
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, attn_tcgen05_kernel, p, tile_offset, map_k, map_v) == cudaSuccess ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, attn_tcgen05_kernel, p, tile_offset, map_k, map_v, runs_k, runs_v) == cudaSuccess ? 0 : 1;
 }

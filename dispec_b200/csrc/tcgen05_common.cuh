@@ -93,6 +93,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 // K-major operand tile, rows of 128 bytes, 128-byte swizzle: groups of 8 rows are 1024 bytes apart
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -213,6 +220,22 @@ inline bool make_map_k_blocks(CUtensorMap* map, const void* base, long rows, lon
   cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)k_blocks};
   cuuint32_t elem[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// A paged pool [pages][heads][page_size][D] seen as (64 of d, rows of a page's heads, pages, D / 64):
+// one box of (64, page_size, pages_per_box, D / 64) brings one head's rows of pages_per_box
+// CONSECUTIVE pages with a single request, laid out as D / 64 slices of [pages_per_box * page_size][64],
+// which is the layout that the same pages give when each is fetched with a box of its own.
+inline bool make_map_page_runs(CUtensorMap* map, const void* base, long num_pages, int heads, int page_size, int D,
+                               int pages_per_box) {
+  EncodeTiled fn = encode_fn();
+  if (fn == nullptr || D % 64 != 0 || num_pages < pages_per_box) return false;
+  cuuint64_t dims[4] = {64u, (cuuint64_t)heads * page_size, (cuuint64_t)num_pages, (cuuint64_t)(D / 64)};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)heads * page_size * D * 2, 128u};
+  cuuint32_t box[4] = {64u, (cuuint32_t)page_size, (cuuint32_t)pages_per_box, (cuuint32_t)(D / 64)};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

@@ -7,9 +7,9 @@ import pytest
 from dispec_b200.cache import CacheGroupSpec, CacheManager, OutOfPagesError, OutOfSlotsError, PagePool
 
 
-def test_pool_hands_out_the_highest_id_first_and_refuses_double_free():
+def test_pool_hands_out_ascending_ids_and_refuses_double_free():
     pool = PagePool(4)
-    assert [pool.alloc() for _ in range(4)] == [3, 2, 1, 0]
+    assert [pool.alloc() for _ in range(4)] == [0, 1, 2, 3]
     with pytest.raises(OutOfPagesError):
         pool.alloc()
     assert pool.release(2) and pool.alloc() == 2
@@ -34,6 +34,21 @@ def test_pages_grow_only_when_full_and_return_on_free():
     assert m.num_free_pages() == 8 and m.free_slots() == 2
     m.check()
     assert m.free("a") == []  # freeing twice is harmless
+
+
+def test_a_request_after_another_gets_its_pages_in_ascending_order_again():
+    m = CacheManager([CacheGroupSpec.key_value(2, 16)], page_size=4, num_pages=12, max_num_seqs=2)
+    m.admit("a")
+    m.extend("a", 20)
+    assert list(m.block_table("a")) == [0, 1, 2, 3, 4]
+    m.admit("b")
+    m.extend("b", 8)
+    m.commit("a", 20)
+    m.free("a")
+    m.admit("c")
+    m.extend("c", 28)  # a's five pages in a's order, then fresh ones
+    assert list(m.block_table("c")) == [0, 1, 2, 3, 4, 7, 8]
+    m.check()
 
 
 def test_extend_takes_nothing_when_it_cannot_take_all():

@@ -164,12 +164,32 @@ def _attention_reference(q, k, v, positions, window, scale):
     return out
 
 
-def _paged(k, v, page, num_pages, dtype, seed):
-    """Scatter contiguous k/v [ctx,KVH,D] into pools through a shuffled page table."""
+def _paged(k, v, page, num_pages, dtype, seed, order="shuffled"):
+    """Scatter contiguous k/v [ctx,KVH,D] into pools through a page table: shuffled; "ascending"
+    (consecutive pages up to the pool's last one); or "runs": consecutive stretches of changing
+    length, with breaks inside key tiles, a descending stretch and the pool's last page in use."""
     ctx, KVH, D = k.shape
     n = (ctx + page - 1) // page
     g = torch.Generator().manual_seed(seed)
-    perm = torch.randperm(num_pages, generator=g)[:n]
+    if order == "shuffled":
+        perm = torch.randperm(num_pages, generator=g)[:n]
+    elif order == "ascending":
+        perm = torch.arange(num_pages - n, num_pages)
+    else:
+        assert order == "runs"
+        free, perm, length = list(range(num_pages)), [], 1
+        while len(perm) < n:  # stretches of 1, 2, ... 9, 1, ... pages taken from both ends in turn
+            take = min(length, n - len(perm))
+            if (length // 3) % 2 == 0:
+                perm += free[-take:]
+                del free[-take:]
+            else:
+                perm += free[:take]
+                del free[:take]
+            if length == 5:
+                perm[-take:] = reversed(perm[-take:])
+            length = length % 9 + 1
+        perm = torch.tensor(perm)
     kp = torch.full((num_pages, KVH, page, D), float("nan"), dtype=dtype)
     vp = kp.clone()
     for b in range(ctx):
@@ -190,7 +210,8 @@ ATTN_CASES = [
 ]
 
 
-def run_attention(kind, dtype, H, KVH, D, page, ctx, q_len, window, plant=None, seed=0, prefill_kernel=None):
+def run_attention(kind, dtype, H, KVH, D, page, ctx, q_len, window, plant=None, seed=0, prefill_kernel=None,
+                  page_order="shuffled"):
     """One sequence, its last q_len positions as queries.  ``plant``: key index whose score is
     made to stand out for every query that can see it."""
     from dispec_b200.ops import attention as A
@@ -209,7 +230,7 @@ def run_attention(kind, dtype, H, KVH, D, page, ctx, q_len, window, plant=None, 
     scale = D ** -0.5
     ref = _attention_reference(q.double(), k.double(), v.double(), positions, window, scale)
     num_pages = (ctx + page - 1) // page + 3
-    kp, vp, perm = _paged(k, v, page, num_pages, dtype, seed)
+    kp, vp, perm = _paged(k, v, page, num_pages, dtype, seed, page_order)
     table = perm.view(1, -1).to(dev())
     qd = q.to(dtype).reshape(q_len, H * D).to(dev())
     out = torch.empty((q_len, H * D), dtype=dtype, device=dev())
@@ -707,6 +728,28 @@ def test_attention_prefill_backends(case, backend):
     assert A.tcgen05_supported(case[2], case[0] // case[1], case[3], torch.bfloat16)
     out, ref = run_attention("tensor_core", torch.bfloat16, *case, prefill_kernel=backend)
     torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("case", TCGEN05_CASES + [(12, 2, 128, 16, 2048, 1100, 0), (14, 2, 64, 8, 1500, 640, 300)])
+@pytest.mark.parametrize("order", ["ascending", "runs"])
+def test_attention_tcgen05_pages_in_runs(case, order, monkeypatch):
+    """Key tiles whose pages follow each other in the pool are fetched with one request per operand;
+    the result is, bit for bit, that of the same keys on scattered pages and that of a build
+    which fetches page by page."""
+    out, ref = run_attention("tensor_core", torch.bfloat16, *case, prefill_kernel="tcgen05", page_order=order)
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+    scattered, _ = run_attention("tensor_core", torch.bfloat16, *case, prefill_kernel="tcgen05")
+    assert torch.equal(out, scattered)
+    monkeypatch.setenv("DISPEC_B200_PAGE_RUNS", "0")
+    by_page, _ = run_attention("tensor_core", torch.bfloat16, *case, prefill_kernel="tcgen05", page_order=order)
+    assert torch.equal(out, by_page)
+
+
+@pytest.mark.parametrize("plant", [0, 63, 64, 200, 511, 699])
+def test_attention_tcgen05_far_key_stands_out_on_pages_in_runs(plant):
+    out, ref = run_attention("tensor_core", torch.bfloat16, 12, 2, 128, 16, 700, 150, 0, plant=plant, seed=plant,
+                             page_order="ascending")
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=3e-2)
 
 
 @pytest.mark.parametrize("plant", [0, 15, 16, 63, 64, 65, 127, 128, 255, 256, 511, 600, 699])
