@@ -6,9 +6,11 @@
 // A tile is 128 query rows of one KV head of one sequence; a row is a (token, head-in-group)
 // pair, so the G query heads that share a KV head share every key/value load.  Keys are walked in
 // tiles of 64 through the page table.  Roles, one CTA per tile:
-//   warp 0      issues the TMA loads of K and V tiles, one lane per page (a ring of four tiles);
-//   warp 1      one thread issues the products S[i] = Q K[i]^T and O[i % 2] += P[i] V[i], each as soon
-//               as its operands are ready (it polls the barriers of both);
+//   warp 0      issues the TMA loads of the K tiles and of the V tiles, each into a ring of its own: a
+//               K tile is free again when its scores are complete, a V tile two softmax iterations
+//               later, when its output product is;
+//   warps 1, 11 one thread each issues the score products S[i] = Q K[i]^T of one softmax group;
+//   warp 10     one thread issues the output products O[i % 2] += P[i] V[i];
 //   warps 2..9  two softmax groups of four warps.  Group g owns the key tiles i = g, g + 2, ...: its own
 //               score buffer S[g] and output accumulator O[g] in tensor memory, its own P[g] in
 //               shared memory and its own running maximum and sum, so the two groups never exchange
@@ -36,19 +38,29 @@ using namespace tc;
 
 constexpr int D = DSP_HEAD_DIM;
 static_assert(D == 64 || D == 128, "this kernel is built for head sizes 64 and 128");
-constexpr int BM = 128, BN = 64, THREADS = 352, STAGES = 4;
-constexpr int PV_WARP = 10;  // warp 0: TMA, warp 1: issues S = Q K^T, warps 2-9: softmax, warp 10: issues O += P V
+constexpr int BM = 128, BN = 64, THREADS = 384;
+constexpr int K_STAGES = 5, V_STAGES = 7;  // tiles in the ring of keys and in the ring of values
+constexpr int BAD_SLOTS = 16;              // a tile's unreadable pages are remembered until its softmax has begun
+static_assert(BAD_SLOTS >= K_STAGES + 4, "a slot is rewritten K_STAGES + 4 tiles later at the earliest");
+// warp 0: TMA, warps 1 and 11: issue S = Q K^T for softmax group 0 and 1, warps 2-9: softmax, warp 10: issues O += P V
+constexpr int PV_WARP = 10, S1_WARP = 11;
 constexpr int KD = D / 64;            // 64-wide slices of the head dimension (128-byte rows)
-constexpr int Q_SLICE = BM * 128;     // bytes of one slice of the Q tile
 constexpr int KV_SLICE = BN * 128;    // bytes of one slice of a K or V tile
-constexpr int Q_BYTES = KD * Q_SLICE;
 constexpr int KV_BYTES = KD * KV_SLICE;
-constexpr int P_BYTES = BM * 128;     // 128 rows x 64 keys, bfloat16
-constexpr int SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + 2 * P_BYTES + 1024;
-constexpr int S_COLS = BN;            // columns of one score buffer in tensor memory
-constexpr int O_COL = 2 * S_COLS;     // the two output accumulators follow the two score buffers
+constexpr int SMEM_BYTES = (K_STAGES + V_STAGES) * KV_BYTES + 1024;
+static_assert(SMEM_BYTES + 1536 <= 227 * 1024, "dynamic and static shared memory of a CTA");
+// Tensor memory, 32-bit columns: two score buffers, two output accumulators, and the A operands of
+// both products, two bfloat16 per column: P of each group (64 keys) and the Q tile.  Operands that
+// the tensor cores take from tensor memory cost no shared-memory bandwidth: with Q and P in shared
+// memory, a key tile moved 128 KB through the shared-memory port (Q 32, K 16, P 16 written and 16
+// read, V 16, the arriving tiles 32), 1,000 of the 1,200 cycles that a tile took.
+constexpr int S_COLS = BN;                 // columns of one score buffer
+constexpr int O_COL = 2 * S_COLS;          // the two output accumulators follow the two score buffers
+constexpr int P_COLS = BN / 2;             // columns of one group's P
+constexpr int P_COL = O_COL + 2 * D;
+constexpr int Q_COL = P_COL + 2 * P_COLS;  // D / 2 columns
 constexpr int TMEM_COLS = 512;
-static_assert(O_COL + 2 * D <= TMEM_COLS, "tensor memory layout");
+static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory layout");
 constexpr float RESCALE_STEP = 8.f;   // the running maximum follows the true one in steps of 2^8
 
 struct Params {
@@ -99,18 +111,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-// one non-blocking look at a barrier phase
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -128,16 +128,19 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
-  __shared__ __align__(8) uint64_t kv_full[STAGES];   // K and V of a tile have landed
-  __shared__ __align__(8) uint64_t kv_empty[STAGES];  // both products of the tile have read them
+  __shared__ __align__(8) uint64_t k_full[K_STAGES];   // the K tile has landed
+  __shared__ __align__(8) uint64_t k_empty[K_STAGES];  // the tile's scores are complete
+  __shared__ __align__(8) uint64_t v_full[V_STAGES];   // the V tile has landed
+  __shared__ __align__(8) uint64_t v_empty[V_STAGES];  // the tile's output product is complete
   __shared__ __align__(8) uint64_t s_full[2];         // a score buffer is complete
   __shared__ __align__(8) uint64_t s_free[2];         // the group has read its score buffer
   __shared__ __align__(8) uint64_t p_full[2];         // P written, O rescaled, V rows zeroed
   __shared__ __align__(8) uint64_t o_done[2];         // O[g] += P V of a tile is complete
+  __shared__ __align__(8) uint64_t q_ready;           // the Q tile is in tensor memory
   __shared__ float merge_m[BM], merge_l[BM];          // group 1's running maximum and sum per row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
-  __shared__ uint32_t bad_pages[STAGES];  // bit j: page j of the key tile in this stage had no valid id (not loaded)
+  __shared__ uint32_t bad_pages[BAD_SLOTS];  // of key tile i, in slot i % BAD_SLOTS; bit j: page j had no valid id (not loaded)
 
   pdl_launch_dependents();
   pdl_wait();
@@ -160,15 +163,17 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
   const int n_kt = kt_end - kt_begin;
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
 
-  unsigned char* q_s = smem;
-  unsigned char* k_s = smem + Q_BYTES;                        // [stage][slice][64 keys][128 bytes]
-  unsigned char* v_s = k_s + STAGES * KV_BYTES;
-  unsigned char* p_s = v_s + STAGES * KV_BYTES;               // [group][128 rows][128 bytes]
+  unsigned char* k_s = smem;                                  // [stage][slice][64 keys][128 bytes]
+  unsigned char* v_s = k_s + K_STAGES * KV_BYTES;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
@@ -176,6 +181,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
       mbar_init(&p_full[b], 4);  // one arrival per warp of the group
       mbar_init(&o_done[b], 1);
     }
+    mbar_init(&q_ready, 4);  // one arrival per warp that writes a quarter of the tile
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -185,113 +191,168 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // ---- Q tile: thread r of warps 2..5 fetches row r (rows past the tile are zero) while the tensor
+  // memory is being allocated, and writes it there afterwards: lane r, two bfloat16 per column
+  uint4 q_row[D / 8];
   if (warp >= 2 && warp < 6) {
-    // ---- Q tile: thread r copies row r into the swizzled K-major layout; rows past the tile are zero
     const int r = (warp & 3) * 32 + lane;
     const bool valid = r < nrows;
     const uint4* src = nullptr;
     if (valid)
       src = reinterpret_cast<const uint4*>(p.q + (size_t)(qs + tok0 + r / G) * p.q_stride +
                                            (size_t)(kvh * G + r % G) * D);
-    const uint32_t row_base = smem_u32(q_s) + (uint32_t)r * 128u;
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-      const uint4 v = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-      st_shared16(row_base + (uint32_t)(c >> 3) * Q_SLICE + (uint32_t)(((c & 7) ^ (r & 7)) << 4), v);
-    }
-    fence_async_smem();
+    for (int c = 0; c < D / 8; ++c) q_row[c] = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  if (warp >= 2 && warp < 6) {
+    const uint32_t q_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)Q_COL;
+#pragma unroll
+    for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      uint32_t w[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        w[4 * c] = q_row[c0 / 4 + c].x;
+        w[4 * c + 1] = q_row[c0 / 4 + c].y;
+        w[4 * c + 2] = q_row[c0 / 4 + c].z;
+        w[4 * c + 3] = q_row[c0 / 4 + c].w;
+      }
+      tmem_st32(q_addr + (uint32_t)c0, w);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_ready);
+  }
 
   if (warp == 0) {
-    // ---- TMA producer: lane j looks up page j of the key tile and issues its loads
+    // ---- TMA producer of the K tiles and the V tiles, each into a ring of its own
     const int pages_per_tile = BN / p.page_size;
-    const uint32_t page_bytes = 2u * KD * (uint32_t)p.page_size * 128u;  // K and V, every slice
-    // pages that hold keys some row may see; the others are not read.  The table entry of the next
-    // tile is fetched before the wait on the ring, so its latency is off the loads' path.
-    auto lookup = [&](int i) -> int {
-      const int first = (kt_begin + i) * BN + lane * p.page_size;
-      if (lane < pages_per_tile && first <= pos_last && first + p.page_size > lo) return table[first / p.page_size];
+    const uint32_t page_bytes = (uint32_t)KD * (uint32_t)p.page_size * 128u;  // every slice, of K or of V
+    // Page ids are looked up for a chunk of 32 / pages_per_tile key tiles at a time, lane l
+    // holding page l % pages_per_tile of the chunk's tile l / pages_per_tile, and the chunk after
+    // the current one is asked for while the current one is walked.  What a tile needs (is a page
+    // wanted, has it a valid id, do the tile's pages follow one another in the pool) is worked
+    // out for the whole chunk with one shuffle and three votes, and the tile's first lane, which
+    // holds its first page, waits for the ring slot and issues the request: per tile the loop
+    // then has one barrier operation in a row, where a table read, issued one tile ahead (900
+    // cycles under load), or four shuffles (250 cycles each while the softmax warps keep the
+    // shared-memory pipe busy) set the pace of the whole kernel; a tile arrives 500 cycles
+    // after its request.
+    const int ppt_shift = __ffs(pages_per_tile) - 1;  // page sizes are powers of two here
+    const int page_shift_p = __ffs(p.page_size) - 1;
+    const int chunk_shift = 5 - ppt_shift, chunk_mask = (1 << chunk_shift) - 1;  // tiles per chunk
+    const int page_in_tile = lane & (pages_per_tile - 1);
+    const uint32_t tile_lanes = pages_per_tile == 32 ? 0xffffffffu : ((1u << pages_per_tile) - 1u);
+    auto load_chunk = [&](int c) -> int {
+      const int i = (c << chunk_shift) + (lane >> ppt_shift);
+      const int first = (kt_begin + i) * BN + page_in_tile * p.page_size;
+      if (i < n_kt && first <= pos_last && first + p.page_size > lo) return table[first >> page_shift_p];
       return -2;  // not wanted
     };
-    int pg_next = lookup(0);
+    int pg = -2, pg_next = load_chunk(0);
+    uint32_t bad_mask = 0, live_mask = 0, run_mask = 0;
+    int sk = 0, rk = 0, sv = 0, rv = 0;  // ring slots of K and of V and their use counts
     for (int i = 0; i < n_kt; ++i) {
-      const int s = i % STAGES;
-      int pg = pg_next;
-      if (i + 1 < n_kt) pg_next = lookup(i + 1);
+      const int in_chunk = i & chunk_mask;
+      if (in_chunk == 0) {
+        pg = pg_next;
+        pg_next = load_chunk((i >> chunk_shift) + 1);
+        // a page id outside the pool: recorded, not loaded, and its keys are hidden from every row
+        const bool bad = pg != -2 && (pg < 0 || pg >= p.num_pages);
+        if (bad) {
+          atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          pg = -1;
+        }
+        bad_mask = __ballot_sync(0xffffffffu, bad);
+        live_mask = __ballot_sync(0xffffffffu, pg >= 0);
+        const int first_pg = __shfl_sync(0xffffffffu, pg, lane & ~(pages_per_tile - 1));
+        run_mask = __ballot_sync(0xffffffffu, pg >= 0 && pg == first_pg + page_in_tile &&
+                                                  first_pg + pages_per_tile <= p.num_pages);
+      }
+      const int shift = in_chunk << ppt_shift;              // the tile's first lane
+      const uint32_t live = (live_mask >> shift) & tile_lanes;
+      const bool in_run = p.page_runs && ((run_mask >> shift) & tile_lanes) == tile_lanes;
+      const bool leader = lane == shift;
+      const bool mine = (lane >> ppt_shift) == in_chunk;   // this lane holds a page of the tile
       int ok = 1;
-      if (lane == 0) ok = !failed && mbar_wait(&kv_empty[s], ((i / STAGES) & 1) ^ 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        if (lane == 0) failed = 1;
+      if (leader) ok = !failed && mbar_wait_both(&k_empty[sk], (rk & 1) ^ 1, &v_empty[sv], (rv & 1) ^ 1);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (leader) failed = 1;
         break;
       }
-      // a page id outside the pool: recorded, not loaded, and its keys are hidden from every row
-      const bool bad = pg != -2 && (pg < 0 || pg >= p.num_pages);
-      if (bad) {
-        atomicOr(p.err, DSP_ERR_BAD_PAGE);
-        pg = -1;
+      if (leader) {
+        bad_pages[i % BAD_SLOTS] = (bad_mask >> shift) & tile_lanes;  // published by the arrival on k_full below
+        if (live == 0) {
+          mbar_arrive(&k_full[sk]);
+          mbar_arrive(&v_full[sv]);
+        } else {
+          mbar_expect_tx(&k_full[sk], (uint32_t)__popc(live) * page_bytes);
+          mbar_expect_tx(&v_full[sv], (uint32_t)__popc(live) * page_bytes);
+        }
       }
-      const uint32_t bad_bits = __ballot_sync(0xffffffffu, bad);
-      const uint32_t live = __ballot_sync(0xffffffffu, pg >= 0);
-      if (lane == 0) {
-        bad_pages[s] = bad_bits;  // published by the arrival on kv_full below
-        if (live == 0) mbar_arrive(&kv_full[s]);
-        else mbar_expect_tx(&kv_full[s], (uint32_t)__popc(live) * page_bytes);
-      }
-      __syncwarp();
       // The tile's pages lie one after the other in the pool (what a pool hands out while it is
       // not fragmented): one request per operand brings them all, where a page of 16 tokens
-      // otherwise takes 2 * KD requests of 2 KB, and the requests, not the bytes, are what the
-      // TMA unit's time goes to.  Both ways leave the same bytes at the same places.
-      const int pg_first = __shfl_sync(0xffffffffu, pg, 0);
-      const bool in_run = __all_sync(0xffffffffu, lane >= pages_per_tile || (pg >= 0 && pg == pg_first + lane));
-      if (p.page_runs && in_run && pg_first + pages_per_tile <= p.num_pages) {
-        if (lane == 0) {
-          tma_load_4d(k_s + s * KV_BYTES, &runs_k, &kv_full[s], 0, kvh * p.page_size, pg_first, 0);
-          tma_load_4d(v_s + s * KV_BYTES, &runs_v, &kv_full[s], 0, kvh * p.page_size, pg_first, 0);
+      // otherwise takes KD requests of 2 KB, and the requests, not the bytes, are what the TMA
+      // unit's time goes to.  Both ways leave the same bytes at the same places.
+      if (in_run) {
+        if (leader) {
+          tma_load_4d(k_s + sk * KV_BYTES, &runs_k, &k_full[sk], 0, kvh * p.page_size, pg, 0);
+          tma_load_4d(v_s + sv * KV_BYTES, &runs_v, &v_full[sv], 0, kvh * p.page_size, pg, 0);
         }
-      } else if (pg >= 0) {
-        const int row = (pg * p.KVH + kvh) * p.page_size;
-        const int dst = s * KV_BYTES + lane * p.page_size * 128;
+      } else {
+        __syncwarp();  // the bytes are announced before any lane's load can count them
+        if (mine && pg >= 0) {
+          const int row = (pg * p.KVH + kvh) * p.page_size;
+          const int dst = page_in_tile * p.page_size * 128;
 #pragma unroll
-        for (int h = 0; h < KD; ++h) {
-          tma_load_2d(k_s + dst + h * KV_SLICE, &map_k, &kv_full[s], h * 64, row);
-          tma_load_2d(v_s + dst + h * KV_SLICE, &map_v, &kv_full[s], h * 64, row);
+          for (int h = 0; h < KD; ++h) {
+            tma_load_2d(k_s + sk * KV_BYTES + dst + h * KV_SLICE, &map_k, &k_full[sk], h * 64, row);
+            tma_load_2d(v_s + sv * KV_BYTES + dst + h * KV_SLICE, &map_v, &v_full[sv], h * 64, row);
+          }
         }
       }
+      if (++sk == K_STAGES) {
+        sk = 0;
+        ++rk;
+      }
+      if (++sv == V_STAGES) {
+        sv = 0;
+        ++rv;
+      }
     }
-  } else if (warp == 1) {
-    // ---- issuer of the score products
+  } else if (warp == 1 || warp == S1_WARP) {
+    // ---- issuers of the score products: warp 1 for the tiles of softmax group 0, warp S1_WARP for
+    // those of group 1.  One thread for both spent 340 cycles per tile on barriers that were long
+    // complete and 700 on issuing eight products and two commits, and these 1,250 cycles a tile,
+    // in one thread, were the kernel's pace.
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(BM, BN);
       // descriptors are linear in the address: the tile's base once, a constant per k step
-      const uint64_t q_desc = umma_desc(smem_u32(q_s));
       const uint64_t k_desc0 = umma_desc(smem_u32(k_s));
       auto issue_scores = [&](int i) {
-        const int s = i % STAGES;
+        const int s = i % K_STAGES;
         tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
         const uint32_t tmem_s = tmem_base + (uint32_t)((i & 1) * S_COLS);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (uint32_t)(k >> 2), in = (uint32_t)(k & 3) * 32u;
-          umma(tmem_s, q_desc + ((off * Q_SLICE + in) >> 4), k_desc + ((off * KV_SLICE + in) >> 4), idesc_s, k != 0);
+          umma_a_tmem(tmem_s, tmem_base + (uint32_t)(Q_COL + k * 8), k_desc + ((off * KV_SLICE + in) >> 4), idesc_s, k != 0);
         }
         umma_commit(&s_full[i & 1]);
+        umma_commit(&k_empty[s]);
       };
-      // The eight products of S and the four of O += P V of a key tile have an issuing thread each
-      // (this one and warp PV_WARP): each waits for its own operands in order, neither polls for
-      // the other's.
-      // The scores of tile a need K[a] and, from the third tile on, that the group has read
-      // S[a % 2] (tile a - 2).
-      bool ok = true;
-      for (int a = 0; a < n_kt && ok; ++a) {
-        ok = mbar_wait(&kv_full[a % STAGES], (a / STAGES) & 1) &&
-             (a < 2 || mbar_wait(&s_free[a & 1], ((a - 2) >> 1) & 1));
+      // The scores of tile a need K[a] and, from the group's second tile on, that the group has
+      // read S[a % 2] (tile a - 2).
+      bool ok = mbar_wait(&q_ready, 0);
+      tc_fence_after();
+      for (int a = warp == 1 ? 0 : 1; a < n_kt && ok; a += 2) {
+        ok = a < 2 ? mbar_wait(&k_full[a % K_STAGES], (a / K_STAGES) & 1)
+                   : mbar_wait_both(&k_full[a % K_STAGES], (a / K_STAGES) & 1, &s_free[a & 1], ((a - 2) >> 1) & 1);
         if (ok) issue_scores(a);
       }
       if (!ok) failed = 1;
@@ -301,22 +362,18 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     if (lane == 0) {
       const uint32_t idesc_o = umma_idesc(BM, D) | (1u << 16);  // B (values) is N-major
       const uint64_t v_desc0 = umma_desc_mn(smem_u32(v_s), KV_SLICE);
-      const uint64_t p_desc0 = umma_desc(smem_u32(p_s));
       bool ok = true;
       for (int b = 0; b < n_kt && ok; ++b) {
-        ok = mbar_wait(&p_full[b & 1], (b >> 1) & 1);
+        const int g = b & 1, st = b % V_STAGES;
+        ok = mbar_wait_both(&v_full[st], (b / V_STAGES) & 1, &p_full[g], (b >> 1) & 1);
         if (!ok) break;
-        const int g = b & 1, st = b % STAGES;
         tc_fence_after();
         const uint64_t v_desc = v_desc0 + (uint64_t)(st * (KV_BYTES >> 4));
-        const uint64_t p_desc = p_desc0 + (uint64_t)(g * (P_BYTES >> 4));
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          umma(tmem_base + (uint32_t)(O_COL + g * D), p_desc + (uint64_t)(k * 2), v_desc + (uint64_t)(k * 128), idesc_o,
-               (b >= 2) || k != 0);
-        // the scores of this tile were complete before its P was written, so every product that
-        // read the stage is behind these commits
-        umma_commit(&kv_empty[st]);
+          umma_a_tmem(tmem_base + (uint32_t)(O_COL + g * D), tmem_base + (uint32_t)(P_COL + g * P_COLS + k * 8),
+                      v_desc + (uint64_t)(k * 128), idesc_o, (b >= 2) || k != 0);
+        umma_commit(&v_empty[st]);
         umma_commit(&o_done[g]);
       }
       if (!ok) failed = 1;
@@ -332,7 +389,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + (uint32_t)(g * S_COLS);
     const uint32_t o_addr = lane_addr + (uint32_t)(O_COL + g * D);
-    const uint32_t p_row = smem_u32(p_s + g * P_BYTES) + (uint32_t)r * 128u;
+    const uint32_t p_addr = lane_addr + (uint32_t)(P_COL + g * P_COLS);
     const float scale = p.scale_log2;
     const int page_shift = __ffs(p.page_size) - 1;  // page sizes are powers of two here
     float m_run = -INFINITY, l_run = 0.f;
@@ -361,7 +418,7 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[g]);
       // tiles every row of the CTA sees whole (most of them) skip the mask
-      const uint32_t bad = bad_pages[i % STAGES];
+      const uint32_t bad = bad_pages[i % BAD_SLOTS];
       if (!(key0 + BN - 1 <= pos0 && key0 >= lo_top) || bad != 0u) {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
@@ -420,14 +477,11 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
           tmem_st_wait();
         }
       }
-      // P row r: 8 pieces of 16 bytes, swizzled by the row
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        st_shared16(p_row + (uint32_t)((c ^ (r & 7)) << 4),
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]));
+      // P row r: 64 bfloat16 in the 32 columns of the group's A operand
+      tmem_st32(p_addr, pk);
       // value rows no row of this tile may see: zero them (whole 128-byte rows, every slice)
       if (key0 < lo || key0 + BN - 1 > pos_last || bad != 0u) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[i % STAGES], (i / STAGES) & 1))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&v_full[i % V_STAGES], (i / V_STAGES) & 1))) {
           ok = false;
           break;
         }
@@ -439,15 +493,16 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
           dead = pg < 0 || pg >= p.num_pages;
         }
         if (dead) {
-          const uint32_t row_addr = smem_u32(v_s + (i % STAGES) * KV_BYTES) + (uint32_t)key_row * 128u +
+          const uint32_t row_addr = smem_u32(v_s + (i % V_STAGES) * KV_BYTES) + (uint32_t)key_row * 128u +
                                     (uint32_t)(r & 1) * 64u;
 #pragma unroll
           for (int h = 0; h < KD; ++h)
 #pragma unroll
             for (int c = 0; c < 4; ++c) st_shared16(row_addr + h * KV_SLICE + c * 16, make_uint4(0, 0, 0, 0));
         }
+        fence_async_smem();
       }
-      fence_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[g]);

@@ -35,6 +35,28 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return mbar_wait_limit(bar, parity, WAIT_LIMIT);
 }
+// Two barriers at once: both are asked in the same turn, so that a thread which needs both pays
+// the shared-memory pipe's latency once, not twice in a row.
+__device__ __forceinline__ bool mbar_wait_both(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b) {
+  const uint32_t addr_a = smem_u32(bar_a), addr_b = smem_u32(bar_b);
+  uint32_t got_a = 0, got_b = 0;  // a phase that was seen complete stays so, whatever the barrier does next
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done_a, done_b;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%2], %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%4], %5;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "selp.u32 %1, 1, 0, q;\n\t}"
+        : "=r"(done_a), "=r"(done_b)
+        : "r"(addr_a), "r"(parity_a), "r"(addr_b), "r"(parity_b)
+        : "memory");
+    got_a |= done_a;
+    got_b |= done_b;
+    if (got_a && got_b) return true;
+  }
+  return false;
+}
 
 // address of the same shared-memory location in CTA `rank` of the cluster
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
@@ -129,6 +151,17 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// The same with the A operand in tensor memory: row i of A in lane i, two bfloat16 per 32-bit column
+// (the lower k in the lower half), 8 columns per product of K 16.
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
