@@ -372,6 +372,52 @@ def tma_ingest_rate() -> dict:
             "table": table}
 
 
+def attention_prefill_times() -> dict:
+    """The attention kernel for portions of prompts alone: one prompt, causal, by head counts,
+    length and how its pages lie in the pool (one after the other, as a pool that is not
+    fragmented hands them out, or scattered).  CUDA events over 20 launches, tile lists built once."""
+    import torch
+    from dispec_b200.ops import attention as A
+    from dispec_b200.ops import library as L
+    dev = torch.device("cuda:0")
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    rows = []
+    for H, KVH, D, T, page in ((12, 2, 128, 2048, 16), (28, 4, 128, 2048, 16), (40, 8, 128, 2048, 16),
+                               (14, 2, 64, 2048, 16), (12, 2, 128, 8192, 16), (12, 2, 128, 32768, 16),
+                               (12, 2, 128, 8192, 64)):
+        G, n = H // KVH, (T + page - 1) // page
+        gen = torch.Generator(device=dev).manual_seed(0)
+        q = torch.randn(T, H * D, device=dev, generator=gen).bfloat16()
+        times = {}
+        for order in ("consecutive", "scattered"):
+            ids = torch.arange(n, device=dev) if order == "consecutive" else torch.randperm(n + 4, device=dev, generator=gen)[:n]
+            kp = torch.randn(n + 4, KVH, page, D, device=dev, generator=gen).bfloat16()
+            vp = torch.randn(n + 4, KVH, page, D, device=dev, generator=gen).bfloat16()
+            table = ids.int().view(1, -1).contiguous()
+            starts = lambda per: (i32([0] * len(range(0, T, per))), i32(list(range(0, T, per))), len(range(0, T, per)))
+            small, big = starts(A.tokens_per_tile(G)), starts(A.prefill_tokens_per_tile(G))
+            out = torch.zeros_like(q)
+            q_start, ctx_len = i32([0, T]), i32([T])
+            run = lambda: A.paged_attention_tiles(q, H * D, kp, vp, table, q_start, ctx_len, small[0], small[1],
+                                                  small[2], 0, out, H, KVH, D, 0, D ** -0.5, 1, big)
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            L.raise_on_device_error("attention for portions of prompts")
+            times[order] = e0.elapsed_time(e1) / 20 * 1000
+        flops = 4 * H * D * T * (T + 1) / 2
+        rows.append({"heads": H, "kv_heads": KVH, "head_dim": D, "tokens": T, "page": page,
+                     "us_pages_consecutive": round(times["consecutive"], 1), "us_pages_scattered": round(times["scattered"], 1),
+                     "tflops_consecutive": round(flops / times["consecutive"] / 1e6), "tflops_scattered": round(flops / times["scattered"] / 1e6)})
+    return {"only": "attn-prefill", "rows": rows}
+
+
 def decode_timeline(args) -> dict:
     """Where the time of a decode step's kernels goes: the weight-streaming products and the
     single-token attention of a captured step (few layers of the recorded shape) record the global
@@ -459,6 +505,8 @@ def run_ours(args) -> dict:
 
     if args.only == "mma-rate":
         return mma_issue_rate()
+    if args.only == "attn-prefill":
+        return attention_prefill_times()
     if args.only == "tma-rate":
         return tma_ingest_rate()
     if args.only == "timeline":
@@ -632,11 +680,12 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill"], default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
                          "tcgen05.mma for one to four issuing threads; tma-rate: bytes a clock an SM takes in from "
-                         "the L2 by TMA, by the size of a request")
+                         "the L2 by TMA, by the size of a request; attn-prefill: the attention kernel for portions of prompts "
+                         "alone, by shape, length and the order of the pages")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

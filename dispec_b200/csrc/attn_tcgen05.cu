@@ -1,7 +1,8 @@
 // Causal grouped-query attention for portions of prompts on the fifth-generation tensor cores:
-// S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory, keys and values
-// come from the paged cache by TMA (one box per page), bfloat16 in, 32-bit softmax and
-// accumulation.  Compiled once per head size (-DDSP_HEAD_DIM=64 or 128).
+// S = Q K^T and O += P V are tcgen05.mma with the accumulators and the A operands (Q, P) in tensor
+// memory, keys and values come from the paged cache by TMA (one request per page, or one per
+// operand and tile where the tile's pages follow one another in the pool), bfloat16 in, 32-bit
+// softmax and accumulation.  Compiled once per head size (-DDSP_HEAD_DIM=64 or 128).
 //
 // A tile is 128 query rows of one KV head of one sequence; a row is a (token, head-in-group)
 // pair, so the G query heads that share a KV head share every key/value load.  Keys are walked in
@@ -12,13 +13,13 @@
 //   warps 1, 11 one thread each issues the score products S[i] = Q K[i]^T of one softmax group;
 //   warp 10     one thread issues the output products O[i % 2] += P[i] V[i];
 //   warps 2..9  two softmax groups of four warps.  Group g owns the key tiles i = g, g + 2, ...: its own
-//               score buffer S[g] and output accumulator O[g] in tensor memory, its own P[g] in
-//               shared memory and its own running maximum and sum, so the two groups never exchange
-//               anything until the end and the softmax of tile i + 1 runs beside that of tile i.
-//               In a group thread r owns row r (accumulator lane r): it reads its 64 scores,
-//               rescales its row of O[g] when the running maximum moved by more than 2^8, and writes
-//               P as bfloat16 in the swizzled layout the second product reads.  At the end group 0
-//               merges the two partial results (like two key splits) and stores the rows.
+//               score buffer S[g], output accumulator O[g] and P[g] in tensor memory and its own
+//               running maximum and sum, so the two groups never exchange anything until the end
+//               and the softmax of tile i + 1 runs beside that of tile i.  In a group thread r owns
+//               row r (lane r of tensor memory): it reads its 64 scores, rescales its row of O[g]
+//               when the running maximum moved by more than 2^8, and writes P as bfloat16, two per
+//               column.  At the end group 0 merges the two partial results (like two key splits)
+//               and stores the rows.
 // The query at position p sees keys b with max(0, p - window + 1) <= b <= p.  Value rows of keys
 // that no row of the tile may see (beyond the last position, before the window, on pages that were
 // given back) are zeroed in shared memory before the second product, so stale cache contents never
@@ -53,7 +54,8 @@ static_assert(SMEM_BYTES + 1536 <= 227 * 1024, "dynamic and static shared memory
 // both products, two bfloat16 per column: P of each group (64 keys) and the Q tile.  Operands that
 // the tensor cores take from tensor memory cost no shared-memory bandwidth: with Q and P in shared
 // memory, a key tile moved 128 KB through the shared-memory port (Q 32, K 16, P 16 written and 16
-// read, V 16, the arriving tiles 32), 1,000 of the 1,200 cycles that a tile took.
+// read, V 16, the arriving tiles 32), 1,000 of the 1,200 cycles that a tile took, and every
+// barrier operation of the control warps waited in that queue.
 constexpr int S_COLS = BN;                 // columns of one score buffer
 constexpr int O_COL = 2 * S_COLS;          // the two output accumulators follow the two score buffers
 constexpr int P_COLS = BN / 2;             // columns of one group's P
@@ -255,9 +257,13 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
     };
     int pg = -2, pg_next = load_chunk(0);
     uint32_t bad_mask = 0, live_mask = 0, run_mask = 0;
-    int sk = 0, rk = 0, sv = 0, rv = 0;  // ring slots of K and of V and their use counts
-    for (int i = 0; i < n_kt; ++i) {
-      const int in_chunk = i & chunk_mask;
+    // Two tiles per turn, each with a lane of its own that waits for the tile's ring slots and
+    // issues its requests: the waits, the announcements and the requests of both run side by side
+    // (a turn costs some 900 cycles of latencies in a row, whatever it does, and at one tile per
+    // turn this warp set the kernel's pace once the products took their operands from tensor memory).
+    int sk = 0, rk = 0, sv = 0, rv = 0;  // ring slots of K and of V of the turn's first tile, and their use counts
+    for (int i = 0; i < n_kt; i += 2) {
+      const int in_chunk = i & chunk_mask;  // chunks hold an even number of tiles
       if (in_chunk == 0) {
         pg = pg_next;
         pg_next = load_chunk((i >> chunk_shift) + 1);
@@ -273,55 +279,68 @@ attn_tcgen05_kernel(const Params p, int tile_offset, const __grid_constant__ CUt
         run_mask = __ballot_sync(0xffffffffu, pg >= 0 && pg == first_pg + page_in_tile &&
                                                   first_pg + pages_per_tile <= p.num_pages);
       }
-      const int shift = in_chunk << ppt_shift;              // the tile's first lane
+      const int second = (lane >> ppt_shift) - in_chunk;  // 0, 1: this lane holds a page of the turn's first, second tile
+      const bool mine = (second == 0 || second == 1) && i + second < n_kt;
+      const int shift = (in_chunk + (second == 1 ? 1 : 0)) << ppt_shift;  // first lane of this lane's tile
       const uint32_t live = (live_mask >> shift) & tile_lanes;
       const bool in_run = p.page_runs && ((run_mask >> shift) & tile_lanes) == tile_lanes;
-      const bool leader = lane == shift;
-      const bool mine = (lane >> ppt_shift) == in_chunk;   // this lane holds a page of the tile
-      int ok = 1;
-      if (leader) ok = !failed && mbar_wait_both(&k_empty[sk], (rk & 1) ^ 1, &v_empty[sv], (rv & 1) ^ 1);
-      if (!__all_sync(0xffffffffu, ok)) {
-        if (leader) failed = 1;
-        break;
+      const bool leader = mine && lane == shift;
+      int my_sk = sk, my_rk = rk, my_sv = sv, my_rv = rv;
+      if (second == 1) {
+        if (++my_sk == K_STAGES) {
+          my_sk = 0;
+          ++my_rk;
+        }
+        if (++my_sv == V_STAGES) {
+          my_sv = 0;
+          ++my_rv;
+        }
       }
       if (leader) {
-        bad_pages[i % BAD_SLOTS] = (bad_mask >> shift) & tile_lanes;  // published by the arrival on k_full below
-        if (live == 0) {
-          mbar_arrive(&k_full[sk]);
-          mbar_arrive(&v_full[sv]);
+        if (*(volatile int*)&failed == 0 &&
+            mbar_wait_both(&k_empty[my_sk], (my_rk & 1) ^ 1, &v_empty[my_sv], (my_rv & 1) ^ 1)) {
+          bad_pages[(i + second) % BAD_SLOTS] = (bad_mask >> shift) & tile_lanes;  // published by the arrival on k_full below
+          if (live == 0) {
+            mbar_arrive(&k_full[my_sk]);
+            mbar_arrive(&v_full[my_sv]);
+          } else {
+            mbar_expect_tx(&k_full[my_sk], (uint32_t)__popc(live) * page_bytes);
+            mbar_expect_tx(&v_full[my_sv], (uint32_t)__popc(live) * page_bytes);
+          }
+          // The tile's pages lie one after the other in the pool (what a pool hands out while it
+          // is not fragmented): one request per operand brings them all, where a page of 16
+          // tokens otherwise takes KD requests of 2 KB, and the requests, not the bytes, are what
+          // the TMA unit's time goes to.  Both ways leave the same bytes at the same places.
+          if (in_run) {
+            tma_load_4d(k_s + my_sk * KV_BYTES, &runs_k, &k_full[my_sk], 0, kvh * p.page_size, pg, 0);
+            tma_load_4d(v_s + my_sv * KV_BYTES, &runs_v, &v_full[my_sv], 0, kvh * p.page_size, pg, 0);
+          }
         } else {
-          mbar_expect_tx(&k_full[sk], (uint32_t)__popc(live) * page_bytes);
-          mbar_expect_tx(&v_full[sv], (uint32_t)__popc(live) * page_bytes);
+          failed = 1;  // nothing more is loaded; the warps that wait for tiles give up in their turn
         }
       }
-      // The tile's pages lie one after the other in the pool (what a pool hands out while it is
-      // not fragmented): one request per operand brings them all, where a page of 16 tokens
-      // otherwise takes KD requests of 2 KB, and the requests, not the bytes, are what the TMA
-      // unit's time goes to.  Both ways leave the same bytes at the same places.
-      if (in_run) {
-        if (leader) {
-          tma_load_4d(k_s + sk * KV_BYTES, &runs_k, &k_full[sk], 0, kvh * p.page_size, pg, 0);
-          tma_load_4d(v_s + sv * KV_BYTES, &runs_v, &v_full[sv], 0, kvh * p.page_size, pg, 0);
-        }
-      } else {
-        __syncwarp();  // the bytes are announced before any lane's load can count them
-        if (mine && pg >= 0) {
+      if (!__all_sync(0xffffffffu, !mine || in_run)) {
+        // some tile of the turn goes page by page: the bytes were announced above, before any
+        // lane's load can count them
+        if (mine && !in_run && pg >= 0 && *(volatile int*)&failed == 0) {
           const int row = (pg * p.KVH + kvh) * p.page_size;
           const int dst = page_in_tile * p.page_size * 128;
 #pragma unroll
           for (int h = 0; h < KD; ++h) {
-            tma_load_2d(k_s + sk * KV_BYTES + dst + h * KV_SLICE, &map_k, &k_full[sk], h * 64, row);
-            tma_load_2d(v_s + sv * KV_BYTES + dst + h * KV_SLICE, &map_v, &v_full[sv], h * 64, row);
+            tma_load_2d(k_s + my_sk * KV_BYTES + dst + h * KV_SLICE, &map_k, &k_full[my_sk], h * 64, row);
+            tma_load_2d(v_s + my_sv * KV_BYTES + dst + h * KV_SLICE, &map_v, &v_full[my_sv], h * 64, row);
           }
         }
       }
-      if (++sk == K_STAGES) {
-        sk = 0;
-        ++rk;
-      }
-      if (++sv == V_STAGES) {
-        sv = 0;
-        ++rv;
+      for (int u = 0; u < 2; ++u) {
+        if (++sk == K_STAGES) {
+          sk = 0;
+          ++rk;
+        }
+        if (++sv == V_STAGES) {
+          sv = 0;
+          ++rv;
+        }
       }
     }
   } else if (warp == 1 || warp == S1_WARP) {
