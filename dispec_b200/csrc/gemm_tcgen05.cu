@@ -67,6 +67,7 @@ __device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_
         reinterpret_cast<uint4*>(dst)[j] = oraw;
       }
     } else {
+#pragma unroll  // constant indices: the accumulators stay in registers
       for (int t = 0; t < 16; ++t) {
         const float g = __uint_as_float(v[t]), u = __uint_as_float(v[16 + t]);
         dst[t] = from_f32<TOut>(silu_times(g, u));
@@ -95,11 +96,14 @@ __device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_
       reinterpret_cast<uint4*>(dst)[j] = oraw;
     }
   } else {
-    for (int t = 0; t < valid; ++t) {
-      float x = __uint_as_float(v[t]);
-      if (e.bias) x += __bfloat162float(e.bias[col + t]);
-      if (res) x += to_f32(res[t]);
-      dst[t] = from_f32<TOut>(x);
+#pragma unroll  // constant indices: a loop up to `valid` would put the accumulators into local memory on every path
+    for (int t = 0; t < 32; ++t) {
+      if (t < valid) {
+        float x = __uint_as_float(v[t]);
+        if (e.bias) x += __bfloat162float(e.bias[col + t]);
+        if (res) x += to_f32(res[t]);
+        dst[t] = from_f32<TOut>(x);
+      }
     }
   }
 }
@@ -262,6 +266,57 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // with multicast frees the stage in both CTAs and announces the finished accumulator to both;
 // both CTAs' epilogue warps arrive on the leader's "accumulator empty" barrier.  No TMA load is
 // multicast.
+// What a chunk of 32 outputs of a row needs beside its accumulators, asked for before they arrive:
+// in the loop "accumulators of the chunk, then its bias and residual, then the stores", every
+// chunk paid the latency of tensor memory and then that of global memory (1,200 to 1,500 cycles a
+// chunk; 5 us for the one tile of a CTA pair in the three narrow products of a layer).
+struct ChunkOperands {
+  uint4 res[4];
+  uint4 bias[4];
+  bool fast;  // bfloat16 output, a whole chunk inside the matrix, 16-byte aligned operands
+};
+template <typename TOut>
+__device__ __forceinline__ void fetch_chunk_operands(const Epilogue& e, int row, int col, ChunkOperands& op) {
+  op.fast = false;
+  if (sizeof(TOut) != 2 || e.epilogue != EPI_PLAIN || row >= e.M || col + 32 > e.N) return;
+  const TOut* dst = reinterpret_cast<const TOut*>(e.C) + (size_t)row * e.ldc + col;
+  const TOut* res = e.residual ? reinterpret_cast<const TOut*>(e.residual) + (size_t)row * e.ldr + col : nullptr;
+  const bf16* bias = e.bias ? e.bias + col : nullptr;
+  if ((((uintptr_t)dst | (uintptr_t)res | (uintptr_t)bias) % 16) != 0) return;
+  op.fast = true;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    op.res[j] = res ? reinterpret_cast<const uint4*>(res)[j] : make_uint4(0u, 0u, 0u, 0u);
+    op.bias[j] = bias ? __ldg(reinterpret_cast<const uint4*>(bias) + j) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+// The chunk's outputs from its accumulators and the operands fetched before; the sums are formed
+// as in store_row_chunk: accumulator + bias + residual in 32 bits, rounded once.
+template <typename TOut>
+__device__ __forceinline__ void store_row_chunk_with(const Epilogue& e, const uint32_t (&v)[32], int row, int col,
+                                                     const ChunkOperands& op) {
+  if (!op.fast) {
+    store_row_chunk<TOut>(e, v, row, col);
+    return;
+  }
+  bf16* dst = reinterpret_cast<bf16*>(e.C) + (size_t)row * e.ldc + col;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const bf16* rb = reinterpret_cast<const bf16*>(&op.res[j]);
+    const bf16* bb = reinterpret_cast<const bf16*>(&op.bias[j]);
+    uint4 oraw;
+    bf16* ob = reinterpret_cast<bf16*>(&oraw);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      float x = __uint_as_float(v[j * 8 + t]);
+      if (e.bias) x += __bfloat162float(bb[t]);
+      if (e.residual) x += __bfloat162float(rb[t]);
+      ob[t] = __float2bfloat16(x);
+    }
+    reinterpret_cast<uint4*>(dst)[j] = oraw;
+  }
+}
+
 constexpr int STAGES2 = 3;   // ring slots of the pair kernel, SUB k blocks each
 constexpr int SUB = 2;       // k blocks per ring slot: one barrier round trip of the issuing thread per 128 of k
 constexpr int HALF_B_BYTES = (BN / 2) * BK * 2;
@@ -466,10 +521,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      for (int c0 = 32 * ((warp - 2) >> 2); c0 < BNP; c0 += 32 * (EPI_WARPS / 4)) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 256 + c0), v);
-        store_row_chunk<TOut>(e, v, row, n0 + c0);
+      // two chunks in flight: while one is turned into outputs, the accumulators, the bias and
+      // the residual of the next are on their way
+      static_assert(BNP % 64 == 0 && EPI_WARPS == 4, "chunks are taken in pairs by four warps");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 256);
+      uint32_t va[32], vb[32];
+      ChunkOperands oa, ob;
+      tmem_ld32_nowait(taddr, va);
+      fetch_chunk_operands<TOut>(e, row, n0, oa);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BNP; c0 += 64) {
+        tmem_ld_wait();
+        tmem_ld32_nowait(taddr + (uint32_t)(c0 + 32), vb);
+        fetch_chunk_operands<TOut>(e, row, n0 + c0 + 32, ob);
+        store_row_chunk_with<TOut>(e, va, row, n0 + c0, oa);
+        tmem_ld_wait();
+        if (c0 + 64 < BNP) {
+          tmem_ld32_nowait(taddr + (uint32_t)(c0 + 64), va);
+          fetch_chunk_operands<TOut>(e, row, n0 + c0 + 64, oa);
+        }
+        store_row_chunk_with<TOut>(e, vb, row, n0 + c0 + 32, ob);
       }
       tc_fence_before();
       __syncwarp();
