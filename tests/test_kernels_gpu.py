@@ -66,6 +66,37 @@ def test_rms_norm(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(515, 1536), (700, 200), (513, 3584), (512, 1000), (600, 5120), (1029, 72)])
+def test_rms_norm_of_many_rows(dtype, rows, hidden):
+    """Hundreds of rows, as in a portion of a prompt, at widths of every kernel form (vectors that
+    fit a CTA's registers, wider ones, widths that are no multiple of a vector): the same checks as
+    for a few rows, and row for row the result of the same rows taken a hundred at a time."""
+    from dispec_b200 import ops
+    x = rnd((rows, hidden), dtype, 13, 2.0)
+    w = (1 + rnd((hidden,), torch.float32, 14, 0.1)).to(dtype)
+    eps = 1e-6
+    y = ops.rms_norm(x, w, eps)
+    xf = x.float()
+    n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype).float()
+    torch.testing.assert_close(y.float(), (w.float() * n).to(dtype).float(), **tol(dtype))
+    few = torch.cat([ops.rms_norm(x[i:i + 100].contiguous(), w, eps) for i in range(0, rows, 100)])
+    torch.testing.assert_close(y.float(), few.float(), **tol(dtype))
+    d = rnd((rows, hidden), dtype, 15)
+    x2 = x.clone()
+    y2 = ops.rms_norm(x2, w, eps, delta=d, write_back=True)
+    s = (x.float() + d.float()).to(dtype)
+    assert torch.equal(x2, s)
+    sf = s.float()
+    n2 = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype).float()
+    torch.testing.assert_close(y2.float(), (w.float() * n2).to(dtype).float(), **tol(dtype))
+    picked = torch.randperm(rows, generator=torch.Generator().manual_seed(3))[:rows - 3].to(torch.int32).to(dev())
+    x3 = x.clone()
+    y3 = ops.rms_norm(x3, w, eps, delta=d, rows=picked)
+    assert torch.equal(x3, x)
+    torch.testing.assert_close(y3.float(), y2[picked.long()].float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     from dispec_b200 import ops
     gu = rnd((5, 2 * 224), dtype, 6, 3.0)
