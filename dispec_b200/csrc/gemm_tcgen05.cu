@@ -319,8 +319,6 @@ __device__ __forceinline__ void store_row_chunk_with(const Epilogue& e, const ui
 
 constexpr int STAGES2 = 3;   // ring slots of the pair kernel, SUB k blocks each
 constexpr int SUB = 2;       // k blocks per ring slot: one barrier round trip of the issuing thread per 128 of k
-constexpr int HALF_B_BYTES = (BN / 2) * BK * 2;
-constexpr int STAGE2_BYTES = A_BYTES + HALF_B_BYTES;  // 32 KB per CTA
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -574,10 +572,7 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
   DSP_REQUIRE(out_dtype == DSP_BF16 || out_dtype == DSP_F32, "dsp_gemm_tcgen05: unknown output dtype %d", out_dtype);
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_gemm_tcgen05: no device error word");
-  CUtensorMap map_a, map_w;
-  DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
-  DSP_REQUIRE(make_map(&map_w, W, N, K, K, pair_mode ? BN / 2 : BN),
-              "dsp_gemm_tcgen05: cannot encode the tensor map of W");
+  CUtensorMap map_a, map_w;  // encoded below, once the tile shape is known (an encoding costs the host a microsecond)
   DSP_REQUIRE(epilogue == EPI_PLAIN || (N % 32 == 0 && bias == nullptr && residual == nullptr),
               "dsp_gemm_tcgen05: the SwiGLU epilogue needs N in whole blocks of 32 and no bias or residual");
   Epilogue e;
@@ -638,6 +633,8 @@ extern "C" int dsp_gemm_tcgen05(const void* A, long lda, const void* W, const vo
     DSP_CHECK_LAUNCH("dsp_gemm_tcgen05 (CTA pairs)");
     return 0;
   }
+  DSP_REQUIRE(make_map(&map_a, A, M, K, lda, BM), "dsp_gemm_tcgen05: cannot encode the tensor map of A");
+  DSP_REQUIRE(make_map(&map_w, W, N, K, K, BN), "dsp_gemm_tcgen05: cannot encode the tensor map of W");
   const long tiles = (long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid((unsigned)(tiles < num_sms ? tiles : num_sms));
   if (out_dtype == DSP_BF16) {
