@@ -237,7 +237,7 @@ class CacheManager:
             return []
         released = []
         for g, table in enumerate(r.tables):
-            for page in reversed(table):  # the free stack then hands them out in table order again
+            for page in table:
                 if page >= 0:
                     self.pools[g].release(page)
                     released.append((g, page))
@@ -257,8 +257,8 @@ class CacheManager:
                 promised += r.reserved[g]
             assert len(held) == len(set(held)), f"group {g}: a page is held twice"
             free = set(pool._free)
-            assert len(free) == len(pool._free), f"group {g}: a page is on the free stack twice"
-            assert not (free & set(held)), f"group {g}: a held page is on the free stack"
+            assert len(free) == len(pool._free), f"group {g}: a page is on the free list twice"
+            assert not (free & set(held)), f"group {g}: a held page is on the free list"
             assert len(free) + len(held) == pool.num_pages, f"group {g}: a page is lost"
             assert promised == pool.reserved, f"group {g}: promises {promised} != {pool.reserved}"
             assert pool.reserved <= len(free), f"group {g}: more promised than free"

@@ -51,6 +51,40 @@ def test_a_request_after_another_gets_its_pages_in_ascending_order_again():
     m.check()
 
 
+def test_portions_of_prompts_get_runs_of_consecutive_pages_while_requests_come_and_go():
+    """The attention kernel for portions of prompts fetches a key tile with one request where the
+    tile's pages follow one another in the pool.  Requests that take their pages portion by portion,
+    beside each other, and end in any order still get such runs: here at least three quarters of
+    the aligned groups of four pages, over a random workload on a pool that is used several times over."""
+    rng = random.Random(5)
+    m = CacheManager([CacheGroupSpec.key_value(2, 16)], page_size=16, num_pages=512, max_num_seqs=8)
+    live, groups, in_run, next_id = {}, 0, 0, 0
+    for _ in range(400):
+        if len(live) < 4 and rng.random() < 0.5:
+            live[next_id] = [0, rng.choice([300, 700, 1500, 2048])]
+            m.admit(next_id)
+            next_id += 1
+        for rid in list(live):
+            have, want = live[rid]
+            if have < want:
+                step = min(want - have, rng.choice([64, 256, 512]))
+                try:
+                    m.extend(rid, have + step)
+                except OutOfPagesError:
+                    continue
+                m.commit(rid, have + step)
+                live[rid][0] = have + step
+            elif rng.random() < 0.3:
+                table = list(m.block_table(rid))
+                for i in range(0, len(table) - 3, 4):
+                    groups += 1
+                    in_run += all(table[i + j] == table[i] + j for j in range(4))
+                m.free(rid)
+                del live[rid]
+        m.check()
+    assert groups > 300 and in_run >= 0.75 * groups, (in_run, groups)
+
+
 def test_extend_takes_nothing_when_it_cannot_take_all():
     groups = [CacheGroupSpec.key_value(1, 8), CacheGroupSpec.key_value(1, 8, window=4)]
     m = CacheManager(groups, page_size=2, num_pages=[10, 2], max_num_seqs=2)
